@@ -1,0 +1,128 @@
+// Host launcher of the tcgen05 GEMM: builds the three tensor maps, picks the template instance and
+// launches one persistent CTA per SM.
+#include "gemm_sm100.cuh"
+#include "tensormap.h"
+#include "yv_ops.h"
+
+namespace yv {
+
+namespace {
+
+int g_sm_count = 0;
+
+int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+int launch_instance(const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, typename OutT>
+int dispatch_layout(const GemmArgs& a, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (!a.a_mn && !a.b_mn) return launch_instance<BN, false, false, OutT>(p, grid, stream);
+  if (!a.a_mn && a.b_mn) return launch_instance<BN, false, true, OutT>(p, grid, stream);
+  if (a.a_mn && a.b_mn) return launch_instance<BN, true, true, OutT>(p, grid, stream);
+  return launch_instance<BN, true, false, OutT>(p, grid, stream);
+}
+
+}  // namespace
+
+int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return 0;
+  if (a.a == nullptr || a.b == nullptr || a.c == nullptr) return -10;
+  const int out_bytes = a.out_fp32 ? 4 : 2;
+  int bn = a.bn;
+  if (bn == 0) {
+    bn = 256;
+    // prefer the tile width that wastes least of N
+    const int waste256 = ((a.N + 255) / 256) * 256 - a.N;
+    const int waste128 = ((a.N + 127) / 128) * 128 - a.N;
+    if (waste128 < waste256 || a.N <= 128) bn = 128;
+  }
+  if (bn != 128 && bn != 256) return -11;
+
+  GemmParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.mode = a.mode;
+  p.accumulate = a.accumulate;
+  p.num_groups = a.num_groups;
+  p.tile_expert = a.tile_expert;
+  p.num_m_tiles = a.num_m_tiles;
+  p.seg_offsets = a.seg_offsets;
+  p.status = a.status;
+  p.b_group_stride = 0;
+  p.c_group_stride = 0;
+
+  // extents of the stored operands
+  uint64_t a_inner, a_outer, b_inner, b_outer, c_outer;
+  const uint64_t groups = static_cast<uint64_t>(a.num_groups);
+  if (a.mode == kDense) {
+    a_inner = a.a_mn ? a.M : a.K;  a_outer = a.a_mn ? a.K : a.M;
+    b_inner = a.b_mn ? a.N : a.K;  b_outer = a.b_mn ? a.K : a.N;
+    c_outer = a.M;
+  } else if (a.mode == kGroupedM) {
+    if (a.a_mn || a.tile_expert == nullptr || a.num_m_tiles == nullptr) return -12;
+    if (a.rows_total % kBM != 0) return -13;
+    p.M = static_cast<int>(a.rows_total);
+    a_inner = a.K;  a_outer = a.rows_total;
+    b_inner = a.b_mn ? a.N : a.K;
+    p.b_group_stride = a.b_mn ? a.K : a.N;
+    b_outer = groups * static_cast<uint64_t>(p.b_group_stride);
+    if (a.b_mn && (a.K % kBK) != 0) return -14;   // a K tile must not run into the next expert's rows
+    c_outer = a.rows_total;
+  } else if (a.mode == kGroupedK) {
+    if (!a.a_mn || !a.b_mn || a.seg_offsets == nullptr) return -15;
+    if (a.M % kBM != 0) return -16;               // C tiles must not cross expert boundaries
+    a_inner = a.M;  a_outer = a.rows_total;
+    b_inner = a.N;  b_outer = a.rows_total;
+    p.c_group_stride = a.M;
+    c_outer = groups * static_cast<uint64_t>(a.M);
+  } else {
+    return -17;
+  }
+  const uint64_t lda = a.lda ? a.lda : a_inner;
+  const uint64_t ldb = a.ldb ? a.ldb : b_inner;
+  const uint64_t ldc = a.ldc ? a.ldc : static_cast<uint64_t>(a.N);
+
+  int r;
+  r = make_tmap_2d(&p.tma_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.a, a_inner, a_outer, lda, 64,
+                   a.a_mn ? kBK : kBM);
+  if (r != 0) return -20 + r;
+  r = make_tmap_2d(&p.tma_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.b, b_inner, b_outer, ldb, 64,
+                   a.b_mn ? kBK : static_cast<uint32_t>(bn));
+  if (r != 0) return -30 + r;
+  r = make_tmap_2d(&p.tma_c, a.out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                   out_bytes, a.c, static_cast<uint64_t>(a.N), c_outer, ldc, 128 / out_bytes, kBM);
+  if (r != 0) return -40 + r;
+
+  const int64_t tiles_m = (p.M + kBM - 1) / kBM;
+  const int64_t tiles_n = (a.N + bn - 1) / bn;
+  int64_t tiles = tiles_m * tiles_n * (a.mode == kGroupedK ? a.num_groups : 1);
+  const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
+  const int grid = static_cast<int>(tiles < cap ? tiles : cap);
+
+  if (bn == 256) {
+    return a.out_fp32 ? dispatch_layout<256, float>(a, p, grid, stream)
+                      : dispatch_layout<256, __nv_bfloat16>(a, p, grid, stream);
+  }
+  return a.out_fp32 ? dispatch_layout<128, float>(a, p, grid, stream)
+                    : dispatch_layout<128, __nv_bfloat16>(a, p, grid, stream);
+}
+
+}  // namespace yv

@@ -1,0 +1,333 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory ->
+// tcgen05.mma (UMMA 128 x BN x 16, fp32 accumulators in TMEM, double buffered) -> tcgen05.ld ->
+// shared staging -> TMA store (or TMA reduce-add when accumulating into C).
+//
+// One CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + MMA issue (one elected lane)
+//   warps 2..5  epilogue (each owns the 32 TMEM lanes  32*(warp%4) .. +31)
+//
+// Three problem modes share the main loop:
+//   kDense     C[M,N]          = A[M,K] * B
+//   kGroupedM  C[rows,N]       = A[rows,K] * B[expert(tile)]      rows are expert-sorted and each
+//                                 expert's segment is padded to a multiple of 128 rows
+//   kGroupedK  C[e][M,N]       = A[:, seg(e)] * B[seg(e), :]       the reduction runs over expert e's
+//                                 row segment (weight gradients of the grouped expert GEMMs)
+// Operand layouts are template flags: K-major ("row-major [rows, K]") or MN-major ("row-major [K, rows]").
+#pragma once
+#include "sm100.cuh"
+
+namespace yv {
+
+enum GemmMode : int { kDense = 0, kGroupedM = 1, kGroupedK = 2 };
+
+struct GemmParams {
+  CUtensorMap tma_a;
+  CUtensorMap tma_b;
+  CUtensorMap tma_c;
+  int M, N, K;                 // per-problem extents (kGroupedM: M = max rows; kGroupedK: K unused)
+  int mode;
+  int accumulate;              // 1: C += result through TMA reduce-add
+  int num_groups;              // experts (grouped modes)
+  int b_group_stride;          // kGroupedM: outer-dim rows of B per expert
+  int c_group_stride;          // kGroupedK: rows of C per expert (= M)
+  const int* tile_expert;      // kGroupedM: expert id of every 128-row tile
+  const int* num_m_tiles;      // kGroupedM: number of valid 128-row tiles (device scalar)
+  const int* seg_offsets;      // kGroupedK: [E+1] row offsets of the expert segments (multiples of 128)
+  uint32_t* status;            // device status word (0 = ok)
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupBand = 16;   // m-tiles per rasterisation band
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kEpiBytes = kBM * 128;            // 128 rows x 128 B per staging buffer
+  static constexpr int kEpiBufs = 2;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kEpiBufs * kEpiBytes + kBarrierBytes + 1024;
+};
+
+struct TileCoord {
+  int a_x, a_y;      // TMA coordinates of the first A box (x = inner)
+  int b_x, b_y;
+  int c_x, c_y;
+  int k_iters;
+};
+
+// Decode linear tile index -> coordinates.  Returns false when idx is past the end.
+template <int BN, bool A_MN, bool B_MN>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int tiles_m, int tiles_n, TileCoord& t) {
+  int m_blk, n_blk, group = 0;
+  if (p.mode == kGroupedK) {
+    const int per_group = tiles_m * tiles_n;
+    group = idx / per_group;
+    if (group >= p.num_groups) return false;
+    const int r = idx - group * per_group;
+    n_blk = r / tiles_m;
+    m_blk = r - n_blk * tiles_m;
+  } else {
+    if (idx >= tiles_m * tiles_n) return false;
+    const int band_tiles = kGroupBand * tiles_n;
+    const int band = idx / band_tiles;
+    const int r = idx - band * band_tiles;
+    const int band_m = min(kGroupBand, tiles_m - band * kGroupBand);
+    n_blk = r / band_m;
+    m_blk = band * kGroupBand + (r - n_blk * band_m);
+  }
+  const int m0 = m_blk * kBM, n0 = n_blk * BN;
+  int k_begin = 0, k_len = p.K;
+  int b_outer_off = 0, c_row_off = 0;
+  if (p.mode == kGroupedM) {
+    const int e = p.tile_expert[m_blk];
+    b_outer_off = e * p.b_group_stride;
+  } else if (p.mode == kGroupedK) {
+    k_begin = p.seg_offsets[group];
+    k_len = p.seg_offsets[group + 1] - k_begin;
+    c_row_off = group * p.c_group_stride;
+  }
+  t.k_iters = (k_len + kBK - 1) / kBK;
+  if (A_MN) { t.a_x = m0; t.a_y = k_begin; } else { t.a_x = k_begin; t.a_y = m0; }
+  if (B_MN) { t.b_x = n0; t.b_y = b_outer_off + k_begin; } else { t.b_x = k_begin; t.b_y = b_outer_off + n0; }
+  t.c_x = n0;
+  t.c_y = c_row_off + m0;
+  return true;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int kStages = S::kStages;
+  constexpr int kColsPerChunk = 128 / sizeof(OutT);       // columns covered by one 128-byte staging row
+  constexpr int kChunks = BN / kColsPerChunk;
+  constexpr uint32_t kTmemCols = (2 * BN <= 512) ? 2 * BN : 512;
+  constexpr uint32_t kIdesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_epi = smem + kStages * S::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + S::kEpiBufs * S::kEpiBytes);
+  uint64_t* full_bar = bars;                       // [kStages]
+  uint64_t* empty_bar = bars + kStages;            // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;         // [2]
+  uint64_t* acc_empty = bars + 2 * kStages + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  int tiles_m, tiles_n;
+  tiles_n = (p.N + BN - 1) / BN;
+  if (p.mode == kGroupedM) {
+    tiles_m = *p.num_m_tiles;
+  } else {
+    tiles_m = (p.M + kBM - 1) / kBM;
+  }
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&p.tma_a);
+    tma_prefetch_desc(&p.tma_b);
+    tma_prefetch_desc(&p.tma_c);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int idx = blockIdx.x; ok; idx += gridDim.x) {
+        TileCoord t;
+        if (!decode_tile<BN, A_MN, B_MN>(p, idx, tiles_m, tiles_n, t)) break;
+        for (int k = 0; k < t.k_iters && ok; ++k, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          ok = mbar_wait(&empty_bar[s], ph ^ 1u, p.status);
+          if (!ok) break;
+          uint8_t* sa = smem + s * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(&full_bar[s], S::kStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_2d(sa + j * (kBK * 128), &p.tma_a, &full_bar[s], t.a_x + j * 64, t.a_y + k * kBK);
+          } else {
+            tma_load_2d(sa, &p.tma_a, &full_bar[s], t.a_x + k * kBK, t.a_y);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (kBK * 128), &p.tma_b, &full_bar[s], t.b_x + j * 64, t.b_y + k * kBK);
+          } else {
+            tma_load_2d(sb, &p.tma_b, &full_bar[s], t.b_x + k * kBK, t.b_y);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------------
+    if (elect_one()) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
+        TileCoord t;
+        if (!decode_tile<BN, A_MN, B_MN>(p, idx, tiles_m, tiles_n, t)) break;
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1u;
+        ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1u, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int k = 0; k < t.k_iters && ok; ++k, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          ok = mbar_wait(&full_bar[s], ph, p.status);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, kBK * 128, 1024)
+                                     : make_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, kBK * 128, 1024)
+                                     : make_smem_desc(sb + kk * 32, 16, 1024);
+            tc_mma_f16_ss(tmem_d, da, db, kIdesc, (k | kk) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);     // releases the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        if (t.k_iters > 0) {
+          tc_commit(&acc_full[acc]);
+        } else {
+          mbar_arrive(&acc_full[acc]);  // empty reduction: the epilogue writes zeros
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------------------------
+    const int quarter = warp & 3;                      // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;               // row of the tile owned by this thread
+    const bool issuer = (threadIdx.x == 64);           // first epilogue thread issues the TMA stores
+    uint32_t tile_it = 0, chunk_it = 0;
+    bool ok = true;
+    for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
+      TileCoord t;
+      if (!decode_tile<BN, A_MN, B_MN>(p, idx, tiles_m, tiles_n, t)) break;
+      const int acc = tile_it & 1;
+      const uint32_t acc_ph = (tile_it >> 1) & 1u;
+      ok = mbar_wait(&acc_full[acc], acc_ph, p.status);
+      // all 128 epilogue threads must take the same branch: barrier with an AND reduction
+      {
+        uint32_t all_ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred pin, pout;\n"
+            "setp.ne.u32 pin, %1, 0;\n"
+            "bar.red.and.pred pout, 1, 128, pin;\n"
+            "selp.u32 %0, 1, 0, pout;\n"
+            "}\n"
+            : "=r"(all_ok)
+            : "r"(static_cast<uint32_t>(ok))
+            : "memory");
+        ok = all_ok != 0u;
+      }
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kChunks; ++c, ++chunk_it) {
+        uint8_t* buf = smem_epi + (chunk_it & 1) * S::kEpiBytes;
+        // the store that last used this buffer (two chunks ago) must have finished reading it
+        if (issuer) tma_store_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t packed[32];
+        if (sizeof(OutT) == 2) {
+          uint32_t v0[32], v1[32];
+          if (t.k_iters > 0) {
+            tmem_ld32(taddr + c * 64, v0);
+            tmem_ld32(taddr + c * 64 + 32, v1);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { v0[i] = 0u; v1[i] = 0u; }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            packed[i] = pack_bf16(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
+            packed[16 + i] = pack_bf16(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
+          }
+        } else {
+          if (t.k_iters > 0) {
+            tmem_ld32(taddr + c * 32, packed);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) packed[i] = 0u;
+          }
+        }
+        // 128-byte row, eight 16-byte pieces, XOR-swizzled with the row index (TMA SWIZZLE_128B)
+        uint4* rowp = reinterpret_cast<uint4*>(buf + row * 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 v = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          rowp[j ^ (row & 7)] = v;
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          if (p.accumulate) {
+            tma_reduce_add_2d(&p.tma_c, buf, t.c_x + c * kColsPerChunk, t.c_y);
+          } else {
+            tma_store_2d(&p.tma_c, buf, t.c_x + c * kColsPerChunk, t.c_y);
+          }
+          tma_store_commit();
+        }
+      }
+      // all TMEM reads of this accumulator are done: hand it back to the MMA warp
+      tc_fence_before_sync();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (issuer) mbar_arrive(&acc_empty[acc]);
+    }
+    if (issuer) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------- teardown ---------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+    // A wait ran out somewhere: give copies that may still be in flight time to land before the
+    // shared memory and TMEM of this CTA are released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace yv
