@@ -1,0 +1,268 @@
+// Flash attention backward for sm_100a, as two tcgen05 kernels that recompute the probabilities from
+// the saved log-sum-exp (natural log of the scaled scores) and delta = rowsum(dO * O):
+//
+//   attn_bwd_dq_kernel   one CTA per (128-query block, query head, sequence), loops over key blocks:
+//        S = Q K^T, dP = dO V^T            (SS MMAs into TMEM)
+//        dS = P * (dP - delta)              (softmax warps: thread r = query row r; bf16 dS over S in TMEM)
+//        dQ += dS K                         (TS MMA; K tile read MN-major from the same shared tile)
+//   attn_bwd_dkv_kernel  one CTA per (128-key block, KV head, sequence), loops over the G query heads
+//        of the group and the query blocks that see this key block:
+//        S^T = K Q^T, dP^T = V dO^T         (lanes = keys, columns = queries)
+//        P^T, dS^T -> bf16 in TMEM
+//        dV += P^T dO,  dK += dS^T Q        (TS MMAs; dO and Q tiles read MN-major)
+//   Both scale by the softmax scale in the epilogue.  No atomics: every output row has one writer.
+#pragma once
+#include "sm100.cuh"
+
+namespace yv {
+
+struct AttnBwdParams {
+  CUtensorMap tma_q, tma_k, tma_v, tma_do;   // 3-D (d, head, token), box (64, 1, 128)
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  const float* lse;      // [hq, total_q] natural log
+  const float* delta;    // [hq, total_q]
+  const int* cu_q;
+  const int* cu_k;
+  int hq, hk;
+  int64_t dq_stride, dk_stride, dv_stride;
+  int64_t total_q;
+  int causal;
+  float scale;           // softmax scale
+  float scale_log2;      // scale * log2(e)
+  uint32_t* status;
+};
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct AttnBwdSmem {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kStages = 2;
+  static constexpr int kTotal = kTile * (2 + 2 * kStages) + 2 * 2 * 128 * 4 + 256 + 1024;
+};
+
+// --------------------------------------------------------------------------------------------------
+// dQ kernel
+// --------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnBwdParams p) {
+  using S = AttnBwdSmem<D>;
+  constexpr int kStages = S::kStages;
+  constexpr int kDBoxes = D / 64;
+  constexpr uint32_t kBoxBytes = 128 * 128;
+  constexpr uint32_t kIdescNT = make_idesc_bf16(128, 128, false, false);   // S, dP
+  constexpr uint32_t kIdescDQ = make_idesc_bf16(128, D, false, true);      // dS (TMEM) x K (MN-major)
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + S::kTile;
+  uint8_t* sK = sDO + S::kTile;
+  uint8_t* sV = sK + kStages * S::kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kStages * S::kTile + 2 * 2 * 128 * 4);
+  uint64_t* qdo_full = bars;            // [1]
+  uint64_t* k_full = bars + 1;          // [2]
+  uint64_t* v_full = bars + 3;          // [2]
+  uint64_t* k_empty = bars + 5;         // [2]  released after dQ MMA (last reader of K_j)
+  uint64_t* v_empty = bars + 7;         // [2]  released after dP MMA
+  uint64_t* sdp_full = bars + 9;        // [1]  S and dP ready
+  uint64_t* ds_full = bars + 10;        // [1]  128 arrivals: dS written
+  uint64_t* dq_done = bars + 11;        // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int hkv = h / (p.hq / p.hk);
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
+  const int n_qblk = (q_len + 127) / 128;
+  const int q_blk = n_qblk - 1 - static_cast<int>(blockIdx.x);
+  if (q_blk < 0) return;
+  const int q0 = q_blk * 128;
+  const int causal_shift = k_len - q_len;
+  int n_kv = (k_len + 127) / 128;
+  if (p.causal) {
+    const int last_key = q0 + 127 + causal_shift;
+    const int lim = last_key / 128 + 1;
+    n_kv = last_key < 0 ? 0 : (lim < n_kv ? lim : n_kv);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_full, 128);
+    mbar_init(dq_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one() && n_kv > 0) {
+      mbar_expect_tx(qdo_full, 2 * S::kTile);
+#pragma unroll
+      for (int c = 0; c < kDBoxes; ++c) {
+        tma_load_3d(sQ + c * kBoxBytes, &p.tma_q, qdo_full, c * 64, h, q_begin + q0);
+        tma_load_3d(sDO + c * kBoxBytes, &p.tma_do, qdo_full, c * 64, h, q_begin + q0);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1u;
+        ok = mbar_wait(&k_empty[s], ph ^ 1u, p.status);
+        if (!ok) break;
+        mbar_expect_tx(&k_full[s], S::kTile);
+#pragma unroll
+        for (int c = 0; c < kDBoxes; ++c)
+          tma_load_3d(sK + s * S::kTile + c * kBoxBytes, &p.tma_k, &k_full[s], c * 64, hkv, k_begin + j * 128);
+        ok = mbar_wait(&v_empty[s], ph ^ 1u, p.status);
+        if (!ok) break;
+        mbar_expect_tx(&v_full[s], S::kTile);
+#pragma unroll
+        for (int c = 0; c < kDBoxes; ++c)
+          tma_load_3d(sV + s * S::kTile + c * kBoxBytes, &p.tma_v, &v_full[s], c * 64, hkv, k_begin + j * 128);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && n_kv > 0) {
+      bool ok = mbar_wait(qdo_full, 0, p.status);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1u;
+        ok = mbar_wait(&k_full[s], ph, p.status);
+        if (!ok) break;
+        ok = mbar_wait(&v_full[s], ph, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t aK = smem_u32(sK + s * S::kTile), aV = smem_u32(sV + s * S::kTile);
+        // S = Q K^T and dP = dO V^T (these overwrite dS_{j-1}: in-order after the dQ MMA issued before)
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          tc_mma_f16_ss(tmem_base + kColS, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024),
+                        kIdescNT, kk != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          tc_mma_f16_ss(tmem_base + kColDP, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024),
+                        kIdescNT, kk != 0 ? 1u : 0u);
+        }
+        tc_commit(&v_empty[s]);
+        tc_commit(sdp_full);
+        ok = mbar_wait(ds_full, j & 1u, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          tc_mma_f16_ts(tmem_base + kColDQ, tmem_base + kColS + kk * 8, make_smem_desc(aK + kk * 2048, kBoxBytes, 1024),
+                        kIdescDQ, (j | kk) != 0 ? 1u : 0u);
+        }
+        tc_commit(&k_empty[s]);
+        tc_commit(dq_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const int q_pos = q0 + row;
+    const bool q_valid = q_pos < q_len;
+    const int key_limit = p.causal ? (q_pos + causal_shift) : (k_len - 1);
+    const int64_t stat_idx = static_cast<int64_t>(h) * p.total_q + q_begin + q_pos;
+    const float lse2 = q_valid ? p.lse[stat_idx] * kLog2e : 0.f;
+    const float delta = q_valid ? p.delta[stat_idx] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      ok = mbar_wait(sdp_full, j & 1u, p.status);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tS = tmem_base + lane_off + kColS, tDP = tmem_base + lane_off + kColDP;
+      const int kbase = j * 128;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tS + c * 32, sv);
+        tmem_ld32(tDP + c * 32, dv);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float r[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kidx = kbase + c * 32 + 2 * i + u;
+            const bool vis = q_valid && kidx <= key_limit && kidx < k_len;
+            const float pr = vis ? exp2f(__uint_as_float(sv[2 * i + u]) * p.scale_log2 - lse2) : 0.f;
+            r[u] = pr * (__uint_as_float(dv[2 * i + u]) - delta);
+          }
+          pk[c * 16 + i] = pack_bf16(r[0], r[1]);
+        }
+      }
+      {
+        uint32_t(&h0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
+        uint32_t(&h1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
+        tmem_st32(tS, h0);
+        tmem_st32(tS + 32, h1);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(ds_full);
+    }
+    if (ok && n_kv > 0) {
+      ok = mbar_wait(dq_done, (n_kv - 1) & 1u, p.status);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      __nv_bfloat16* orow = p.dq + static_cast<int64_t>(q_begin + q_pos) * p.dq_stride + static_cast<int64_t>(h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ov[32];
+        if (n_kv > 0) {
+          tmem_ld32(tmem_base + lane_off + kColDQ + c * 32, ov);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (q_valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(ov[8 * i + 0]) * p.scale, __uint_as_float(ov[8 * i + 1]) * p.scale);
+            v.y = pack_bf16(__uint_as_float(ov[8 * i + 2]) * p.scale, __uint_as_float(ov[8 * i + 3]) * p.scale);
+            v.z = pack_bf16(__uint_as_float(ov[8 * i + 4]) * p.scale, __uint_as_float(ov[8 * i + 5]) * p.scale);
+            v.w = pack_bf16(__uint_as_float(ov[8 * i + 6]) * p.scale, __uint_as_float(ov[8 * i + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+}  // namespace yv
+
+#include "attention_bwd_dkv.cuh"

@@ -1,0 +1,295 @@
+// dK / dV kernel of the flash attention backward (see attention_bwd.cuh for the scheme).
+// TMEM columns: [0,128) S^T then P^T (bf16), [128,256) dP^T then dS^T (bf16), [256,256+D) dV, [384,384+D) dK.
+#pragma once
+
+namespace yv {
+
+template <int D>
+__global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnBwdParams p) {
+  using S = AttnBwdSmem<D>;
+  constexpr int kStages = S::kStages;
+  constexpr int kDBoxes = D / 64;
+  constexpr uint32_t kBoxBytes = 128 * 128;
+  constexpr uint32_t kIdescNT = make_idesc_bf16(128, 128, false, false);
+  constexpr uint32_t kIdescAcc = make_idesc_bf16(128, D, false, true);
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + S::kTile;
+  uint8_t* sQ = sV + S::kTile;
+  uint8_t* sDO = sQ + kStages * S::kTile;
+  float* s_lse = reinterpret_cast<float*>(sDO + kStages * S::kTile);   // [2][128]
+  float* s_delta = s_lse + 2 * 128;                                     // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * 128);
+  uint64_t* kv_full = bars;             // [1]
+  uint64_t* q_full = bars + 1;          // [2]
+  uint64_t* do_full = bars + 3;         // [2]
+  uint64_t* q_empty = bars + 5;         // [2]
+  uint64_t* do_empty = bars + 7;        // [2]
+  uint64_t* sdp_full = bars + 9;        // [1]
+  uint64_t* pds_full = bars + 10;       // [1] 128 arrivals
+  uint64_t* acc_done = bars + 11;       // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, hkv = blockIdx.y;
+  const int G = p.hq / p.hk;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
+  const int n_kblk = (k_len + 127) / 128;
+  const int k_blk = static_cast<int>(blockIdx.x);
+  if (k_blk >= n_kblk) return;
+  const int k0 = k_blk * 128;
+  const int causal_shift = k_len - q_len;
+  const int n_qblk = (q_len + 127) / 128;
+  int i_start = 0;
+  if (p.causal) {
+    const int first_q = k0 - causal_shift;          // first query position that sees key k0
+    i_start = first_q > 0 ? first_q / 128 : 0;
+  }
+  const int n_i = n_qblk > i_start ? n_qblk - i_start : 0;
+  const int n_it = n_i * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1); mbar_init(&do_full[s], 1);
+      mbar_init(&q_empty[s], 1); mbar_init(&do_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(acc_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one() && n_it > 0) {
+      mbar_expect_tx(kv_full, 2 * S::kTile);
+#pragma unroll
+      for (int c = 0; c < kDBoxes; ++c) {
+        tma_load_3d(sK + c * kBoxBytes, &p.tma_k, kv_full, c * 64, hkv, k_begin + k0);
+        tma_load_3d(sV + c * kBoxBytes, &p.tma_v, kv_full, c * 64, hkv, k_begin + k0);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int g = it / n_i, i = i_start + it % n_i;
+        const int h = hkv * G + g;
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(&q_empty[s], ph ^ 1u, p.status);
+        if (!ok) break;
+        mbar_expect_tx(&q_full[s], S::kTile);
+#pragma unroll
+        for (int c = 0; c < kDBoxes; ++c)
+          tma_load_3d(sQ + s * S::kTile + c * kBoxBytes, &p.tma_q, &q_full[s], c * 64, h, q_begin + i * 128);
+        ok = mbar_wait(&do_empty[s], ph ^ 1u, p.status);
+        if (!ok) break;
+        mbar_expect_tx(&do_full[s], S::kTile);
+#pragma unroll
+        for (int c = 0; c < kDBoxes; ++c)
+          tma_load_3d(sDO + s * S::kTile + c * kBoxBytes, &p.tma_do, &do_full[s], c * 64, h, q_begin + i * 128);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && n_it > 0) {
+      bool ok = mbar_wait(kv_full, 0, p.status);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(&q_full[s], ph, p.status);
+        if (!ok) break;
+        ok = mbar_wait(&do_full[s], ph, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t aQ = smem_u32(sQ + s * S::kTile), aDO = smem_u32(sDO + s * S::kTile);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          tc_mma_f16_ss(tmem_base + kColST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
+                        kIdescNT, kk != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          tc_mma_f16_ss(tmem_base + kColDPT, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + off, 16, 1024),
+                        kIdescNT, kk != 0 ? 1u : 0u);
+        }
+        tc_commit(sdp_full);
+        ok = mbar_wait(pds_full, it & 1u, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          tc_mma_f16_ts(tmem_base + kColDV, tmem_base + kColST + kk * 8,
+                        make_smem_desc(aDO + kk * 2048, kBoxBytes, 1024), kIdescAcc, (it | kk) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          tc_mma_f16_ts(tmem_base + kColDK, tmem_base + kColDPT + kk * 8,
+                        make_smem_desc(aQ + kk * 2048, kBoxBytes, 1024), kIdescAcc, (it | kk) != 0 ? 1u : 0u);
+        }
+        tc_commit(&q_empty[s]);
+        tc_commit(&do_empty[s]);
+        tc_commit(acc_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                 // key row of the tile
+    const int tix = threadIdx.x - 64;                    // 0..127 among the softmax threads
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const int key = k0 + row;
+    const bool key_valid = key < k_len;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int g = it / n_i, i = i_start + it % n_i;
+      const int h = hkv * G + g;
+      const int qb = i * 128;
+      float* lse_b = s_lse + (it & 1) * 128;
+      float* del_b = s_delta + (it & 1) * 128;
+      {
+        const int qpos = qb + tix;
+        const bool v = qpos < q_len;
+        const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
+        lse_b[tix] = v ? p.lse[idx] * kLog2e : INFINITY;     // +inf -> probability 0 for rows past the end
+        del_b[tix] = v ? p.delta[idx] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = mbar_wait(sdp_full, it & 1u, p.status);
+      {
+        uint32_t all_ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred pin, pout;\n"
+            "setp.ne.u32 pin, %1, 0;\n"
+            "bar.red.and.pred pout, 1, 128, pin;\n"
+            "selp.u32 %0, 1, 0, pout;\n"
+            "}\n"
+            : "=r"(all_ok)
+            : "r"(static_cast<uint32_t>(ok))
+            : "memory");
+        ok = all_ok != 0u;
+      }
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tST = tmem_base + lane_off + kColST, tDPT = tmem_base + lane_off + kColDPT;
+      // a query column c is visible to this key iff key <= (qb + c) + shift
+      const int first_vis_c = p.causal ? (key - causal_shift - qb) : 0;
+      uint32_t pp[64], ds[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tST + c * 32, sv);
+        tmem_ld32(tDPT + c * 32, dv);
+        tc_wait_ld();
+#pragma unroll
+        for (int i2 = 0; i2 < 16; ++i2) {
+          float pr[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c * 32 + 2 * i2 + u;
+            const bool vis = key_valid && col >= first_vis_c;
+            const float prob = vis ? exp2f(__uint_as_float(sv[2 * i2 + u]) * p.scale_log2 - lse_b[col]) : 0.f;
+            pr[u] = prob;
+            dsv[u] = prob * (__uint_as_float(dv[2 * i2 + u]) - del_b[col]);
+          }
+          pp[c * 16 + i2] = pack_bf16(pr[0], pr[1]);
+          ds[c * 16 + i2] = pack_bf16(dsv[0], dsv[1]);
+        }
+      }
+      {
+        uint32_t(&a0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pp[0]);
+        uint32_t(&a1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pp[32]);
+        uint32_t(&b0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ds[0]);
+        uint32_t(&b1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ds[32]);
+        tmem_st32(tST, a0);
+        tmem_st32(tST + 32, a1);
+        tmem_st32(tDPT, b0);
+        tmem_st32(tDPT + 32, b1);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(pds_full);
+    }
+    if (ok && n_it > 0) {
+      ok = mbar_wait(acc_done, (n_it - 1) & 1u, p.status);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const int64_t tok = k_begin + key;
+      __nv_bfloat16* dkrow = p.dk + tok * p.dk_stride + static_cast<int64_t>(hkv) * D;
+      __nv_bfloat16* dvrow = p.dv + tok * p.dv_stride + static_cast<int64_t>(hkv) * D;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t col = which == 0 ? kColDV : kColDK;
+        const float sc = which == 0 ? 1.f : p.scale;
+        __nv_bfloat16* orow = which == 0 ? dvrow : dkrow;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ov[32];
+          if (n_it > 0) {
+            tmem_ld32(tmem_base + lane_off + col + c * 32, ov);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int i2 = 0; i2 < 32; ++i2) ov[i2] = 0u;
+          }
+          if (key_valid) {
+#pragma unroll
+            for (int i2 = 0; i2 < 4; ++i2) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(ov[8 * i2 + 0]) * sc, __uint_as_float(ov[8 * i2 + 1]) * sc);
+              v.y = pack_bf16(__uint_as_float(ov[8 * i2 + 2]) * sc, __uint_as_float(ov[8 * i2 + 3]) * sc);
+              v.z = pack_bf16(__uint_as_float(ov[8 * i2 + 4]) * sc, __uint_as_float(ov[8 * i2 + 5]) * sc);
+              v.w = pack_bf16(__uint_as_float(ov[8 * i2 + 6]) * sc, __uint_as_float(ov[8 * i2 + 7]) * sc);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i2 * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+// delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]   (one warp per (token, head))
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int64_t total_q, int hq, int D, int64_t o_stride,
+                                  int64_t do_stride) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= total_q * hq) return;
+  const int64_t t = w / hq;
+  const int h = static_cast<int>(w % hq);
+  const __nv_bfloat16* orow = o + t * o_stride + static_cast<int64_t>(h) * D;
+  const __nv_bfloat16* drow = dout + t * do_stride + static_cast<int64_t>(h) * D;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + d));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + d));
+    s += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+  if (lane == 0) delta[static_cast<int64_t>(h) * total_q + t] = s;
+}
+
+}  // namespace yv

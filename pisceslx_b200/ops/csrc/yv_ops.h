@@ -96,15 +96,16 @@ int launch_gate_bias_update(float* bias, const int* counts, int E, float rate, f
 // Attention (attention.cu)
 // ------------------------------------------------------------------------------------------------
 struct AttnArgs {
-  const void* q = nullptr;     // bf16 [T, hq, d]   (row stride q_stride elements)
-  const void* k = nullptr;     // bf16 [T, hk, d]
-  const void* v = nullptr;     // bf16 [T, hk, d]
-  void* o = nullptr;           // bf16 [T, hq, d]
-  float* lse = nullptr;        // fp32 [hq, T]
-  const int* cu_seqlens = nullptr;  // int32 [B+1] token offsets of the packed sequences
+  const void* q = nullptr;     // bf16 [Tq, hq, d]   (row stride q_stride elements)
+  const void* k = nullptr;     // bf16 [Tk, hk, d]
+  const void* v = nullptr;     // bf16 [Tk, hk, d]
+  void* o = nullptr;           // bf16 [Tq, hq, d]
+  float* lse = nullptr;        // fp32 [hq, Tq]  natural-log LSE of the scaled scores
+  const int* cu_q = nullptr;   // int32 [B+1] token offsets of the packed query sequences
+  const int* cu_k = nullptr;   // int32 [B+1] token offsets of the packed key sequences
   int batch = 0;
-  int max_seqlen = 0;
-  int64_t total_tokens = 0;
+  int max_q = 0, max_k = 0;    // longest sequence (sizes the grid)
+  int64_t total_q = 0, total_k = 0;
   int hq = 0, hk = 0, d = 0;
   int64_t q_stride = 0, k_stride = 0, v_stride = 0, o_stride = 0;
   int causal = 1;
@@ -113,13 +114,12 @@ struct AttnArgs {
 };
 int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream);
 struct AttnBwdArgs {
-  AttnArgs f;
-  const void* dout = nullptr;  // bf16 [T, hq, d]
-  void* dq = nullptr;          // bf16 [T, hq, d]
-  void* dk = nullptr;          // bf16 [T, hk, d]
-  void* dv = nullptr;          // bf16 [T, hk, d]
-  float* delta = nullptr;      // fp32 [hq, T] scratch
-  float* dq_acc = nullptr;     // fp32 [T, hq, d] scratch (zeroed by the launcher)
+  AttnArgs f;                  // forward tensors (o and lse are inputs here)
+  const void* dout = nullptr;  // bf16 [Tq, hq, d]
+  void* dq = nullptr;          // bf16 [Tq, hq, d]
+  void* dk = nullptr;          // bf16 [Tk, hk, d]
+  void* dv = nullptr;          // bf16 [Tk, hk, d]
+  float* delta = nullptr;      // fp32 [hq, Tq] scratch
   int64_t do_stride = 0, dq_stride = 0, dk_stride = 0, dv_stride = 0;
 };
 int launch_attn_bwd(const AttnBwdArgs& a, cudaStream_t stream);
@@ -131,15 +131,17 @@ struct PagedDecodeArgs {
   const int* block_table = nullptr;  // int32 [B, max_blocks_per_seq]
   const int* seq_lens = nullptr;     // int32 [B]
   void* o = nullptr;               // bf16 [B, hq, d]
-  float* partial_o = nullptr;      // fp32 [B, hq, splits, d]
-  float* partial_ml = nullptr;     // fp32 [B, hq, splits, 2]
+  float* partial_o = nullptr;      // fp32 [B, hq, splits, d]   scratch
+  float* partial_ml = nullptr;     // fp32 [B, hq, splits, 2]   scratch
   int batch = 0, hq = 0, hk = 0, d = 0, block = 64, max_blocks_per_seq = 0, splits = 1, num_blocks = 0;
   float scale = 1.f;
   uint32_t* status = nullptr;
 };
 int launch_paged_decode(const PagedDecodeArgs& a, cudaStream_t stream);
+// k, v: [T, hk*d] rows with the given strides; caches: [num_slots, hk*d]; slot_map int32 [T] (-1 = skip)
 int launch_kv_cache_write(const void* k, const void* v, void* k_cache, void* v_cache, const int* slot_map,
-                          int64_t tokens, int hk, int d, int64_t num_slots, uint32_t* status, cudaStream_t stream);
+                          int64_t tokens, int row_elems, int64_t k_stride, int64_t v_stride, int64_t num_slots,
+                          uint32_t* status, cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // Loss / optimizers / misc (loss_optim.cu)
