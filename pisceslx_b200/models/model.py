@@ -1,0 +1,309 @@
+"""``YvModel`` (trunk) and ``YvModelForCausalLM`` (trunk + LM head + losses).
+
+Mirrors the reference's forward contract (model/core/model.py:1979-2615): embedding -> optional
+multimodal tokens prepended -> per layer FiLM parameters + block -> final RMSNorm -> LM head; the LM loss
+is the shifted cross-entropy with ``ignore_index=-100`` (:2504-2509), right-aligned to the label length
+when modal tokens are prepended (:2497-2498), plus the multi-token-prediction loss (:2519-2538) and the
+MoE aux loss when ``moe_aux_loss_free`` is off (:2575-2578).  Padded positions have their embeddings
+zeroed (:2107-2109).  The output is a dict with attribute access (``YvModelOutput``, :487).
+
+Internally tokens are packed ``[T, H]``; the LM head and the loss are fused (``ops.loss``) so the logits of
+the whole batch never exist during training.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from ..config import YvConfig
+from ..ops import functional as F_
+from ..ops.loss import linear_cross_entropy
+from .attention import AttnContext
+from .blocks import YvTransformerBlock
+from .norms import YvRMSNorm, YvRotaryEmbedding
+
+
+class YvModelOutput(dict):
+    """dict with attribute access (``out.loss`` == ``out['loss']``)."""
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError as e:
+            raise AttributeError(k) from e
+
+    def __setattr__(self, k, v):
+        self[k] = v
+
+
+class YvModel(nn.Module):
+    def __init__(self, cfg: YvConfig, parallel=None):
+        super().__init__()
+        self.cfg, self.parallel = cfg, parallel
+        pp_size = parallel.pp_size if parallel is not None else 1
+        pp_rank = parallel.pp_rank if parallel is not None else 0
+        per = math.ceil(cfg.n_layer / pp_size)
+        self.layer_lo, self.layer_hi = pp_rank * per, min(cfg.n_layer, (pp_rank + 1) * per)
+        self.is_first_stage, self.is_last_stage = pp_rank == 0, pp_rank == pp_size - 1
+        if self.is_first_stage:
+            self.embed = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+            nn.init.normal_(self.embed.weight, std=cfg.initializer_range)
+        self.layers = nn.ModuleList([YvTransformerBlock(cfg, i, parallel) for i in range(self.layer_lo, self.layer_hi)])
+        if self.is_last_stage:
+            self.norm = YvRMSNorm(cfg.hidden_size, cfg.layer_norm_eps)
+        rot = cfg.partial_rope_dim if cfg.use_partial_rope else cfg.head_dim
+        scaling = "yarn" if cfg.use_dynamic_yarn else ("linear" if cfg.linear_rope_scale != 1.0 else "none")
+        factor = cfg.rope_scaling_factor if cfg.use_dynamic_yarn else cfg.linear_rope_scale
+        self.rotary = YvRotaryEmbedding(rot, min(cfg.max_position_embeddings, 8192), cfg.rope_theta, scaling, factor,
+                                        cfg.max_position_embeddings) if cfg.use_rotary_pos_emb else None
+        # optional components, attached by their builders (lazy like the reference, model.py:1276-1516)
+        self.subconscious: Optional[nn.Module] = None      # YvSubconsciousSystem / YvPQKnowledgeField
+        self.vision_encoder: Optional[nn.Module] = None
+        self.video_encoder: Optional[nn.Module] = None
+        self.audio_encoder: Optional[nn.Module] = None
+        self.modal_fusion: Optional[nn.Module] = None
+        self.materialized_components: List[str] = []
+
+    # ------------------------------------------------------------------------------------------------
+    def attach(self, name: str, module: nn.Module) -> None:
+        setattr(self, name, module)
+        if name not in self.materialized_components:
+            self.materialized_components.append(name)
+
+    def build_context(self, batch: int, seq: int, device: torch.device, lengths: Optional[torch.Tensor] = None,
+                      causal: bool = True) -> AttnContext:
+        """Context for ``batch`` sequences of equal length ``seq`` (or the given per-sequence lengths)."""
+        if lengths is None:
+            cu = torch.arange(0, (batch + 1) * seq, seq, dtype=torch.int32, device=device)
+            pos = torch.arange(seq, dtype=torch.int32, device=device).repeat(batch)
+            max_len = seq
+        else:
+            cu = torch.zeros(batch + 1, dtype=torch.int32, device=device)
+            cu[1:] = torch.cumsum(lengths.int(), 0)
+            total = int(cu[-1].item())
+            seq_id = torch.repeat_interleave(torch.arange(batch, device=device), lengths.long())
+            pos = (torch.arange(total, device=device) - cu[:-1].long()[seq_id]).int()
+            max_len = int(lengths.max().item())
+        cos = sin = None
+        if self.rotary is not None:
+            cos, sin = self.rotary.tables(max_len, device)
+        return AttnContext(positions=pos, cu_seqlens=cu, max_len=max_len, cos=cos, sin=sin, causal=causal)
+
+    def embed_tokens(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        h = self.embed(input_ids)
+        if attention_mask is not None:
+            h = h * attention_mask.unsqueeze(-1).to(h.dtype)
+        return h
+
+    def run_layers(self, h: torch.Tensor, ctx: AttnContext, batch: int,
+                   film_source: Optional[Any] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """h [T, H] -> (final hidden [T, H] before the last norm is applied by the caller, aux loss)."""
+        delta: Optional[torch.Tensor] = None
+        aux_total = h.new_zeros((), dtype=torch.float32)
+        if film_source is not None:
+            film_source.begin(h, batch)
+        for blk in self.layers:
+            film = film_source.film_params(blk.layer_idx, h if delta is None else h + delta) \
+                if film_source is not None else None
+            h, delta, aux = blk(h, delta, ctx, film)
+            aux_total = aux_total + aux.float()
+        if film_source is not None:
+            film_source.end()
+        return (h, delta), aux_total
+
+    def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
+                inputs_embeds: Optional[torch.Tensor] = None, prefix_embeds: Optional[torch.Tensor] = None,
+                ctx: Optional[AttnContext] = None, hidden_in: Optional[torch.Tensor] = None) -> YvModelOutput:
+        """Returns ``hidden_states`` [B, S_total, H] (normalised on the last pipeline stage) and ``aux_loss``.
+
+        ``prefix_embeds`` [B, P, H] (modal fusion tokens) are concatenated in front of the text embeddings.
+        ``hidden_in`` feeds a non-first pipeline stage."""
+        if self.is_first_stage:
+            h = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids, attention_mask)
+            if prefix_embeds is not None:
+                h = torch.cat([prefix_embeds.to(h.dtype), h], dim=1)
+        else:
+            h = hidden_in
+        B, S, H = h.shape
+        if ctx is None:
+            ctx = self.build_context(B, S, h.device)
+        flat = h.reshape(B * S, H)
+        if self.parallel is not None and self.parallel.tp_size > 1 and self.cfg.sequence_parallel:
+            from ..parallel import tp
+            flat = tp.scatter_sequence(flat, self.parallel.tp_group)
+        (hf, delta), aux = self.run_layers(flat, ctx, B, self.subconscious)
+        if self.is_last_stage:
+            out = self.norm(hf) if delta is None else self.norm(delta, residual=hf)[0]
+        else:
+            out = hf if delta is None else hf + delta
+        if self.parallel is not None and self.parallel.tp_size > 1 and self.cfg.sequence_parallel:
+            from ..parallel import tp
+            out = tp.gather_sequence(out, self.parallel.tp_group)
+        return YvModelOutput(hidden_states=out.view(B, S, H), aux_loss=aux)
+
+
+class YvModelForCausalLM(nn.Module):
+    def __init__(self, cfg: YvConfig, parallel=None):
+        super().__init__()
+        self.cfg, self.parallel = cfg, parallel
+        self.model = YvModel(cfg, parallel)
+        self.tied = cfg.tie_word_embeddings and self.model.is_first_stage and self.model.is_last_stage
+        if self.model.is_last_stage and not self.tied:
+            self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
+            nn.init.normal_(self.lm_head, std=cfg.initializer_range)
+        self.num_mtp = cfg.num_mtp_heads
+        if self.num_mtp > 0 and not cfg.mtp_share_embeddings and self.model.is_last_stage:
+            self.mtp_heads = nn.ParameterList(
+                [nn.Parameter(torch.randn(cfg.vocab_size, cfg.hidden_size) * cfg.initializer_range)
+                 for _ in range(self.num_mtp)])
+
+    @property
+    def head_weight(self) -> torch.Tensor:
+        return self.model.embed.weight if self.tied else self.lm_head
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """hidden [..., H] -> fp32 logits [..., V] (inference / evaluation only)."""
+        return F_.linear(hidden, self.head_weight, out_fp32=True)
+
+    def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
+                labels: Optional[torch.Tensor] = None, prefix_embeds: Optional[torch.Tensor] = None,
+                inputs_embeds: Optional[torch.Tensor] = None, ctx: Optional[AttnContext] = None,
+                num_valid: Optional[int] = None, return_logits: Optional[bool] = None,
+                return_hidden: bool = False, hidden_in: Optional[torch.Tensor] = None, **modal: Any) -> YvModelOutput:
+        cfg = self.cfg
+        if prefix_embeds is None and modal and self.model.modal_fusion is not None:
+            prefix_embeds = self.model.modal_fusion.encode_modalities(self.model, **modal)
+        out = self.model(input_ids, attention_mask, inputs_embeds, prefix_embeds, ctx, hidden_in)
+        hidden, aux = out["hidden_states"], out["aux_loss"]
+        res = YvModelOutput(aux_loss=aux, loss=None, lm_loss=None, mtp_loss=None, logits=None)
+        if return_hidden:
+            res["hidden_states"] = hidden
+        if not self.model.is_last_stage:
+            res["hidden_states"] = hidden
+            return res
+        if return_logits is None:
+            return_logits = labels is None
+        if return_logits:
+            res["logits"] = self.logits(hidden)
+        if labels is not None:
+            B, S, H = hidden.shape
+            L = labels.shape[1]
+            h_txt = hidden[:, S - L:, :]                      # right-align to the labels (modal prefix skipped)
+            h_in = h_txt[:, :-1, :].reshape(-1, H)
+            tgt = labels[:, 1:].reshape(-1)
+            nv = None
+            if num_valid is not None:
+                nv = num_valid
+            lm_loss = linear_cross_entropy(h_in, self.head_weight, tgt, -100, nv)
+            loss = lm_loss
+            res["lm_loss"] = lm_loss
+            if self.num_mtp > 0:
+                mtp = hidden.new_zeros((), dtype=torch.float32)
+                for i in range(self.num_mtp):
+                    if L - 2 - i <= 0:
+                        break
+                    w = self.head_weight if cfg.mtp_share_embeddings else self.mtp_heads[i]
+                    hi = h_txt[:, : L - 2 - i, :].reshape(-1, H)
+                    ti = labels[:, 2 + i:].reshape(-1)
+                    mtp = mtp + linear_cross_entropy(hi, w, ti, -100, None)
+                mtp = mtp / self.num_mtp * cfg.mtp_loss_weight
+                res["mtp_loss"] = mtp
+                loss = loss + mtp
+            if not cfg.moe_aux_loss_free:
+                loss = loss + cfg.moe_aux_loss_weight * aux
+            res["loss"] = loss
+        return res
+
+    # ------------------------------------------------------------------------------------------------
+    # reference-layout state dict (consolidated checkpoint key names)
+    # ------------------------------------------------------------------------------------------------
+    def to_reference_state_dict(self) -> Dict[str, torch.Tensor]:
+        sd: Dict[str, torch.Tensor] = {}
+        m = self.model
+        if m.is_first_stage:
+            sd["embed.weight"] = m.embed.weight.detach().clone()
+        for blk in m.layers:
+            blk.export_state(f"layers.{blk.layer_idx}.", sd)
+        if m.is_last_stage:
+            sd["norm.weight"] = m.norm.weight.detach().clone()
+            sd["lm_head.weight"] = self.head_weight.detach().clone()
+            if self.num_mtp > 0 and not self.cfg.mtp_share_embeddings:
+                for i, w in enumerate(self.mtp_heads):
+                    sd[f"mtp_heads.{i}.weight"] = w.detach().clone()
+        for name in m.materialized_components:
+            mod = getattr(m, name, None)
+            if isinstance(mod, nn.Module):
+                for k, v in mod.state_dict().items():
+                    sd[f"{name}.{k}"] = v.detach().clone()
+        return sd
+
+    def load_reference_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> List[str]:
+        """Load a consolidated checkpoint; returns the list of keys that were not consumed."""
+        m = self.model
+        used = set()
+        with torch.no_grad():
+            if m.is_first_stage:
+                m.embed.weight.copy_(sd["embed.weight"])
+                used.add("embed.weight")
+            for blk in m.layers:
+                blk.import_state(f"layers.{blk.layer_idx}.", sd)
+            if m.is_last_stage:
+                m.norm.weight.copy_(sd["norm.weight"])
+                used.add("norm.weight")
+                if not self.tied and "lm_head.weight" in sd:
+                    self.lm_head.copy_(sd["lm_head.weight"])
+                used.add("lm_head.weight")
+            for name in m.materialized_components:
+                mod = getattr(m, name, None)
+                if isinstance(mod, nn.Module):
+                    sub = {k[len(name) + 1:]: v for k, v in sd.items() if k.startswith(name + ".")}
+                    if sub:
+                        mod.load_state_dict(sub, strict=strict)
+                        used.update(name + "." + k for k in sub)
+        prefixes = tuple(f"layers.{b.layer_idx}." for b in m.layers)
+        return [k for k in sd if k not in used and not k.startswith(prefixes)]
+
+    # ------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, **kw: Any):
+        from .generation import generate
+        return generate(self, input_ids, max_new_tokens=max_new_tokens, **kw)
+
+    def resize_token_embeddings(self, new_size: int) -> None:
+        old = self.model.embed.weight.data
+        new = torch.empty(new_size, old.shape[1], dtype=old.dtype, device=old.device).normal_(std=self.cfg.initializer_range)
+        n = min(new_size, old.shape[0])
+        new[:n] = old[:n]
+        self.model.embed.weight = nn.Parameter(new)
+        if not self.tied:
+            oldh = self.lm_head.data
+            newh = torch.empty(new_size, oldh.shape[1], dtype=oldh.dtype, device=oldh.device).normal_(
+                std=self.cfg.initializer_range)
+            newh[:n] = oldh[:n]
+            self.lm_head = nn.Parameter(newh)
+        self.cfg.vocab_size = new_size
+
+
+def build_model(cfg: YvConfig, device: Optional[torch.device | str] = None, dtype: Optional[torch.dtype] = None,
+                parallel=None, seed: int = 0) -> YvModelForCausalLM:
+    """Construct the model directly on ``device`` in ``dtype`` (no fp32 staging copy)."""
+    device = torch.device(device) if device is not None else torch.device("cpu")
+    dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+    prev = torch.get_default_dtype()
+    torch.manual_seed(seed)
+    if device.type == "cuda":
+        torch.cuda.manual_seed(seed)
+    try:
+        torch.set_default_dtype(dtype)
+        with torch.device(device):
+            model = YvModelForCausalLM(cfg, parallel)
+    finally:
+        torch.set_default_dtype(prev)
+    # routing state stays fp32 regardless of the parameter dtype
+    for mod in model.modules():
+        if hasattr(mod, "expert_bias"):
+            mod.expert_bias.data = mod.expert_bias.data.float()
+    return model

@@ -127,6 +127,31 @@ void gemm_grouped_k(const Tensor& a, const Tensor& b, Tensor c, const Tensor& se
   check_rc(yv::launch_gemm(g, cur_stream()), "gemm_grouped_k");
 }
 
+// Batched: a [G, M, K] (or [G, K, M] when a_mn), b [G, N, K] (or [G, K, N] when b_mn), c [G, M, N]; contiguous.
+void gemm_batched(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, bool accumulate, int64_t bn,
+                  const c10::optional<Tensor>& status) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_cuda(c, "c");
+  TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3 && a.is_contiguous() && b.is_contiguous() &&
+              c.is_contiguous(), "gemm_batched: contiguous 3-D operands expected");
+  TORCH_CHECK(a.size(0) == b.size(0) && a.size(0) == c.size(0), "gemm_batched: batch sizes differ");
+  const c10::cuda::CUDAGuard guard(a.device());
+  yv::GemmArgs g;
+  g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = c.data_ptr();
+  g.a_mn = a_mn; g.b_mn = b_mn;
+  g.mode = 3;
+  g.num_groups = static_cast<int>(a.size(0));
+  g.M = static_cast<int>(a_mn ? a.size(2) : a.size(1));
+  g.K = static_cast<int>(a_mn ? a.size(1) : a.size(2));
+  g.N = static_cast<int>(b_mn ? b.size(2) : b.size(1));
+  TORCH_CHECK((b_mn ? b.size(1) : b.size(2)) == g.K, "gemm_batched: K mismatch");
+  TORCH_CHECK(c.size(1) == g.M && c.size(2) == g.N, "gemm_batched: output shape mismatch");
+  g.out_fp32 = dt_code(c);
+  g.accumulate = accumulate ? 1 : 0;
+  g.bn = static_cast<int>(bn);
+  g.status = statusp(status);
+  check_rc(yv::launch_gemm(g, cur_stream()), "gemm_batched");
+}
+
 // ------------------------------------------------------------------------------------------------
 // elementwise
 // ------------------------------------------------------------------------------------------------

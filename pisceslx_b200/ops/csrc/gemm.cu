@@ -68,6 +68,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.b_group_stride = 0;
   p.c_group_stride = 0;
+  p.a_group_stride = 0;
 
   // extents of the stored operands
   uint64_t a_inner, a_outer, b_inner, b_outer, c_outer;
@@ -93,6 +94,16 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     b_inner = a.N;  b_outer = a.rows_total;
     p.c_group_stride = a.M;
     c_outer = groups * static_cast<uint64_t>(a.M);
+  } else if (a.mode == kBatched) {
+    // every operand stacks `num_groups` equal problems along its outer dimension
+    if (a.M % kBM != 0) return -18;                       // C / A row tiles must not cross batch entries
+    if ((a.a_mn || a.b_mn) && (a.K % kBK) != 0) return -19;
+    p.a_group_stride = a.a_mn ? a.K : a.M;
+    p.b_group_stride = a.b_mn ? a.K : a.N;
+    p.c_group_stride = a.M;
+    a_inner = a.a_mn ? a.M : a.K;  a_outer = groups * static_cast<uint64_t>(p.a_group_stride);
+    b_inner = a.b_mn ? a.N : a.K;  b_outer = groups * static_cast<uint64_t>(p.b_group_stride);
+    c_outer = groups * static_cast<uint64_t>(a.M);
   } else {
     return -17;
   }
@@ -113,7 +124,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
 
   const int64_t tiles_m = (p.M + kBM - 1) / kBM;
   const int64_t tiles_n = (a.N + bn - 1) / bn;
-  int64_t tiles = tiles_m * tiles_n * (a.mode == kGroupedK ? a.num_groups : 1);
+  int64_t tiles = tiles_m * tiles_n * ((a.mode == kGroupedK || a.mode == kBatched) ? a.num_groups : 1);
   const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
 

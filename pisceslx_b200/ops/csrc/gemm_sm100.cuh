@@ -13,13 +13,15 @@
 //                                 expert's segment is padded to a multiple of 128 rows
 //   kGroupedK  C[e][M,N]       = A[:, seg(e)] * B[seg(e), :]       the reduction runs over expert e's
 //                                 row segment (weight gradients of the grouped expert GEMMs)
+//   kBatched   C[g][M,N]       = A[g] * B[g]                        equal-shaped problems stacked along the
+//                                 outer dimension of every operand (Muon's Newton-Schulz iterations)
 // Operand layouts are template flags: K-major ("row-major [rows, K]") or MN-major ("row-major [K, rows]").
 #pragma once
 #include "sm100.cuh"
 
 namespace yv {
 
-enum GemmMode : int { kDense = 0, kGroupedM = 1, kGroupedK = 2 };
+enum GemmMode : int { kDense = 0, kGroupedM = 1, kGroupedK = 2, kBatched = 3 };
 
 struct GemmParams {
   CUtensorMap tma_a;
@@ -30,7 +32,8 @@ struct GemmParams {
   int accumulate;              // 1: C += result through TMA reduce-add
   int num_groups;              // experts (grouped modes)
   int b_group_stride;          // kGroupedM: outer-dim rows of B per expert
-  int c_group_stride;          // kGroupedK: rows of C per expert (= M)
+  int c_group_stride;          // kGroupedK / kBatched: rows of C per group
+  int a_group_stride;          // kBatched: outer-dim rows of A per batch entry
   const int* tile_expert;      // kGroupedM: expert id of every 128-row tile
   const int* num_m_tiles;      // kGroupedM: number of valid 128-row tiles (device scalar)
   const int* seg_offsets;      // kGroupedK: [E+1] row offsets of the expert segments (multiples of 128)
@@ -65,7 +68,7 @@ struct TileCoord {
 template <int BN, bool A_MN, bool B_MN>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int tiles_m, int tiles_n, TileCoord& t) {
   int m_blk, n_blk, group = 0;
-  if (p.mode == kGroupedK) {
+  if (p.mode == kGroupedK || p.mode == kBatched) {
     const int per_group = tiles_m * tiles_n;
     group = idx / per_group;
     if (group >= p.num_groups) return false;
@@ -83,8 +86,12 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
   }
   const int m0 = m_blk * kBM, n0 = n_blk * BN;
   int k_begin = 0, k_len = p.K;
-  int b_outer_off = 0, c_row_off = 0;
-  if (p.mode == kGroupedM) {
+  int a_outer_off = 0, b_outer_off = 0, c_row_off = 0;
+  if (p.mode == kBatched) {
+    a_outer_off = group * p.a_group_stride;
+    b_outer_off = group * p.b_group_stride;
+    c_row_off = group * p.c_group_stride;
+  } else if (p.mode == kGroupedM) {
     const int e = p.tile_expert[m_blk];
     b_outer_off = e * p.b_group_stride;
   } else if (p.mode == kGroupedK) {
@@ -93,7 +100,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
     c_row_off = group * p.c_group_stride;
   }
   t.k_iters = (k_len + kBK - 1) / kBK;
-  if (A_MN) { t.a_x = m0; t.a_y = k_begin; } else { t.a_x = k_begin; t.a_y = m0; }
+  if (A_MN) { t.a_x = m0; t.a_y = a_outer_off + k_begin; } else { t.a_x = k_begin; t.a_y = a_outer_off + m0; }
   if (B_MN) { t.b_x = n0; t.b_y = b_outer_off + k_begin; } else { t.b_x = k_begin; t.b_y = b_outer_off + n0; }
   t.c_x = n0;
   t.c_y = c_row_off + m0;
