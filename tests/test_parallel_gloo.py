@@ -1,0 +1,112 @@
+"""Multi-process CPU tests (Gloo, world_size 2): the parallel layouts must reproduce the single-process model.
+
+Each case spawns its ranks as child processes that train the tiny Yv text MoE (4 layers, hidden 256, 4q/2kv
+heads, 8 routed experts top-2 + 1 shared expert) for a few AdamW steps and write their losses; the parent
+compares them with a single-process run on the same global batch."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent("""
+    import json, os, sys
+    sys.path.insert(0, {root!r})
+    import torch
+    from pisceslx_b200 import YvConfig
+    from pisceslx_b200.models import build_model
+    from pisceslx_b200.parallel.state import init_parallel, destroy_parallel
+    from pisceslx_b200.engine.trainer import YvTrainer, YvTrainerConfig
+    tp, ep, steps, out = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
+    torch.manual_seed(0)
+    par = init_parallel(tp=tp, ep=ep, backend="gloo", device=torch.device("cpu"), timeout_s=120)
+    cfg = YvConfig.tiny_text_moe(vocab_size=1024)
+    cfg.n_layer = 2
+    cfg.use_gradient_checkpointing = False
+    cfg.extra["moe_deterministic"] = True
+    model = build_model(cfg, "cpu", torch.float32, parallel=par if par.world_size > 1 else None, seed=7)
+    full = torch.load(sys.argv[5])
+    from pisceslx_b200.engine.checkpoint import load_full_into
+    load_full_into(model, full)
+    tr = YvTrainer(model, YvTrainerConfig(micro_batch_size=2, optimizer="adamw", lr=1e-3, max_steps=100,
+                                          clip_grad_norm=0.0), parallel=par if par.world_size > 1 else None)
+    g = torch.Generator().manual_seed(0)
+    data = torch.randint(0, 1024, (steps, 4, 32), generator=g)
+    losses = []
+    for s in range(steps):
+        b = data[s]
+        if par.dp_size > 1:
+            per = b.shape[0] // par.dp_size
+            b = b[par.dp_rank * per:(par.dp_rank + 1) * per]
+        losses.append(tr.train_step({{"input_ids": b, "labels": b}})["loss"])
+    if par.world_size > 1:
+        t = torch.tensor(losses, dtype=torch.float64)
+        torch.distributed.all_reduce(t, group=par.dp_group) if par.dp_size > 1 else None
+        losses = (t / par.dp_size).tolist()
+    if par.rank == 0:
+        json.dump(losses, open(out, "w"))
+    destroy_parallel()
+""")
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(tmp_path, world, tp, ep, steps, init_path, tag):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(root=ROOT))
+    out = tmp_path / f"loss_{tag}.json"
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, str(script), str(tp), str(ep), str(steps), str(out),
+                                       str(init_path)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        logs.append(o.decode()[-3000:])
+    assert all(p.returncode == 0 for p in procs), "\n".join(logs)
+    return json.load(open(out))
+
+
+@pytest.fixture(scope="module")
+def init_weights(tmp_path_factory):
+    sys.path.insert(0, ROOT)
+    from pisceslx_b200 import YvConfig
+    from pisceslx_b200.models import build_model
+    cfg = YvConfig.tiny_text_moe(vocab_size=1024)
+    cfg.n_layer = 2
+    m = build_model(cfg, "cpu", torch.float32, seed=7)
+    p = tmp_path_factory.mktemp("init") / "full.pt"
+    torch.save(m.to_reference_state_dict(), p)
+    return p
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("tp,ep", [(1, 2), (2, 1)])
+def test_parallel_matches_single_process(tmp_path, init_weights, tp, ep):
+    steps = 4
+    single = _run(tmp_path, 1, 1, 1, steps, init_weights, "single")
+    multi = _run(tmp_path, 2, tp, ep, steps, init_weights, f"tp{tp}ep{ep}")
+    assert len(single) == len(multi) == steps
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
+    assert single[-1] < single[0]
