@@ -63,6 +63,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   p.accumulate = a.accumulate;
   p.num_groups = a.num_groups;
   p.tile_expert = a.tile_expert;
+  p.tile_rows = a.tile_rows;
   p.num_m_tiles = a.num_m_tiles;
   p.seg_offsets = a.seg_offsets;
   p.status = a.status;

@@ -35,6 +35,7 @@ struct GemmParams {
   int c_group_stride;          // kGroupedK / kBatched: rows of C per group
   int a_group_stride;          // kBatched: outer-dim rows of A per batch entry
   const int* tile_expert;      // kGroupedM: expert id of every 128-row tile
+  const int* tile_rows;        // kGroupedM (optional): index of the 128-row tile in A / C for every listed tile
   const int* num_m_tiles;      // kGroupedM: number of valid 128-row tiles (device scalar)
   const int* seg_offsets;      // kGroupedK: [E+1] row offsets of the expert segments (multiples of 128)
   uint32_t* status;            // device status word (0 = ok)
@@ -84,7 +85,9 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
     n_blk = r / band_m;
     m_blk = band * kGroupBand + (r - n_blk * band_m);
   }
-  const int m0 = m_blk * kBM, n0 = n_blk * BN;
+  // grouped-M problems may list their 128-row tiles explicitly (receive regions of several sources)
+  const int row_tile = (p.mode == kGroupedM && p.tile_rows != nullptr) ? p.tile_rows[m_blk] : m_blk;
+  const int m0 = row_tile * kBM, n0 = n_blk * BN;
   int k_begin = 0, k_len = p.K;
   int a_outer_off = 0, b_outer_off = 0, c_row_off = 0;
   if (p.mode == kBatched) {

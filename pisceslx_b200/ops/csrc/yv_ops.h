@@ -24,6 +24,7 @@ struct GemmArgs {
   int num_groups = 1;
   int64_t rows_total = 0;      // grouped modes: rows of the expert-sorted, padded row dimension
   const int* tile_expert = nullptr;
+  const int* tile_rows = nullptr;   // grouped-M only: explicit row-tile index per listed tile (optional)
   const int* num_m_tiles = nullptr;
   const int* seg_offsets = nullptr;
   uint32_t* status = nullptr;
