@@ -1,0 +1,3 @@
+"""Multimodal encoders and fusion."""
+from .fusion import YvAudioEncoder, YvCrossModalAttention, YvDynamicModalFusion, attach_multimodal
+from .vision import YvPatchEmbed, YvVideoEncoder, YvVisionEncoder, YvViTBlock

@@ -100,7 +100,7 @@ class _AllGatherLinear(torch.autograd.Function):
     def forward(ctx, x, w, group, fused):
         ctx.group, ctx.fused = group, fused
         if fused and x.is_cuda:
-            from . import fused as fz
+            from . import fused_tp as fz
             xg, y = fz.allgather_gemm(x, w, group)
         else:
             xg = all_gather_rows(x, group)
@@ -115,7 +115,7 @@ class _AllGatherLinear(torch.autograd.Function):
         dy = dy.contiguous()
         if x.is_cuda:
             if ctx.fused:
-                from . import fused as fz
+                from . import fused_tp as fz
                 dx = fz.gemm_reduce_scatter(dy, w, group, b_mn=True)          # (dy @ w) reduce-scattered
             else:
                 dx = reduce_scatter_rows(F_.gemm(dy, w, b_mn=True), group)
@@ -137,7 +137,7 @@ class _LinearReduceScatter(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         if x.is_cuda:
             if fused:
-                from . import fused as fz
+                from . import fused_tp as fz
                 return fz.gemm_reduce_scatter(x.contiguous(), w, group, b_mn=False)
             return reduce_scatter_rows(F_.gemm(x.contiguous(), w), group)
         return reduce_scatter_rows(x @ w.to(x.dtype).t(), group)
@@ -147,7 +147,7 @@ class _LinearReduceScatter(torch.autograd.Function):
         x, w = ctx.saved_tensors
         if x.is_cuda:
             if ctx.fused:
-                from . import fused as fz
+                from . import fused_tp as fz
                 dyg, dx = fz.allgather_gemm(dy.contiguous(), w, ctx.group, b_mn=True)   # all_gather(dy) @ w
             else:
                 dyg = all_gather_rows(dy.contiguous(), ctx.group)

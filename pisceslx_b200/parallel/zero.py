@@ -36,7 +36,8 @@ def _is_sequence_parallel_param(name: str) -> bool:
 class _FlatGroup:
     """One replicated parameter set + its process group."""
 
-    def __init__(self, named: List[Tuple[str, torch.nn.Parameter]], group: Any, world: int, rank: int):
+    def __init__(self, named: List[Tuple[str, torch.nn.Parameter]], group: Any, world: int, rank: int,
+                 fused: bool = False, tag: str = "g"):
         self.group, self.world, self.rank = group, world, rank
         self.named = named
         # greedy balance: biggest tensors first, each to the least loaded owner
@@ -55,8 +56,15 @@ class _FlatGroup:
             self.offsets[n] = cur[o]
             cur[o] += (p.numel() + 127) // 128 * 128
         dev, dt = named[0][1].device, named[0][1].dtype
-        self.flat_param = torch.zeros(world * self.shard, dtype=dt, device=dev)
-        self.flat_grad = torch.zeros(world * self.shard, dtype=dt, device=dev)
+        self.symm_param = self.symm_grad = None
+        if fused and dev.type == "cuda":
+            from . import fused as fz
+            (self.symm_param, self.flat_param), (self.symm_grad, self.flat_grad) = fz.symmetric_flat_buffers(
+                group, tag, world * self.shard, dt)
+            self.flat_grad.zero_()
+        else:
+            self.flat_param = torch.zeros(world * self.shard, dtype=dt, device=dev)
+            self.flat_grad = torch.zeros(world * self.shard, dtype=dt, device=dev)
         for n, p in named:
             off = self.offsets[n]
             view = self.flat_param[off:off + p.numel()].view(p.shape)
@@ -100,14 +108,19 @@ class YvGradientSynchronizer:
         self.groups: List[_FlatGroup] = []
         self.dp_size = parallel.dp_size
 
-        def add(named, group):
-            if named and group is not None and dist.get_world_size(group) > 1:
-                self.groups.append(_FlatGroup(named, group, dist.get_world_size(group), dist.get_rank(group)))
-
-        add(dense, parallel.dp_group)
-        add(expert, parallel.expert_grad_group)
-        add(seqpar, parallel.stage_group)
+        if fused is None:
+            from . import fused as fz
+            fused = fz.enabled() and next(model.parameters()).is_cuda
         self.fused = fused
+
+        def add(named, group, tag):
+            if named and group is not None and dist.get_world_size(group) > 1:
+                self.groups.append(_FlatGroup(named, group, dist.get_world_size(group), dist.get_rank(group),
+                                              fused=bool(fused), tag=tag))
+
+        add(dense, parallel.dp_group, "dense")
+        add(expert, parallel.expert_grad_group, "expert")
+        add(seqpar, parallel.stage_group, "seqpar")
         self._micro, self._total = 0, 1
         self._managed: Dict[int, Tuple[_FlatGroup, str]] = {}
         for g in self.groups:
@@ -143,13 +156,10 @@ class YvGradientSynchronizer:
         backward and before ``optimizer.step()``."""
         for g in self.groups:
             scale = 1.0 / (self.dp_size * self._total)
-            use_fused = self.fused
-            if use_fused is None:
+            handled: List[str] = []
+            if self.fused and g.symm_grad is not None:
                 from . import fused as fz
-                use_fused = fz.enabled() and g.flat_grad.is_cuda
-            if use_fused:
-                from . import fused as fz
-                fz.reduce_scatter_grads(g, scale)
+                handled = fz.reduce_scatter_grads(g, scale, self.optimizer)
             else:
                 shard = g.my_grad_shard()
                 if g.flat_grad.is_cuda:
@@ -159,6 +169,8 @@ class YvGradientSynchronizer:
                 shard.mul_(scale)
             # hand the reduced gradients of the owned tensors to the optimizer
             for n, p in g.owned():
+                if n in handled:
+                    continue
                 grad = g.grad_views[n]
                 if hasattr(self.optimizer, "consume_external_grad"):
                     self.optimizer.consume_external_grad(p, grad)
@@ -170,7 +182,10 @@ class YvGradientSynchronizer:
     def after_step(self) -> None:
         """All-gather the updated parameter shards (call after ``optimizer.step()``)."""
         for g in self.groups:
-            if g.flat_param.is_cuda:
+            if self.fused and g.symm_param is not None:
+                from . import fused as fz
+                fz.all_gather_params(g)
+            elif g.flat_param.is_cuda:
                 dist.all_gather_into_tensor(g.flat_param, g.my_param_shard().clone(), group=g.group)
             else:
                 parts = [torch.empty_like(g.my_param_shard()) for _ in range(g.world)]

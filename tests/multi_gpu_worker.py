@@ -1,0 +1,84 @@
+"""Worker of the multi-GPU tests (launched by torchrun, one rank per GPU).
+
+Trains a small Yv text MoE (kernel-friendly sizes) for a few steps in the requested layout, once with the fused
+peer-memory collectives and once with the NCCL implementations, and writes the losses of every mode to a JSON
+file; the parent test compares them with each other and with a single-GPU run of the same global batch."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+from pisceslx_b200 import YvConfig
+from pisceslx_b200.engine.checkpoint import load_full_into
+from pisceslx_b200.engine.trainer import YvTrainer, YvTrainerConfig
+from pisceslx_b200.models import build_model
+from pisceslx_b200.ops import check_status
+from pisceslx_b200.parallel import fused as fz
+from pisceslx_b200.parallel.state import init_parallel
+
+
+def small_cfg() -> YvConfig:
+    cfg = YvConfig(vocab_size=4096, hidden_size=512, n_layer=2, n_head=8, n_kv_head=4, head_dim=64, rope_theta=1e4,
+                   moe_num_experts=8, moe_top_k=2, moe_shared_experts=1, moe_expert_intermediate_size=256,
+                   moe_shared_intermediate_size=512, intermediate_size=512, tie_word_embeddings=False,
+                   max_position_embeddings=4096)
+    cfg.use_gradient_checkpointing = True
+    return cfg
+
+
+def run(par, full_sd, fused: bool, steps: int, streaming: bool):
+    fz.set_enabled(fused)
+    cfg = small_cfg()
+    cfg.fused_comm = fused
+    model = build_model(cfg, par.device, torch.bfloat16, parallel=par if par.world_size > 1 else None, seed=3)
+    load_full_into(model, full_sd)
+    tr = YvTrainer(model, YvTrainerConfig(micro_batch_size=2, optimizer="muon", lr=2e-3, max_steps=100, clip_grad_norm=0.0,
+                                          streaming_optimizer=streaming, track_grad_norm=False),
+                   parallel=par if par.world_size > 1 else None)
+    g = torch.Generator().manual_seed(0)
+    data = torch.randint(0, cfg.vocab_size, (steps, 4, 256), generator=g)
+    losses = []
+    for s in range(steps):
+        b = data[s]
+        if par.dp_size > 1:
+            per = b.shape[0] // par.dp_size
+            b = b[par.dp_rank * per:(par.dp_rank + 1) * per]
+        b = b.to(par.device)
+        losses.append(tr.train_step({"input_ids": b, "labels": b})["loss"])
+    torch.cuda.synchronize()
+    check_status()
+    t = torch.tensor(losses, dtype=torch.float64, device=par.device)
+    if par.world_size > 1 and par.dp_size > 1:
+        dist.all_reduce(t, group=par.dp_group)
+        t /= par.dp_size
+    return t.tolist()
+
+
+def main() -> None:
+    tp, ep, out_path = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    par = init_parallel(tp=tp, ep=ep, timeout_s=120)
+    torch.manual_seed(0)
+    ref_model = build_model(small_cfg(), "cpu", torch.float32, seed=3)
+    full_sd = ref_model.to_reference_state_dict()
+    res = {}
+    if par.world_size == 1:
+        for streaming in (False, True):
+            res["stream" if streaming else "plain"] = run(par, full_sd, False, 3, streaming)
+        json.dump(res, open(out_path, "w"))
+        return
+    for streaming in (False, True):
+        for fused in (False, True):
+            key = f"{'fused' if fused else 'nccl'}_{'stream' if streaming else 'plain'}"
+            res[key] = run(par, full_sd, fused, 3, streaming)
+    if par.rank == 0:
+        json.dump(res, open(out_path, "w"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,64 @@
+"""Multi-GPU tests (need >= 2 B200s on one box): fused peer-memory collectives against the NCCL implementations
+and against a single-GPU run, for expert parallel and tensor parallel layouts."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _launch(world: int, tp: int, ep: int, out: str) -> dict:
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(tp), str(ep), out]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
+    return json.load(open(out))
+
+
+def _single(out: str) -> dict:
+    cmd = [sys.executable, os.path.join(ROOT, "tests", "multi_gpu_worker.py"), "1", "1", out]
+    env = dict(os.environ, PYTHONPATH=ROOT, WORLD_SIZE="1", RANK="0", LOCAL_RANK="0")
+    env.pop("MASTER_ADDR", None)
+    # world size 1 initialises no process group: the worker then runs the single-GPU modes only
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
+    return json.load(open(out))
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    return _single(str(tmp_path_factory.mktemp("single") / "single.json"))
+
+
+@pytest.mark.parametrize("tp,ep", [(1, 2), (2, 1)])
+def test_fused_matches_nccl_and_single(tmp_path, single, tp, ep):
+    res = _launch(2, tp, ep, str(tmp_path / "multi.json"))
+    for mode in ("plain", "stream"):
+        ref = single[mode]
+        for impl in ("nccl", "fused"):
+            got = res[f"{impl}_{mode}"]
+            assert len(got) == len(ref)
+            for a, b in zip(got, ref):
+                assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (impl, mode, got, ref)
+        # the two implementations move the same data: they agree more tightly with each other
+        for a, b in zip(res[f"nccl_{mode}"], res[f"fused_{mode}"]):
+            assert abs(a - b) < 1.5e-2 * max(1.0, abs(b))
+        assert ref[-1] < ref[0]
