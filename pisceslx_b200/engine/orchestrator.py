@@ -1,0 +1,168 @@
+"""Train / infer orchestrators behind ``manage.py``.
+
+``PiscesLxTrainOrchestrator.run(args)`` follows the reference flow (tools/train/orchestrator.py:881-1811): model
+YAML -> nested ``training_config`` / ``distributed`` sections -> stage YAML (``configs/train/<stage>.yaml``) -> CLI
+overrides (later wins; unknown keys are ignored), process group from the torchrun environment, dataset + collator,
+trainer, optional resume, run-store reporting, checkpoints ``checkpoint_step_<N>.pt`` / ``final_model.pt``.
+``PiscesLxInferOrchestrator.run(args)`` is the one-shot generation entry (tools/infer/orchestrator.py:85-244).
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from pathlib import Path
+from typing import Any, Dict, Optional
+
+import torch
+import yaml
+
+from ..config import YvConfig
+from .loader import REPO_ROOT, attach_optional_components, load_model_for_inference, resolve_model_config
+from .runstore import PiscesLxRunIdFactory, PiscesLxRunStore, PiscesLxTrainingRunReporter
+from .trainer import YvTrainer, YvTrainerConfig
+
+
+def load_stage_config(stage: str, path: Optional[str] = None) -> Dict[str, Any]:
+    p = Path(path) if path else REPO_ROOT / "configs" / "train" / f"{stage}.yaml"
+    if not p.exists():
+        p = REPO_ROOT / "configs" / "train" / "default.yaml"
+    return yaml.safe_load(p.read_text()) or {}
+
+
+def build_trainer_config(model_cfg: YvConfig, stage_cfg: Dict[str, Any], args: Any) -> YvTrainerConfig:
+    tc = dict(model_cfg.extra.get("training_config") or {})
+    opt = dict(stage_cfg.get("optimizer") or {})
+    sch = dict(stage_cfg.get("scheduler") or {})
+    cfg = YvTrainerConfig(
+        micro_batch_size=int(stage_cfg.get("micro_batch_size", tc.get("micro_batch_size", 1))),
+        optimizer=str(opt.get("name", tc.get("optimizer", "muon"))),
+        lr=float(opt.get("lr", tc.get("lr", 2e-4))),
+        weight_decay=float(opt.get("weight_decay", tc.get("weight_decay", 0.1))),
+        scheduler=str(sch.get("type", "cosine")),
+        warmup_steps=max(1, int(sch.get("warmup_steps", tc.get("warmup_steps", 1)))),
+        min_lr_ratio=max(0.1, float(sch.get("min_lr_ratio", 0.1))),
+        max_steps=int(stage_cfg.get("max_steps", 1000)),
+        clip_grad_norm=float(stage_cfg.get("clip_grad_norm", 1.0)),
+        save_steps=int(stage_cfg.get("save_steps", 1000)),
+        log_steps=int(stage_cfg.get("log_steps", 10)),
+    )
+    for name in ("micro_batch_size", "max_steps", "lr", "optimizer", "save_steps", "output_dir"):
+        v = getattr(args, name, None)
+        if v is not None:
+            setattr(cfg, name, v)
+    return cfg
+
+
+class PiscesLxTrainOrchestrator:
+    def __init__(self, args: Any):
+        self.args = args
+
+    def run(self, args: Any) -> int:
+        from ..data.datasets import build_dataloader
+        from ..models import build_model
+        from ..parallel.state import destroy_parallel, init_parallel
+        from ..utils.seed import PiscesLxDeterminism
+
+        PiscesLxDeterminism.seed_everything(args.seed)
+        model_cfg = resolve_model_config(args.model_size, args.model_config)
+        dist_cfg = dict(model_cfg.extra.get("distributed") or {})
+        tp = args.tensor_parallel or int(dist_cfg.get("tensor_parallel", 1))
+        ep = args.expert_parallel or int(dist_cfg.get("expert_parallel", 1))
+        pp = args.pipeline_parallel or int(dist_cfg.get("pipeline_parallel", 1))
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world == 1:
+            tp = ep = pp = 1
+        device = torch.device(args.device) if args.device else None
+        par = init_parallel(tp=tp, ep=ep, pp=pp, device=device)
+        if args.no_fused_comm:
+            from ..parallel import fused
+            fused.set_enabled(False)
+        stage_cfg = load_stage_config(args.stage, args.train_config)
+        tcfg = build_trainer_config(model_cfg, stage_cfg, args)
+        seq_len = args.seq_len or int(stage_cfg.get("seq_len", 512))
+        batch = args.batch_size or tcfg.micro_batch_size * int(stage_cfg.get("gradient_accumulation_steps", 1))
+        dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, None: None}[args.dtype]
+        if par.device.type == "cpu":
+            model_cfg.use_gradient_checkpointing = False
+        if args.dry_run:
+            if par.rank == 0:
+                print(json.dumps({"model": model_cfg.count_parameters(), "trainer": tcfg.__dict__, "seq_len": seq_len,
+                                  "batch": batch, "parallel": {"tp": tp, "ep": ep, "pp": pp, "world": world}},
+                                 default=str))
+            return 0
+        model = build_model(model_cfg, par.device, dtype, parallel=par if world > 1 else None, seed=args.seed)
+        attach_optional_components(model, model_cfg, par)
+        tcfg.streaming_optimizer = bool(stage_cfg.get("streaming_optimizer", False))
+        trainer = YvTrainer(model, tcfg, parallel=par if world > 1 else None)
+        store = PiscesLxRunStore(Path(args.run_dir) if args.run_dir else None)
+        run_id = args.run_id or PiscesLxRunIdFactory.new("train")
+        reporter = None
+        if par.rank == 0:
+            if not (store.run_dir(run_id) / "state.json").exists():
+                store.init_run(run_id, {"command": "train", "args": {k: v for k, v in vars(args).items()}})
+            store.update_state(run_id, status="running", pid=os.getpid())
+            reporter = PiscesLxTrainingRunReporter(store, run_id, trainer)
+            trainer.callbacks.append(reporter)
+        if args.resume_ckpt:
+            from .checkpoint import load_checkpoint
+            load_checkpoint(trainer, args.resume_ckpt, reset_lr=args.reset_lr)
+        loader = build_dataloader(args.dataset, model_cfg.vocab_size, seq_len, batch, seed=args.seed + par.dp_rank)
+        status = "completed"
+        try:
+            for batch_t in loader:
+                if trainer.global_step >= tcfg.max_steps or (reporter is not None and reporter.stop_requested):
+                    break
+                while reporter is not None and reporter.paused and not reporter.stop_requested:
+                    time.sleep(0.5)
+                    reporter.poll_control()
+                res = trainer.train_step(batch_t)
+                if par.rank == 0 and trainer.global_step % max(tcfg.log_steps, 1) == 0:
+                    print(f"step {res['global_step']} loss {res['loss']:.4f} lr {res['learning_rate']:.3e} "
+                          f"tok/s {res['token_throughput']:.0f}", flush=True)
+                if tcfg.save_steps and trainer.global_step % tcfg.save_steps == 0:
+                    from .checkpoint import save_checkpoint
+                    save_checkpoint(trainer, f"{tcfg.output_dir}/checkpoint_step_{trainer.global_step}.pt")
+        except KeyboardInterrupt:
+            status = "interrupted"
+        except Exception as e:
+            status = "failed"
+            if par.rank == 0:
+                store.append_event(run_id, "error", message=str(e))
+            raise
+        finally:
+            from .checkpoint import save_checkpoint
+            if tcfg.save_steps:
+                save_checkpoint(trainer, f"{tcfg.output_dir}/final_model.pt")
+            if par.rank == 0:
+                store.update_state(run_id, status=status, finished=time.time(), global_step=trainer.global_step)
+            if world > 1:
+                destroy_parallel()
+        return 0
+
+
+class PiscesLxInferOrchestrator:
+    def __init__(self, args: Any):
+        self.args = args
+
+    def run(self, args: Any) -> int:
+        from ..models.tokenizer import YvTokenizer
+        tok = YvTokenizer.instance()
+        if args.dry_run:
+            print(json.dumps({"prompt_tokens": len(tok.encode(args.prompt)), "model_size": args.model_size}))
+            return 0
+        model = load_model_for_inference(args.model_size, args.ckpt, args.device, args.model_config)
+        ids = torch.tensor([tok.encode(args.prompt)], dtype=torch.long, device=next(model.parameters()).device)
+        ids = ids.clamp_(0, model.cfg.vocab_size - 1)
+        t0 = time.perf_counter()
+        if args.speculative:
+            from ..models.speculative import YvSpeculativeDecoder
+            out, stats = YvSpeculativeDecoder(model).speculative_generate(ids, max_new_tokens=args.max_new_tokens)
+        else:
+            out, stats = model.generate(ids, max_new_tokens=args.max_new_tokens, temperature=args.temperature,
+                                        top_k=args.top_k, top_p=args.top_p)
+        dt = time.perf_counter() - t0
+        text = tok.decode(out[0, ids.shape[1]:].tolist())
+        print(json.dumps({"text": text, "stats": stats, "seconds": dt,
+                          "tokens_per_second": stats.get("generated_tokens", 0) / max(dt, 1e-9)}))
+        return 0

@@ -1,0 +1,157 @@
+"""Kernel micro-benchmarks and the small cases used for ``ncu`` captures.
+
+    python -m pisceslx_b200.ops.bench_kernels --kernel gemm --m 8192 --n 8192 --k 8192 --iters 10
+    python -m pisceslx_b200.ops.bench_kernels --kernel attn_fwd --batch 4 --seq 4096
+    python -m pisceslx_b200.ops.bench_kernels --all --json out.json
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, a write of a 256 MB buffer between timed
+launches (larger than L2) unless the operands themselves exceed L2.  Fractions are taken against the measured
+peaks in ``MEASURED_PEAKS.json`` at the repository root when present (copy bandwidth and cuBLAS bf16 burst
+throughput), else against 6.65 TB/s and 1.59 PFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+from typing import Any, Callable, Dict
+
+import torch
+
+from . import kernels, status_word
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> Dict[str, Any]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
+
+
+def timeit(fn: Callable[[], None], iters: int, flush: bool = True) -> float:
+    K = kernels()
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if buf is not None:
+            K.l2_flush(buf)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def bench_gemm(a: argparse.Namespace) -> Dict[str, Any]:
+    K, st = kernels(), status_word(torch.device("cuda"))
+    M, N, Kd = a.m, a.n, a.k
+    A = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16)
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: K.gemm(A, B, C, False, False, False, a.bn, st), a.iters)
+    tf = 2.0 * M * N * Kd / ms / 1e9
+    return {"kernel": "gemm_sm100", "shape": [M, N, Kd], "ms": ms, "tflops": tf, "frac_of_peak": tf / peaks()["bf16_tflops"]}
+
+
+def bench_attn(a: argparse.Namespace, bwd: bool) -> Dict[str, Any]:
+    K, st = kernels(), status_word(torch.device("cuda"))
+    B, S, hq, hk, d = a.batch, a.seq, a.hq, a.hk, a.d
+    T = B * S
+    qkv = torch.randn(T, (hq + 2 * hk) * d, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv[:, : hq * d], qkv[:, hq * d:(hq + hk) * d], qkv[:, (hq + hk) * d:]
+    o = torch.empty(T, hq * d, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(hq, T, device="cuda")
+    cu = torch.arange(0, T + 1, S, dtype=torch.int32, device="cuda")
+    sc = 1.0 / math.sqrt(d)
+    flops = 4.0 * B * hq * S * S * d / 2
+    K.attn_fwd(q, k, v, o, lse, cu, None, S, S, hq, hk, d, True, sc, st)
+    if not bwd:
+        ms = timeit(lambda: K.attn_fwd(q, k, v, o, lse, cu, None, S, S, hq, hk, d, True, sc, st), a.iters)
+        tf = flops / ms / 1e9
+        return {"kernel": "attn_fwd", "shape": [B, S, hq, hk, d], "ms": ms, "tflops": tf,
+                "frac_of_peak": tf / peaks()["bf16_tflops"]}
+    do = torch.randn_like(o)
+    dqkv = torch.empty_like(qkv)
+    dq, dk, dv = dqkv[:, : hq * d], dqkv[:, hq * d:(hq + hk) * d], dqkv[:, (hq + hk) * d:]
+    delta = torch.empty(hq, T, device="cuda")
+    ms = timeit(lambda: K.attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, cu, None, S, S, hq, hk, d, True, sc, st), a.iters)
+    tf = 2.5 * flops / ms / 1e9
+    return {"kernel": "attn_bwd", "shape": [B, S, hq, hk, d], "ms": ms, "tflops_5gemm": tf,
+            "frac_of_peak": tf / peaks()["bf16_tflops"]}
+
+
+def bench_rmsnorm(a: argparse.Namespace) -> Dict[str, Any]:
+    K = kernels()
+    T, H = a.m, a.n
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn_like(x)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    y, ro, rstd = torch.empty_like(x), torch.empty_like(x), torch.empty(T, device="cuda")
+    ms = timeit(lambda: K.rmsnorm_fwd(x, r, w, None, None, 1, y, ro, rstd, 1e-6), a.iters)
+    gbs = 4.0 * T * H * 2 / ms / 1e6
+    return {"kernel": "rmsnorm_fwd(+residual)", "shape": [T, H], "ms": ms, "gbs": gbs, "frac_of_peak": gbs / peaks()["hbm_gbs"]}
+
+
+def bench_decode(a: argparse.Namespace) -> Dict[str, Any]:
+    from . import functional as F_
+    B, hq, hk, d, blk, ctx = a.batch, a.hq, a.hk, a.d, 64, a.seq
+    nb = B * (ctx // blk)
+    kc = torch.randn(nb, blk, hk, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    bt = torch.arange(nb, dtype=torch.int32, device="cuda").view(B, ctx // blk)
+    sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn(B, hq, d, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: F_.paged_decode(q, kc, vc, bt, sl), a.iters, flush=False)
+    gbs = 2.0 * kc.numel() * 2 / ms / 1e6
+    return {"kernel": "paged_decode", "shape": [B, ctx, hq, hk, d], "ms": ms, "gbs": gbs,
+            "frac_of_peak": gbs / peaks()["hbm_gbs"]}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "decode"])
+    ap.add_argument("--all", action="store_true")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hk", type=int, default=8)
+    ap.add_argument("--d", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args()
+    res = []
+    if a.all:
+        for shape in [(8192, 8192, 8192), (16384, 6144, 4096), (16384, 4096, 4096), (8192, 5632, 4096)]:
+            a.m, a.n, a.k = shape
+            res.append(bench_gemm(a))
+        res.append(bench_attn(a, False))
+        res.append(bench_attn(a, True))
+        a.m, a.n = 32768, 4096
+        res.append(bench_rmsnorm(a))
+        a.batch, a.seq = 64, 4096
+        res.append(bench_decode(a))
+    else:
+        fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
+              "rmsnorm": bench_rmsnorm, "decode": bench_decode}[a.kernel]
+        res.append(fn(a))
+    out = {"peaks": peaks(), "results": res}
+    print(json.dumps(out, indent=1))
+    if a.json:
+        json.dump(out, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,196 @@
+"""Inference engine with continuous batching over the paged KV cache.
+
+The reference serves one request at a time on one GPU: prefill, then a Python decode loop per request
+(tools/infer/core.py:1106-1144); ``max_concurrency`` only limits HTTP handlers.  Here requests are queued, each
+engine step admits waiting requests while cache blocks are free (prefill, one request at a time so that TTFT stays
+low), and all running sequences decode together in one batched step (one token each) through the paged-decode
+kernel.  Finished sequences release their blocks immediately.  ``generate`` / ``generate_stream`` /
+``embeddings`` keep the reference engine's surface (``PiscesLxInferenceEngine``).
+"""
+from __future__ import annotations
+
+import threading
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Any, Callable, Deque, Dict, Iterator, List, Optional
+
+import torch
+
+from ..models.cache import YvPagedKVCache, cache_for_model
+from ..models.generation import YvSampler, YvSamplingConfig, _decode_step, _prefill
+from ..models.tokenizer import YvTokenizer
+
+
+@dataclass
+class YvRequest:
+    request_id: int
+    prompt_ids: List[int]
+    max_new_tokens: int = 128
+    sampling: YvSamplingConfig = field(default_factory=YvSamplingConfig)
+    stop_token_ids: List[int] = field(default_factory=list)
+    output_ids: List[int] = field(default_factory=list)
+    arrival: float = field(default_factory=time.perf_counter)
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+    finished: bool = False
+    finish_reason: Optional[str] = None
+    on_token: Optional[Callable[[int], None]] = None
+    _next_logits: Optional[torch.Tensor] = None
+
+    @property
+    def ttft(self) -> Optional[float]:
+        return None if self.first_token_time is None else self.first_token_time - self.arrival
+
+
+@dataclass
+class YvEngineConfig:
+    max_num_seqs: int = 64
+    num_blocks: int = 4096
+    block_size: int = 64
+    max_model_len: int = 131072
+    eos_token_id: Optional[int] = None
+
+
+class YvInferenceEngine:
+    def __init__(self, model: torch.nn.Module, tokenizer: Optional[YvTokenizer] = None,
+                 cfg: Optional[YvEngineConfig] = None):
+        self.model, self.tokenizer, self.cfg = model.eval(), tokenizer or YvTokenizer.instance(), cfg or YvEngineConfig()
+        p = next(model.parameters())
+        self.device = p.device
+        tp = model.parallel.tp_size if getattr(model, "parallel", None) is not None else 1
+        self.cache: YvPagedKVCache = cache_for_model(model.cfg, self.device, self.cfg.num_blocks, self.cfg.block_size,
+                                                     tp_size=tp, n_layer=len(model.model.layers), dtype=p.dtype)
+        self.cache.layer_offset = model.model.layer_lo
+        self.waiting: Deque[YvRequest] = deque()
+        self.running: List[YvRequest] = []
+        self._next_id = 0
+        self._lock = threading.Lock()
+        self.stats = {"requests": 0, "tokens_generated": 0, "prefill_tokens": 0, "steps": 0, "errors": 0,
+                      "ttft": [], "latency": []}
+        self.eos = self.cfg.eos_token_id if self.cfg.eos_token_id is not None else model.cfg.eos_token_id
+
+    # ---- request management ---------------------------------------------------------------------------
+    def add_request(self, prompt_ids: List[int], max_new_tokens: int = 128,
+                    sampling: Optional[YvSamplingConfig] = None, stop_token_ids: Optional[List[int]] = None,
+                    on_token: Optional[Callable[[int], None]] = None) -> YvRequest:
+        with self._lock:
+            rid = self._next_id
+            self._next_id += 1
+        req = YvRequest(rid, list(prompt_ids), max_new_tokens, sampling or YvSamplingConfig(),
+                        list(stop_token_ids or []), on_token=on_token)
+        self.waiting.append(req)
+        self.stats["requests"] += 1
+        return req
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _finish(self, req: YvRequest, reason: str) -> None:
+        req.finished, req.finish_reason, req.finish_time = True, reason, time.perf_counter()
+        self.cache.free_sequence(req.request_id)
+        if req.ttft is not None:
+            self.stats["ttft"].append(req.ttft)
+        self.stats["latency"].append(req.finish_time - req.arrival)
+
+    def _emit(self, req: YvRequest, token: int) -> None:
+        req.output_ids.append(token)
+        self.stats["tokens_generated"] += 1
+        if req.first_token_time is None:
+            req.first_token_time = time.perf_counter()
+        if req.on_token is not None:
+            req.on_token(token)
+        if token == self.eos or token in req.stop_token_ids:
+            self._finish(req, "stop")
+        elif len(req.output_ids) >= req.max_new_tokens:
+            self._finish(req, "length")
+
+    # ---- one scheduler iteration ---------------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self) -> None:
+        self.stats["steps"] += 1
+        # admit: prefill waiting requests while there is room
+        while self.waiting and len(self.running) < self.cfg.max_num_seqs:
+            req = self.waiting[0]
+            need = (len(req.prompt_ids) + req.max_new_tokens + self.cfg.block_size - 1) // self.cfg.block_size
+            if need > self.cache.alloc.available():
+                if not self.running:
+                    self.waiting.popleft()
+                    req.finished, req.finish_reason = True, "error: prompt does not fit the KV cache"
+                    self.stats["errors"] += 1
+                    continue
+                break
+            self.waiting.popleft()
+            self.cache.add_sequence(req.request_id)
+            ids = torch.tensor([req.prompt_ids], dtype=torch.long, device=self.device)
+            logits = _prefill(self.model, ids, self.cache, [req.request_id])
+            self.stats["prefill_tokens"] += len(req.prompt_ids)
+            tok = int(YvSampler(req.sampling).sample(logits, ids)[0])
+            self.running.append(req)
+            self._emit(req, tok)
+        self.running = [r for r in self.running if not r.finished]
+        if not self.running:
+            return
+        # decode: one token for every running sequence in a single batched step
+        seq_ids = [r.request_id for r in self.running]
+        last = torch.tensor([r.output_ids[-1] for r in self.running], dtype=torch.long, device=self.device)
+        logits = _decode_step(self.model, last, self.cache, seq_ids)
+        greedy = all(r.sampling.strategy == "greedy" for r in self.running)
+        if greedy:
+            toks = logits.argmax(-1).tolist()
+        else:
+            toks = []
+            for i, r in enumerate(self.running):
+                prev = torch.tensor([r.prompt_ids + r.output_ids], dtype=torch.long, device=self.device)
+                toks.append(int(YvSampler(r.sampling).sample(logits[i:i + 1], prev)[0]))
+        for r, t in zip(self.running, toks):
+            self._emit(r, int(t))
+        self.running = [r for r in self.running if not r.finished]
+
+    def run_until_done(self) -> None:
+        while self.has_work():
+            self.step()
+
+    # ---- reference-style surface --------------------------------------------------------------------------------
+    def generate(self, prompt: str, max_new_tokens: int = 128, temperature: float = 0.0, top_k: int = 0,
+                 top_p: float = 1.0, **_: Any) -> Dict[str, Any]:
+        strat = "greedy" if temperature <= 0 else "top_k_top_p"
+        req = self.add_request(self.tokenizer.encode(prompt), max_new_tokens,
+                               YvSamplingConfig(strategy=strat, temperature=max(temperature, 1e-5), top_k=top_k,
+                                                top_p=top_p))
+        while not req.finished:
+            self.step()
+        return {"text": self.tokenizer.decode(req.output_ids), "tokens": req.output_ids,
+                "finish_reason": req.finish_reason, "ttft": req.ttft,
+                "usage": {"prompt_tokens": len(req.prompt_ids), "completion_tokens": len(req.output_ids)}}
+
+    def generate_stream(self, prompt: str, max_new_tokens: int = 128, **kw: Any) -> Iterator[str]:
+        out: List[int] = []
+        req = self.add_request(self.tokenizer.encode(prompt), max_new_tokens, on_token=out.append)
+        sent = 0
+        while not req.finished or sent < len(out):
+            if not req.finished:
+                self.step()
+            while sent < len(out):
+                yield self.tokenizer.decode([out[sent]])
+                sent += 1
+
+    @torch.no_grad()
+    def embeddings(self, text: str) -> List[float]:
+        """Mean of the final hidden states (reference tools/infer/core.py:1191-1204)."""
+        ids = torch.tensor([self.tokenizer.encode(text)], dtype=torch.long, device=self.device)
+        out = self.model(input_ids=ids, return_logits=False, return_hidden=True)
+        return out["hidden_states"].float().mean(1)[0].tolist()
+
+    def get_stats(self) -> Dict[str, Any]:
+        s = dict(self.stats)
+        tt = sorted(s.pop("ttft"))
+        lat = s.pop("latency")
+        s["p50_ttft"] = tt[len(tt) // 2] if tt else None
+        s["mean_latency"] = sum(lat) / len(lat) if lat else None
+        s["running"], s["waiting"] = len(self.running), len(self.waiting)
+        s["free_blocks"] = self.cache.alloc.available()
+        return s
+
+
+PiscesLxInferenceEngine = YvInferenceEngine

@@ -1,0 +1,3 @@
+"""Platform utilities."""
+from .dc import (PiscesLxDeterminism, PiscesLxDeviceResolver, PiscesLxHostMemoryBudget, PiscesLxLogger, PiscesLxMetrics,
+                 PiscesLxPaths, PiscesLxTracing, PiscesLxVramController)
