@@ -1,0 +1,50 @@
+// Allocation-free entry point for paged-KV decode attention.
+//
+// This entry point has no counterpart in the reference project: it exists for callers of this library that
+// are not allowed to allocate device memory at the moment they need a decode step - a serving loop whose
+// memory pool was sized up front and handed out completely, a step recorded after the process has frozen
+// its allocator, or a host that drives the library from a language runtime without access to the PyTorch
+// caching allocator.  The regular path (torch.ops.yv.paged_decode) asks its caller for two fp32 scratch
+// tensors for the split-KV partial results; here that scratch lives in a fixed array inside the library.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Capacity of the built-in scratch: batch * hq * splits * (d + 2) floats must not exceed this number.
+// The array is part of the library image: every GPU that loads the library holds these 8.25 MiB until the
+// process exits.
+#define YV_NOALLOC_SCRATCH_FLOATS 2162688
+
+// Error codes (0 = launched).
+#define YV_NOALLOC_OK 0
+#define YV_NOALLOC_TOO_LARGE -1      // the problem needs more scratch than YV_NOALLOC_SCRATCH_FLOATS
+#define YV_NOALLOC_BAD_ARGUMENT -2   // unsupported head size / group size, null pointer, splits < 1
+#define YV_NOALLOC_SETUP_FAILED -3   // the address of the scratch array could not be resolved on this device
+// positive values are cudaError_t codes from the launch
+
+// One decode step over a paged KV cache, exactly the computation of the regular paged decode:
+//   q [batch, hq, d] bf16, caches [num_blocks, block, hk, d] bf16, block_table [batch, max_blocks_per_seq] int32,
+//   seq_lens [batch] int32, o [batch, hq, d] bf16 (written).  `stream` is a cudaStream_t (0 = default stream).
+//
+// Properties a caller can rely on:
+//   * calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are the caller's;
+//   * the first call on each device resolves the device address of the scratch array (one
+//     cudaGetSymbolAddress with that device current).  Make that first call outside of any stream capture;
+//   * every call uses the same scratch array.  Nothing in it has to start at zero (each element is written
+//     before it is read within a call), and it keeps the last call's partial results afterwards.  Two calls
+//     that overlap on the GPU (different streams, or different threads on one device) race on it: serialise
+//     calls per device;
+//   * sizes beyond the capacity are rejected with YV_NOALLOC_TOO_LARGE and nothing is launched.
+int yv_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                            const int32_t* seq_lens, void* o, int batch, int hq, int hk, int d, int block,
+                            int max_blocks_per_seq, int num_blocks, int splits, float scale, void* stream);
+
+// Human-readable text for the codes above (static storage).
+const char* yv_noalloc_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
