@@ -179,6 +179,18 @@ __global__ void axpby_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
   }
 }
 
+// out[g] = a * I + b * A[g] + c * A2[g] for a batch of n x n matrices (Newton-Schulz polynomial on the Gram side)
+__global__ void ns_poly_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ A2,
+                               __nv_bfloat16* __restrict__ out, int64_t total, int n, float a, float b, float c) {
+  const int64_t nn = static_cast<int64_t>(n) * n;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i % nn;
+    const float diag = (r / n == r % n) ? a : 0.f;
+    out[i] = __float2bfloat16(diag + b * __bfloat162float(A[i]) + c * __bfloat162float(A2[i]));
+  }
+}
+
 __global__ void sumsq_kernel(const void* __restrict__ x, int dtype, int64_t n, float* __restrict__ out) {
   float s = 0.f;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
@@ -348,6 +360,14 @@ int launch_frob_normalize(void* x, float* norms, int batch, int64_t per_matrix, 
 int launch_axpby(const void* x, const void* y, void* out, int64_t n, float a, float b, cudaStream_t stream) {
   if (n <= 0) return 0;
   axpby_kernel<<<grid_for(n, 256), 256, 0, stream>>>(YV_BF(x), YV_BF(y), YV_BFM(out), n, a, b);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_ns_poly(const void* A, const void* A2, void* out, int64_t batch, int n, float a, float b, float c,
+                   cudaStream_t stream) {
+  const int64_t total = batch * static_cast<int64_t>(n) * n;
+  if (total <= 0) return 0;
+  ns_poly_kernel<<<grid_for(total, 256), 256, 0, stream>>>(YV_BF(A), YV_BF(A2), YV_BFM(out), total, n, a, b, c);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -166,6 +166,9 @@ int launch_muon_apply(void* p, const void* u, int64_t n, float lr, float wd, flo
 int launch_frob_normalize(void* x, float* norms, int batch, int64_t per_matrix, float eps, cudaStream_t stream);
 // out = a*x + b*y (bf16 in/out)
 int launch_axpby(const void* x, const void* y, void* out, int64_t n, float a, float b, cudaStream_t stream);
+// out = a * I + b * A + c * A2 for a batch of n x n bf16 matrices
+int launch_ns_poly(const void* A, const void* A2, void* out, int64_t batch, int n, float a, float b, float c,
+                   cudaStream_t stream);
 int launch_sumsq(const void* x, int dtype, int64_t n, float* out_accum, cudaStream_t stream);
 int launch_scale(void* x, int dtype, int64_t n, const float* scale_dev, float scale_host, cudaStream_t stream);
 // im2col for non-overlapping patches: img [B,C,H,W] fp32/bf16 -> patches bf16 [B*gh*gw, Kpad] (normalised by mean/std)
