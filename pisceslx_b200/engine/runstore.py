@@ -231,7 +231,20 @@ class PiscesLxTaskRecovery:
             return True
 
     @staticmethod
-    def find_latest_checkpoint(directory: str) -> Optional[PiscesLxCheckpointInfo]:
+    def _readable(path: str) -> bool:
+        """A ``torch.save`` file is a zip archive whose directory sits at the end: a file cut short in mid-write
+        has none, so opening the archive (no tensor is read) tells the two apart."""
+        if os.path.isdir(path):
+            return os.path.exists(os.path.join(path, "meta.json")) or bool(os.listdir(path))
+        import zipfile
+        try:
+            with zipfile.ZipFile(path) as z:
+                return len(z.namelist()) > 0
+        except (zipfile.BadZipFile, OSError):
+            return False
+
+    @staticmethod
+    def find_latest_checkpoint(directory: str, validate: bool = False) -> Optional[PiscesLxCheckpointInfo]:
         best: Optional[PiscesLxCheckpointInfo] = None
         for f in glob.glob(os.path.join(directory, "checkpoint_step_*.pt")) + glob.glob(
                 os.path.join(directory, "checkpoint_step_*_sharded")):
@@ -240,6 +253,8 @@ class PiscesLxTaskRecovery:
                 continue
             if os.path.isfile(f) and os.path.getsize(f) == 0:
                 continue                                   # a truncated file is not a checkpoint
+            if validate and not PiscesLxTaskRecovery._readable(f):
+                continue
             info = PiscesLxCheckpointInfo(f, int(m.group(1)), os.path.getmtime(f))
             if best is None or info.step > best.step:
                 best = info

@@ -75,6 +75,7 @@ class YvTrainer:
         self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.elastic_guard: Any = None                    # parallel.elastic.YvElasticGuard, set by the orchestrator
 
     # ------------------------------------------------------------------------------------------------
     def _stage(self, t: torch.Tensor) -> torch.Tensor:
@@ -110,6 +111,8 @@ class YvTrainer:
         """One optimizer step over ``batch`` (host or device tensors: input_ids [B,S], labels [B,S], optional
         attention_mask).  Returns the step result; ``loss`` is read back from the device."""
         cfg = self.cfg
+        if self.elastic_guard is not None:                # peers' liveness + last step's device status, host only
+            self.elastic_guard.before_step()
         self.model.train()
         t0 = time.perf_counter()
         ev0 = ev1 = None
