@@ -143,7 +143,7 @@ def main() -> None:
     cfg.tensor_parallel, cfg.expert_parallel = tp, ep
     cfg.fused_comm = not args.no_fused_comm
     cfg.use_gradient_checkpointing = True
-    seqs = args.seqs_per_gpu or 32
+    seqs = args.seqs_per_gpu or 64            # 64 per GPU = the named global batch of 512 sequences on 8 GPUs
     micro = args.micro_batch or (2 if world == 1 else 4)
     model = build_model(cfg, dev, torch.bfloat16, parallel=par if world > 1 else None, seed=1234)
     tcfg = YvTrainerConfig(micro_batch_size=micro, optimizer="muon", lr=2e-4, weight_decay=0.1, warmup_steps=10,
@@ -176,13 +176,22 @@ def main() -> None:
     check_status()
 
     # ---- kernel launch census over one untimed step ----
+    # A step is n_micro identical micro-batches plus a fixed part (optimizer, collectives); counting a one- and a
+    # two-micro-batch step under the profiler gives both terms without tracing a full-size step.
     launches_per_step = None
     try:
         from torch.profiler import ProfilerActivity, profile
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            run(dev_batches, 1)
-            torch.cuda.synchronize(dev)
-        launches_per_step = sum(e.count for e in prof.key_averages() if "yv::" in e.key)
+
+        def census(n_micro: int) -> int:
+            small = dev_batches[0][: micro * n_micro]
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                trainer.train_step({"input_ids": small, "labels": small})
+                torch.cuda.synchronize(dev)
+            return sum(e.count for e in prof.key_averages() if "yv::" in e.key)
+
+        l1, l2 = census(1), census(2)
+        n_micro_step = (seqs_rank + micro - 1) // micro
+        launches_per_step = (l1 - (l2 - l1)) + (l2 - l1) * n_micro_step
     except Exception:
         launches_per_step = None
 

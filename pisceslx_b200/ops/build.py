@@ -29,6 +29,28 @@ def _cuda_home() -> str:
     return os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
+def _host_cxx() -> str:
+    """The distribution's g++.  The library must share the process's libstdc++ with torch: a compiler named by
+    ``$CXX`` that links its own static copy gives two sets of locale facets in one process, and the first
+    formatted error message (a ``TORCH_CHECK`` that prints a number) then crashes instead of raising.  ``YV_CXX``
+    overrides; the link step names ``-lstdc++`` explicitly and the result is checked for that dependency."""
+    forced = os.environ.get("YV_CXX")
+    if forced:
+        return forced
+    import shutil
+    for cand in ("/usr/bin/g++", shutil.which("g++")):
+        if cand and os.path.exists(cand):
+            return cand
+    return "g++"
+
+
+def _check_dynamic_libstdcxx(so: Path) -> None:
+    r = subprocess.run(["readelf", "-d", str(so)], capture_output=True, text=True)
+    if r.returncode == 0 and "libstdc++.so" not in r.stdout:
+        raise RuntimeError(f"{so} does not depend on the shared libstdc++ (static C++ runtime linked in): "
+                           "set YV_CXX to the system g++")
+
+
 def _newer(src: Path, dst: Path, extra: List[Path]) -> bool:
     if not dst.exists():
         return True
@@ -59,11 +81,11 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         obj = OBJ / (name + ".o")
         objs.append(obj)
         if force or _newer(src, obj, headers):
-            jobs.append([nvcc] + NVCC_FLAGS + ["-I", str(CSRC), "-c", str(src), "-o", str(obj)])
+            jobs.append([nvcc, "-ccbin", _host_cxx()] + NVCC_FLAGS + ["-I", str(CSRC), "-c", str(src), "-o", str(obj)])
     inc = []
     for p in ce.include_paths("cuda"):
         inc += ["-isystem", p]
-    cxx = os.environ.get("CXX", "g++")
+    cxx = _host_cxx()
     for name in CPP_SOURCES:
         src = CSRC / name
         obj = OBJ / (name + ".o")
@@ -82,8 +104,9 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
         cmd = [cxx, "-shared", "-o", str(SO)] + [str(o) for o in objs] + [
             f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
-            f"-L{os.path.join(_cuda_home(), 'lib64')}", "-lcudart", f"-Wl,-rpath,{torch_lib}"]
+            f"-L{os.path.join(_cuda_home(), 'lib64')}", "-lcudart", "-lstdc++", f"-Wl,-rpath,{torch_lib}"]
         _run(cmd)
+        _check_dynamic_libstdcxx(SO)
     return SO
 
 

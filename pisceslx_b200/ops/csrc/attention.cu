@@ -46,7 +46,7 @@ int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.causal = a.causal;
   p.scale_log2 = a.scale * kLog2eHost;
   p.status = a.status;
-  dim3 grid((a.max_q + kAttnQRows - 1) / kAttnQRows, a.hq, a.batch);
+  dim3 grid((a.max_q + 127) / 128, a.hq, a.batch);
   if (a.d == 128) {
     static bool cfg = false;
     if (!cfg) { r = set_smem(attn_fwd_kernel<128>, AttnFwdSmem<128>::kTotal); if (r) return r; cfg = true; }

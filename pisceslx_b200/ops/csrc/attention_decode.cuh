@@ -58,94 +58,52 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const PagedDecodePara
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
   }
 
-  // Keys of the split are walked with a stride of 16 groups; every group takes KPI keys per step so that
-  // 2 * KPI * EPL/8 independent 16-byte loads are in flight before the first one is consumed, and the running
-  // (max, sum, accumulator) is rescaled once per step instead of once per key.
-  constexpr int KPI = 4;
-  constexpr int VEC = EPL / 8;
-  const int key0 = blk0 * p.block;
-  const int key1 = min(seq_len, blk1 * p.block);
-  const int* table = p.block_table + static_cast<int64_t>(b) * p.max_blocks_per_seq;
-  for (int kbase = key0 + grp; kbase < key1; kbase += 16 * KPI) {
-    uint4 kraw[KPI][VEC], vraw[KPI][VEC];
-    bool live[KPI];
-#pragma unroll
-    for (int j = 0; j < KPI; ++j) {
-      const int t = kbase + 16 * j;
-      live[j] = t < key1;
-      if (live[j]) {
-        const int phys = table[t / p.block];
-        if (phys < 0 || phys >= p.num_blocks) {
-          if (p.status != nullptr && sub == 0) atomicOr(p.status, kStatusIndexOutOfRange);
-          live[j] = false;
-        } else {
-          const int64_t off = ((static_cast<int64_t>(phys) * p.block + (t % p.block)) * p.hk + kvh) * D + sub * EPL;
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            kraw[j][e] = *reinterpret_cast<const uint4*>(p.k_cache + off + e * 8);
-            vraw[j][e] = *reinterpret_cast<const uint4*>(p.v_cache + off + e * 8);
-          }
-        }
-      }
+  for (int blk = blk0; blk < blk1; ++blk) {
+    const int phys = p.block_table[static_cast<int64_t>(b) * p.max_blocks_per_seq + blk];
+    if (phys < 0 || phys >= p.num_blocks) {
+      if (p.status != nullptr && tid == 0) atomicOr(p.status, kStatusIndexOutOfRange);
+      continue;
     }
-    float sc[KPI][G];
+    const int in_blk = min(p.block, seq_len - blk * p.block);
+    for (int t0 = 0; t0 < in_blk; t0 += 16) {
+      const int t = t0 + grp;
+      const bool live = t < in_blk;
+      float kf[EPL], vf[EPL];
+      if (live) {
+        const int64_t off = ((static_cast<int64_t>(phys) * p.block + t) * p.hk + kvh) * D + sub * EPL;
 #pragma unroll
-    for (int j = 0; j < KPI; ++j) {
-      float kf[EPL];
-      if (live[j]) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[j][e]);
+        for (int e = 0; e < EPL; e += 8) {
+          const uint4 kr = *reinterpret_cast<const uint4*>(p.k_cache + off + e);
+          const uint4 vr = *reinterpret_cast<const uint4*>(p.v_cache + off + e);
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kr);
+          const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vr);
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
             const float2 a = __bfloat1622float2(k2[x]);
-            kf[e * 8 + 2 * x] = a.x;
-            kf[e * 8 + 2 * x + 1] = a.y;
+            const float2 c = __bfloat1622float2(v2[x]);
+            kf[e + 2 * x] = a.x; kf[e + 2 * x + 1] = a.y;
+            vf[e + 2 * x] = c.x; vf[e + 2 * x + 1] = c.y;
           }
         }
       }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         float s = 0.f;
-        if (live[j]) {
+        if (live) {
 #pragma unroll
           for (int e = 0; e < EPL; ++e) s += kf[e] * s_q[g][sub * EPL + e];
         }
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
-        sc[j][g] = live[j] ? s : -1.0e30f;
-      }
-    }
+        if (live) {
+          const float mn = fmaxf(m[g], s);
+          const float alpha = exp2f(m[g] - mn);
+          const float pr = exp2f(s - mn);
+          l[g] = l[g] * alpha + pr;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float mn = m[g];
-#pragma unroll
-      for (int j = 0; j < KPI; ++j) mn = fmaxf(mn, sc[j][g]);
-      const float alpha = exp2f(m[g] - mn);
-      float pr[KPI], ps = 0.f;
-#pragma unroll
-      for (int j = 0; j < KPI; ++j) {
-        pr[j] = live[j] ? exp2f(sc[j][g] - mn) : 0.f;
-        ps += pr[j];
-      }
-      l[g] = l[g] * alpha + ps;
-      m[g] = mn;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[g][e] *= alpha;
-#pragma unroll
-      for (int j = 0; j < KPI; ++j) {
-        if (live[j]) {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[j][e]);
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              const float2 c = __bfloat1622float2(v2[x]);
-              acc[g][e * 8 + 2 * x] += pr[j] * c.x;
-              acc[g][e * 8 + 2 * x + 1] += pr[j] * c.y;
-            }
-          }
+          for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * alpha + pr * vf[e];
+          m[g] = mn;
         }
       }
     }

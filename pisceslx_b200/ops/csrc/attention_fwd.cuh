@@ -1,16 +1,12 @@
 // Flash attention forward for sm_100a: GQA, causal or full, packed variable-length sequences.
 //
-// One CTA per (256-query block, query head, sequence); 320 threads:
-//   warp 0        TMA producer: two Q tiles once, then K_j / V_j tiles through two-stage rings
-//   warp 1        MMA issuer.  For each of the two 128-row query tiles t: S_t = Q_t K_j^T (SS) into TMEM,
-//                 O_t += P_t V_j (TS: P_t is read from TMEM where the softmax warps wrote it over S_t).
-//                 The two tiles are staggered: while the softmax warps of one tile work, the tensor core runs
-//                 the other tile's P V and next Q K^T.
-//   warps 2..5    softmax of tile 0: thread r owns query row r (= TMEM lane r)
-//   warps 6..9    softmax of tile 1
-// The softmax is bound by the special-function unit (exp2 and the bf16 packing both issue there), so every
-// other exponential is evaluated on the FMA pipe instead (round-to-nearest split + cubic for 2^frac).
-// TMEM columns: [0,128) S0/P0, [128,256) S1/P1, [256,256+D) O0, [384,384+D) O1.
+// One CTA per (128-query block, query head, sequence); 192 threads:
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles through two-stage rings
+//   warp 1      MMA issuer:  S_j = Q K_j^T (SS) into one of two TMEM S buffers, O += P_j V_j (TS: P read
+//               from TMEM where the softmax warps wrote it over S_j)
+//   warps 2..5  softmax: thread r owns query row r (= TMEM lane r): tcgen05.ld the 128 scores, online
+//               softmax with lazy rescaling of the O accumulator, pack P to bf16, tcgen05.st
+// TMEM columns: [0,128) S0/P0, [128,256) S1/P1, [256,256+D) O.
 #pragma once
 #include "sm100.cuh"
 
@@ -32,33 +28,17 @@ struct AttnFwdParams {
   uint32_t* status;
 };
 
-constexpr int kAttnThreads = 320;
-constexpr int kAttnBlock = 128;     // key rows per tile; query rows per tile
-constexpr int kAttnQRows = 256;     // query rows per CTA (two tiles)
+constexpr int kAttnThreads = 192;
+constexpr int kAttnBlock = 128;     // query rows and key rows per tile
 constexpr float kMaskValue = -1.0e30f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units: O is rescaled only when the row max grew by more
 
 template <int D>
 struct AttnFwdSmem {
-  static constexpr int kTile = kAttnBlock * D * 2;       // bytes of one 128-row Q/K/V tile
+  static constexpr int kTile = kAttnBlock * D * 2;       // bytes of one Q/K/V tile
   static constexpr int kStages = 2;
-  static constexpr int kTotal = kTile * (2 + 2 * kStages) + 256 + 1024;
+  static constexpr int kTotal = kTile * (1 + 2 * kStages) + 256 + 1024;
 };
-
-// 2^x for x <= 0 on the FMA / integer pipes: x = n + f with n = round(x), f in [-0.5, 0.5];
-// 2^f by a cubic (relative error ~1e-4, far below bf16 resolution), 2^n by an exponent-field add.
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -125.f);
-  const float magic = 12582912.f;                  // 1.5 * 2^23: adding it rounds x to an integer in the mantissa
-  const float r = x + magic;
-  const float n = r - magic;
-  const float f = x - n;
-  float p = fmaf(f, 0.0555041086f, 0.2402265069f);
-  p = fmaf(p, f, 0.6931471806f);
-  p = fmaf(p, f, 1.0f);
-  const int shift = (__float_as_int(r) - 0x4B400000) << 23;
-  return __int_as_float(__float_as_int(p) + shift);
-}
 
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
@@ -69,11 +49,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   constexpr uint32_t kIdescQK = make_idesc_bf16(128, 128, false, false);
   constexpr uint32_t kIdescPV = make_idesc_bf16(128, D, false, true);
   constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kOCol = 256;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                                   // two tiles
-  uint8_t* sK = sQ + 2 * S::kTile;
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + S::kTile;
   uint8_t* sV = sK + kStages * S::kTile;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kStages * S::kTile);
   uint64_t* q_full = bars;                 // [1]
@@ -81,10 +62,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   uint64_t* k_empty = bars + 3;            // [2]
   uint64_t* v_full = bars + 5;             // [2]
   uint64_t* v_empty = bars + 7;            // [2]
-  uint64_t* s_full = bars + 9;             // [2] per query tile
-  uint64_t* p_full = bars + 11;            // [2] per query tile, 128 arrivals
-  uint64_t* o_done = bars + 13;            // [2] per query tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* s_full = bars + 9;             // [2]
+  uint64_t* p_full = bars + 11;            // [2]
+  uint64_t* o_done = bars + 13;            // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -93,27 +74,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   const int hkv = h / (p.hq / p.hk);
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
-  const int n_qblk = (q_len + kAttnQRows - 1) / kAttnQRows;
+  const int n_qblk = (q_len + kAttnBlock - 1) / kAttnBlock;
   // heavy (late) query blocks first for causal load balance
   const int q_blk = n_qblk - 1 - static_cast<int>(blockIdx.x);
   if (q_blk < 0) return;
-  const int q0 = q_blk * kAttnQRows;
-  const int n_kv_all = (k_len + kAttnBlock - 1) / kAttnBlock;
+  const int q0 = q_blk * kAttnBlock;
+  int n_kv = (k_len + kAttnBlock - 1) / kAttnBlock;
   // causal: query i (bottom-right aligned when k_len != q_len) sees keys <= i + (k_len - q_len)
   const int causal_shift = k_len - q_len;
-  int n_kv_t[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    int n = n_kv_all;
-    if (p.causal) {
-      const int last_key = q0 + t * kAttnBlock + kAttnBlock - 1 + causal_shift;
-      const int lim = last_key / kAttnBlock + 1;
-      n = last_key < 0 ? 0 : (lim < n ? lim : n);
-    }
-    if (q0 + t * kAttnBlock >= q_len) n = 0;           // the second tile may lie past the end of the sequence
-    n_kv_t[t] = n;
+  if (p.causal) {
+    const int last_key = q0 + kAttnBlock - 1 + causal_shift;
+    const int lim = last_key / kAttnBlock + 1;
+    n_kv = last_key < 0 ? 0 : (lim < n_kv ? lim : n_kv);
   }
-  const int n_kv = n_kv_t[0] > n_kv_t[1] ? n_kv_t[0] : n_kv_t[1];
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&p.tma_q);
@@ -127,8 +100,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 128);
-      mbar_init(&o_done[s], 1);
     }
+    mbar_init(o_done, 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -143,12 +116,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
   if (warp == 0) {
     // ------------------------------------ producer ------------------------------------------
     if (elect_one() && n_kv > 0) {
-      mbar_expect_tx(q_full, 2 * S::kTile);
+      mbar_expect_tx(q_full, S::kTile);
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
-#pragma unroll
-        for (int c = 0; c < kDBoxes; ++c)
-          tma_load_3d(sQ + t * S::kTile + c * kBoxBytes, &p.tma_q, q_full, c * 64, h, q_begin + q0 + t * kAttnBlock);
+      for (int c = 0; c < kDBoxes; ++c) tma_load_3d(sQ + c * kBoxBytes, &p.tma_q, q_full, c * 64, h, q_begin + q0);
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j % kStages;
@@ -174,84 +144,62 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
     if (elect_one() && n_kv > 0) {
       bool ok = mbar_wait(q_full, 0, p.status);
       const uint32_t aQ = smem_u32(sQ);
-      // S_t(j) = Q_t K_j^T.  The K stage is released after the last tile that uses block j has read it.
-      auto issue_qk = [&](int t, int j) {
+      auto issue_qk = [&](int j) -> bool {
         const int s = j % kStages;
+        if (!mbar_wait(&k_full[s], (j / kStages) & 1u, p.status)) return false;
+        tc_fence_after_sync();
         const uint32_t aK = smem_u32(sK + s * S::kTile);
-        const uint32_t tS = tmem_base + static_cast<uint32_t>(t * 128);
+        const uint32_t tS = tmem_base + static_cast<uint32_t>((j & 1) * 128);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-          tc_mma_f16_ss(tS, make_smem_desc(aQ + t * S::kTile + off, 16, 1024), make_smem_desc(aK + off, 16, 1024),
-                        kIdescQK, kk != 0 ? 1u : 0u);
+          tc_mma_f16_ss(tS, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), kIdescQK,
+                        kk != 0 ? 1u : 0u);
         }
-        tc_commit(&s_full[t]);
+        tc_commit(&k_empty[s]);
+        tc_commit(&s_full[j & 1]);
+        return true;
       };
-      auto issue_pv = [&](int t, int j) {
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
         const int s = j % kStages;
+        ok = mbar_wait(&p_full[j & 1], (j >> 1) & 1u, p.status);
+        if (!ok) break;
+        ok = mbar_wait(&v_full[s], (j / kStages) & 1u, p.status);
+        if (!ok) break;
+        tc_fence_after_sync();
         const uint32_t aV = smem_u32(sV + s * S::kTile);
-        const uint32_t tP = tmem_base + static_cast<uint32_t>(t * 128);
-        const uint32_t tO = tmem_base + 256u + static_cast<uint32_t>(t * 128);
+        const uint32_t tP = tmem_base + static_cast<uint32_t>((j & 1) * 128);
+        const uint32_t tO = tmem_base + kOCol;
 #pragma unroll
         for (int kk = 0; kk < kAttnBlock / 16; ++kk) {
           // 16 keys per step: 8 packed bf16x2 columns of P; 16 key rows (2048 B) of the V tile
           tc_mma_f16_ts(tO, tP + kk * 8, make_smem_desc(aV + kk * 2048, kBoxBytes, 1024), kIdescPV,
                         (j | kk) != 0 ? 1u : 0u);
         }
-        tc_commit(&o_done[t]);
-      };
-      // prologue: both tiles' first scores
-      if (ok) {
-        ok = mbar_wait(&k_full[0], 0, p.status);
-        if (ok) {
-          tc_fence_after_sync();
-          for (int t = 0; t < 2; ++t)
-            if (n_kv_t[t] > 0) issue_qk(t, 0);
-          tc_commit(&k_empty[0]);
-        }
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j % kStages;
-        const bool have_next = (j + 1 < n_kv);
-        if (have_next) {
-          ok = mbar_wait(&k_full[(j + 1) % kStages], ((j + 1) / kStages) & 1u, p.status);
-          if (!ok) break;
-        }
-        ok = mbar_wait(&v_full[s], (j / kStages) & 1u, p.status);
-        if (!ok) break;
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j < n_kv_t[t]) {
-            ok = mbar_wait(&p_full[t], j & 1u, p.status);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_pv(t, j);
-            if (j + 1 < n_kv_t[t]) issue_qk(t, j + 1);       // in order after the P V product that read P_t(j)
-          }
-        }
-        if (!ok) break;
         tc_commit(&v_empty[s]);
-        if (have_next) tc_commit(&k_empty[(j + 1) % kStages]);
+        tc_commit(o_done);
       }
     }
   } else {
     // ------------------------------------ softmax / epilogue --------------------------------
-    const int tile = (warp - 2) >> 2;                 // 0 or 1
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;              // query row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const int q_pos = q0 + tile * kAttnBlock + row;   // position inside the sequence
+    const int q_pos = q0 + row;                       // position inside the sequence
     const int key_limit = p.causal ? (q_pos + causal_shift) : (k_len - 1);   // last visible key
-    const int my_kv = n_kv_t[tile];
-    const uint32_t tS = tmem_base + lane_off + static_cast<uint32_t>(tile * 128);
-    const uint32_t tO = tmem_base + lane_off + 256u + static_cast<uint32_t>(tile * 128);
     float m_used = -1.0e29f;                          // running max (log2 domain); above kMaskValue so masked scores give 0
     float l_sum = 0.f;
     bool ok = true;
-    for (int j = 0; j < my_kv && ok; ++j) {
-      ok = mbar_wait(&s_full[tile], j & 1u, p.status);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1u, p.status);
       if (!ok) break;
       tc_fence_after_sync();
+      const uint32_t tS = tmem_base + lane_off + static_cast<uint32_t>((j & 1) * 128);
       uint32_t sreg[128];
       {
         uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sreg[0]);
@@ -286,18 +234,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       uint32_t pk[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        const float a = exp2f(__uint_as_float(sreg[2 * i]) - m_used);          // special-function unit
-        const float c = exp2_fma(__uint_as_float(sreg[2 * i + 1]) - m_used);   // FMA pipe
+        const float a = exp2f(__uint_as_float(sreg[2 * i]) - m_used);
+        const float c = exp2f(__uint_as_float(sreg[2 * i + 1]) - m_used);
         rs += a + c;
         pk[i] = pack_bf16(a, c);
       }
       l_sum = l_sum * alpha + rs;
       if (__any_sync(0xFFFFFFFFu, rescale)) {
         // O holds sums relative to the old max: wait for the previous P V product, then scale the row
-        ok = mbar_wait(&o_done[tile], (j - 1) & 1u, p.status);
+        ok = mbar_wait(o_done, (j - 1) & 1u, p.status);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
         tc_fence_after_sync();
+        const uint32_t tO = tmem_base + lane_off + kOCol;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t ov[32];
@@ -316,11 +265,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       }
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&p_full[tile]);
+      mbar_arrive(&p_full[j & 1]);
     }
     // ---- epilogue: O / l, LSE ----
-    if (ok && my_kv > 0) {
-      ok = mbar_wait(&o_done[tile], (my_kv - 1) & 1u, p.status);
+    if (ok && n_kv > 0) {
+      ok = mbar_wait(o_done, (n_kv - 1) & 1u, p.status);
       ok = __all_sync(0xFFFFFFFFu, ok);
     }
     if (ok) {
@@ -328,10 +277,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       const bool valid = q_pos < q_len;
       const float inv_l = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
       __nv_bfloat16* orow = p.o + (static_cast<int64_t>(q_begin + q_pos) * p.o_stride) + static_cast<int64_t>(h) * D;
+      const uint32_t tO = tmem_base + lane_off + kOCol;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t ov[32];
-        if (my_kv > 0) {
+        if (n_kv > 0) {
           tmem_ld32(tO + c * 32, ov);
           tc_wait_ld();
         } else {

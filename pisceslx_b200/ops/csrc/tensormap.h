@@ -13,6 +13,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn get_encode_tiled() {
+  // The encoder is a driver call and fails (invalid context) in a thread that has not yet made a runtime call of
+  // its own, e.g. a fresh autograd worker whose first device work is a TMA kernel.  A null free is the cheapest
+  // runtime call that binds the device's primary context to the calling thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (fn == nullptr) {
     void* p = nullptr;
