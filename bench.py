@@ -148,7 +148,7 @@ def main() -> None:
     model = build_model(cfg, dev, torch.bfloat16, parallel=par if world > 1 else None, seed=1234)
     tcfg = YvTrainerConfig(micro_batch_size=micro, optimizer="muon", lr=2e-4, weight_decay=0.1, warmup_steps=10,
                            max_steps=10_000, streaming_optimizer=True, clip_grad_norm=0.0, log_steps=1,
-                           track_grad_norm=False)
+                           track_grad_norm=False, recompute_policy="auto")
     trainer = YvTrainer(model, tcfg, parallel=par if world > 1 else None)
 
     # tensor-parallel peers work on the same sequences: batch size and seed follow the data-parallel rank
@@ -173,6 +173,8 @@ def main() -> None:
 
     # ---- warm-up (untimed) ----
     run(dev_batches, args.warmup)
+    while trainer.recompute_planner is not None and trainer.recompute_planner.stage < 3:
+        run(dev_batches, 1)                      # the recompute plan needs two measured steps before it is final
     check_status()
 
     # ---- kernel launch census over one untimed step ----
@@ -241,7 +243,8 @@ def main() -> None:
                                 "ffn2816, vocab 154856" + ("" if args.layers == 32 else f" [INVALID: {args.layers} layers]"),
                        "global_batch": seqs_rank * par.dp_size, "seq_len": SEQ,
                        "micro_batch": micro, "parallelism": par_name, "optimizer": "Muon(2-D)+AdamW, bf16 states, "
-                       "gradients consumed inside backward", "activation_recompute": "per layer",
+                       "gradients consumed inside backward", "activation_recompute": ("per layer, sized from measured memory: " + trainer.recompute_planner.summary())
+                       if trainer.recompute_planner is not None else "per layer",
                        "l2": "inputs larger than L2 (80 GB of weights and >1 GB of activations per layer)",
                        "fused_comm": bool(cfg.fused_comm) if world > 1 else None},
             "clocks": clocks, "e2e": e2e,

@@ -47,6 +47,7 @@ class YvTrainerConfig:
     output_dir: str = ".pisceslx/ckpt"
     abort_on_non_finite: bool = True
     state_dtype: Optional[str] = None       # "bf16" | "fp32" | None (= parameter dtype)
+    recompute_policy: str = "config"        # "config": as the model config says; "auto": sized from measured memory
     optimizer_kwargs: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -76,6 +77,10 @@ class YvTrainer:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.elastic_guard: Any = None                    # parallel.elastic.YvElasticGuard, set by the orchestrator
+        self.recompute_planner: Any = None
+        if cfg.recompute_policy == "auto" and self.device.type == "cuda" and hasattr(model, "model"):
+            from .memory_plan import YvRecomputePlanner
+            self.recompute_planner = YvRecomputePlanner(model, self.device)
 
     # ------------------------------------------------------------------------------------------------
     def _stage(self, t: torch.Tensor) -> torch.Tensor:
@@ -113,6 +118,8 @@ class YvTrainer:
         cfg = self.cfg
         if self.elastic_guard is not None:                # peers' liveness + last step's device status, host only
             self.elastic_guard.before_step()
+        if self.recompute_planner is not None:
+            self.recompute_planner.before_step()
         self.model.train()
         t0 = time.perf_counter()
         ev0 = ev1 = None
@@ -156,6 +163,8 @@ class YvTrainer:
         self.global_step += 1
         loss_val = float(mean_loss.item())                # D2H read of the step result
         self.d2h_bytes += 4
+        if self.recompute_planner is not None:
+            self.recompute_planner.after_step()
         step_ms = None
         if ev1 is not None:
             ev1.record()

@@ -112,6 +112,12 @@ class YvTransformerBlock(nn.Module):
                 return self._body(recomputing, h_, d_, ctx, f)
 
             return recompute(run, h, delta, fs, fb)
+        if getattr(self, "measure_stored", False) and h.is_cuda and torch.is_grad_enabled():
+            # bytes this layer's forward leaves allocated for its backward (read by the recompute planner)
+            m0 = torch.cuda.memory_allocated(h.device)
+            out = self._body(False, h, delta, ctx, film_params)
+            self.stored_bytes = max(getattr(self, "stored_bytes", 0), torch.cuda.memory_allocated(h.device) - m0)
+            return out
         return self._body(False, h, delta, ctx, film_params)
 
     # checkpoint key mapping -----------------------------------------------------------------------
