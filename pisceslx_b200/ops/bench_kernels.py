@@ -116,9 +116,36 @@ def bench_decode(a: argparse.Namespace) -> Dict[str, Any]:
             "frac_of_peak": gbs / peaks()["hbm_gbs"]}
 
 
+def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
+    """Batched Newton-Schulz on [batch, m, n] (the Muon orthogonalisation of a stack of expert matrices), plus the
+    three batched GEMMs of one iteration timed separately."""
+    from ..optim.muon import NS_COEFFS, newton_schulz_batched
+    K, st = kernels(), status_word(torch.device("cuda"))
+    G, n, m = a.batch, a.m, a.n
+    x = torch.randn(G, n, m, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: newton_schulz_batched(x), max(1, a.iters // 3))
+    s, l = min(n, m), max(n, m)
+    flops = len(NS_COEFFS) * G * (4.0 * s * s * l + 2.0 * s ** 3)
+    A = torch.empty(G, s, s, device="cuda", dtype=torch.bfloat16)
+    A2, Y = torch.empty_like(A), torch.empty_like(x)
+    if n <= m:
+        t_gram = timeit(lambda: K.gemm_batched(x, x, A, False, False, False, 0, st), a.iters)
+        t_sq = timeit(lambda: K.gemm_batched(A, A, A2, False, False, False, 0, st), a.iters)
+        t_apply = timeit(lambda: K.gemm_batched(A2, x, Y, False, True, False, 0, st), a.iters)
+    else:
+        t_gram = timeit(lambda: K.gemm_batched(x, x, A, True, True, False, 0, st), a.iters)
+        t_sq = timeit(lambda: K.gemm_batched(A, A, A2, False, False, False, 0, st), a.iters)
+        t_apply = timeit(lambda: K.gemm_batched(x, A2, Y, False, False, False, 0, st), a.iters)
+    tf = flops / ms / 1e9
+    return {"kernel": "newton_schulz_batched", "shape": [G, n, m], "ms": ms, "tflops": tf,
+            "frac_of_peak": tf / peaks()["bf16_tflops"],
+            "gemm_tflops": {"gram": 2.0 * G * s * s * l / t_gram / 1e9, "square": 2.0 * G * s ** 3 / t_sq / 1e9,
+                            "apply": 2.0 * G * s * s * l / t_apply / 1e9}}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="gemm", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "decode"])
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns"])
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -145,7 +172,7 @@ def main() -> None:
         res.append(bench_decode(a))
     else:
         fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
-              "rmsnorm": bench_rmsnorm, "decode": bench_decode}[a.kernel]
+              "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz}[a.kernel]
         res.append(fn(a))
     out = {"peaks": peaks(), "results": res}
     print(json.dumps(out, indent=1))

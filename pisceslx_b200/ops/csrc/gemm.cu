@@ -20,17 +20,24 @@ int sm_count() {
   return g_sm_count;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
+template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0>
 int launch_instance(const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT>;
+  auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT, COMM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
+  kern<<<grid, COMM == 1 ? kGemmThreadsAllGather : kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
+}
+
+// The fused tensor-parallel variants exist for A stored [M,K] and bf16 output only.
+template <int BN, int COMM>
+int dispatch_comm(const GemmArgs& a, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (a.b_mn) return launch_instance<BN, false, true, __nv_bfloat16, COMM>(p, grid, stream);
+  return launch_instance<BN, false, false, __nv_bfloat16, COMM>(p, grid, stream);
 }
 
 template <int BN, typename OutT>
@@ -123,12 +130,42 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
                    out_bytes, a.c, static_cast<uint64_t>(a.N), c_outer, ldc, 128 / out_bytes, kBM);
   if (r != 0) return -40 + r;
 
+  p.comm_world = 1; p.comm_rank = 0; p.comm_blocks_per_rank = 0;
+  p.comm_local = nullptr; p.comm_flags = nullptr; p.comm_flag_target = 0; p.comm_row_bytes = 0;
+  for (int i = 0; i < 8; ++i) p.comm_peer[i] = nullptr;
+  if (a.comm != 0) {
+    if (a.comm != 1 && a.comm != 2) return -50;
+    if (a.mode != kDense || a.a_mn || a.out_fp32 || a.accumulate) return -51;
+    if (a.comm_world < 2 || a.comm_world > 8 || a.comm_rank < 0 || a.comm_rank >= a.comm_world) return -52;
+    if (a.comm_rows_per_rank <= 0 || a.comm_rows_per_rank % kBM != 0 ||
+        a.comm_rows_per_rank * a.comm_world != a.M) return -53;
+    if (a.comm == 1 && (a.comm_flags == nullptr || (a.lda != 0 && a.lda != a.K))) return -54;
+    if (a.comm == 2 && (a.N % 64) != 0) return -55;
+    for (int r = 0; r < a.comm_world; ++r)
+      if (r != a.comm_rank && a.comm_peer[r] == nullptr) return -56;
+    p.comm_world = a.comm_world; p.comm_rank = a.comm_rank;
+    p.comm_blocks_per_rank = static_cast<int>(a.comm_rows_per_rank / kBM);
+    for (int r = 0; r < a.comm_world; ++r) p.comm_peer[r] = a.comm_peer[r];
+    p.comm_local = static_cast<uint8_t*>(const_cast<void*>(a.a));
+    p.comm_flags = a.comm_flags;
+    p.comm_row_bytes = a.comm == 1 ? static_cast<long long>(a.K) * 2 : static_cast<long long>(a.N) * 2;
+  }
+
   const int64_t tiles_m = (p.M + kBM - 1) / kBM;
   const int64_t tiles_n = (a.N + bn - 1) / bn;
   int64_t tiles = tiles_m * tiles_n * ((a.mode == kGroupedK || a.mode == kBatched) ? a.num_groups : 1);
   const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
 
+  if (a.comm == 1) {
+    cudaError_t e = cudaMemsetAsync(a.comm_flags, 0, sizeof(uint32_t) * static_cast<size_t>(tiles_m), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    p.comm_flag_target = static_cast<uint32_t>(grid);
+    return bn == 256 ? dispatch_comm<256, 1>(a, p, grid, stream) : dispatch_comm<128, 1>(a, p, grid, stream);
+  }
+  if (a.comm == 2) {
+    return bn == 256 ? dispatch_comm<256, 2>(a, p, grid, stream) : dispatch_comm<128, 2>(a, p, grid, stream);
+  }
   if (bn == 256) {
     return a.out_fp32 ? dispatch_layout<256, float>(a, p, grid, stream)
                       : dispatch_layout<256, __nv_bfloat16>(a, p, grid, stream);

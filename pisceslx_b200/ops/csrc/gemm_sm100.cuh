@@ -39,11 +39,25 @@ struct GemmParams {
   const int* num_m_tiles;      // kGroupedM: number of valid 128-row tiles (device scalar)
   const int* seg_offsets;      // kGroupedK: [E+1] row offsets of the expert segments (multiples of 128)
   uint32_t* status;            // device status word (0 = ok)
+  // ---- fused tensor-parallel collectives (template parameter COMM != 0; dense mode, K-major A, bf16 C) ----
+  // COMM 1, all-gather -> GEMM: A = the local gathered buffer [world * rows_per_rank, K]; one extra warp per CTA
+  //   pulls the peers' shards into it 128-row block by block and counts each block complete in comm_flags; the
+  //   TMA producer waits for a block's count before it loads tiles of that block.  Own rows come first.
+  // COMM 2, GEMM -> reduce-scatter: tiles whose rows another rank owns are stored straight into that rank's inbox
+  //   [source rank][rows_per_rank, N] from the epilogue registers; own rows go to C as usual and come last.
+  int comm_world, comm_rank;
+  int comm_blocks_per_rank;    // 128-row blocks per rank
+  void* comm_peer[8];          // COMM 1: peers' published shards; COMM 2: peers' inboxes
+  uint8_t* comm_local;         // COMM 1: base of the local gathered A
+  uint32_t* comm_flags;        // COMM 1: one counter per 128-row block, zeroed before the launch
+  uint32_t comm_flag_target;   // COMM 1: count that marks a block complete (= number of CTAs)
+  long long comm_row_bytes;    // COMM 1: bytes per row of A; COMM 2: bytes per row of an inbox
 };
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
+constexpr int kGemmThreadsAllGather = 224;   // + one warp that pulls the peers' shards
 constexpr int kGroupBand = 16;   // m-tiles per rasterisation band
 
 template <int BN>
@@ -63,10 +77,11 @@ struct TileCoord {
   int b_x, b_y;
   int c_x, c_y;
   int k_iters;
+  int m_blk;         // 128-row block of A / C this tile covers
 };
 
 // Decode linear tile index -> coordinates.  Returns false when idx is past the end.
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int COMM = 0>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int tiles_m, int tiles_n, TileCoord& t) {
   int m_blk, n_blk, group = 0;
   if (p.mode == kGroupedK || p.mode == kBatched) {
@@ -84,6 +99,11 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
     const int band_m = min(kGroupBand, tiles_m - band * kGroupBand);
     n_blk = r / band_m;
     m_blk = band * kGroupBand + (r - n_blk * band_m);
+    if (COMM != 0) {
+      // rotate the row blocks: all-gather starts with the rows this rank already holds, reduce-scatter ends with them
+      const int shift = (COMM == 1 ? p.comm_rank : p.comm_rank + 1) * p.comm_blocks_per_rank;
+      m_blk = (m_blk + shift) % tiles_m;
+    }
   }
   // grouped-M problems may list their 128-row tiles explicitly (receive regions of several sources)
   const int row_tile = (p.mode == kGroupedM && p.tile_rows != nullptr) ? p.tile_rows[m_blk] : m_blk;
@@ -107,11 +127,12 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
   if (B_MN) { t.b_x = n0; t.b_y = b_outer_off + k_begin; } else { t.b_x = k_begin; t.b_y = b_outer_off + n0; }
   t.c_x = n0;
   t.c_y = c_row_off + m0;
+  t.m_blk = row_tile;
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0>
+__global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   constexpr int kColsPerChunk = 128 / sizeof(OutT);       // columns covered by one 128-byte staging row
@@ -170,7 +191,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __gri
       bool ok = true;
       for (int idx = blockIdx.x; ok; idx += gridDim.x) {
         TileCoord t;
-        if (!decode_tile<BN, A_MN, B_MN>(p, idx, tiles_m, tiles_n, t)) break;
+        if (!decode_tile<BN, A_MN, B_MN, COMM>(p, idx, tiles_m, tiles_n, t)) break;
+        if (COMM == 1 && t.m_blk / p.comm_blocks_per_rank != p.comm_rank) {
+          // rows of another rank: the copier warps of all CTAs must have landed this block in local memory
+          const volatile uint32_t* flag = p.comm_flags + t.m_blk;
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(const_cast<const uint32_t*>(flag)) < p.comm_flag_target) {
+            if ((++spins & 0x3Fu) == 0u) {
+              if (globaltimer_ns() - t0 > YV_WAIT_LIMIT_NS) {
+                if (p.status != nullptr) atomicOr(p.status, kStatusPeerTimeout);
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();      // the block was written by generic-proxy stores; TMA reads it next
+        }
         for (int k = 0; k < t.k_iters && ok; ++k, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -203,7 +242,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __gri
       bool ok = true;
       for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
         TileCoord t;
-        if (!decode_tile<BN, A_MN, B_MN>(p, idx, tiles_m, tiles_n, t)) break;
+        if (!decode_tile<BN, A_MN, B_MN, COMM>(p, idx, tiles_m, tiles_n, t)) break;
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1u;
         ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1u, p.status);
@@ -236,6 +275,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __gri
         }
       }
     }
+  } else if (COMM == 1 && warp == 6) {
+    // ------------------------------- all-gather copier ----------------------------------------
+    // Every CTA's copier warp takes a 1/gridDim slice of each remote 128-row block, in the order in which the
+    // tiles will need the blocks, and counts the block in its flag when its slice has landed.
+    const int bpr = p.comm_blocks_per_rank;
+    const int64_t vec_per_block = (static_cast<int64_t>(kBM) * p.comm_row_bytes) >> 4;
+    for (int lb = bpr; lb < tiles_m; ++lb) {
+      const int phys = (lb + p.comm_rank * bpr) % tiles_m;
+      const int owner = phys / bpr;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.comm_peer[owner]) +
+                                                        static_cast<int64_t>(phys - owner * bpr) * kBM * p.comm_row_bytes);
+      uint4* dst = reinterpret_cast<uint4*>(p.comm_local + static_cast<int64_t>(phys) * kBM * p.comm_row_bytes);
+      const int64_t stride = static_cast<int64_t>(gridDim.x) * 32;
+      int64_t i = static_cast<int64_t>(blockIdx.x) * 32 + lane;
+      for (; i + 7 * stride < vec_per_block; i += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ld_peer_v4(src + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * stride] = v[u];
+      }
+      for (; i < vec_per_block; i += stride) dst[i] = ld_peer_v4(src + i);
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(p.comm_flags + phys, 1u);
+    }
+  } else if (warp >= 6) {
+    // no role (the kernel was launched with the all-gather block size without the all-gather mode)
   } else {
     // ------------------------------- epilogue -------------------------------------------------
     const int quarter = warp & 3;                      // TMEM lane quarter this warp may access
@@ -245,7 +312,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __gri
     bool ok = true;
     for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
       TileCoord t;
-      if (!decode_tile<BN, A_MN, B_MN>(p, idx, tiles_m, tiles_n, t)) break;
+      if (!decode_tile<BN, A_MN, B_MN, COMM>(p, idx, tiles_m, tiles_n, t)) break;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1u;
       ok = mbar_wait(&acc_full[acc], acc_ph, p.status);
@@ -267,6 +334,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_sm100_kernel(const __gri
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (COMM == 2 && sizeof(OutT) == 2 && t.m_blk / p.comm_blocks_per_rank != p.comm_rank) {
+        // reduce-scatter push: this thread's row of the tile goes from registers into the owner's inbox,
+        // inbox[source = this rank][row inside the owner's shard][column]
+        const int owner = t.m_blk / p.comm_blocks_per_rank;
+        const int64_t rows_per_rank = static_cast<int64_t>(p.comm_blocks_per_rank) * kBM;
+        const int64_t in_row = static_cast<int64_t>(t.m_blk - owner * p.comm_blocks_per_rank) * kBM + row;
+        uint8_t* drow = static_cast<uint8_t*>(p.comm_peer[owner]) +
+                        (static_cast<int64_t>(p.comm_rank) * rows_per_rank + in_row) * p.comm_row_bytes;
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          const int col0 = t.c_x + c * 64;
+          if (col0 >= p.N) break;                           // N is a multiple of 64 in this mode
+          uint32_t v0[32], v1[32];
+          tmem_ld32(taddr + c * 64, v0);
+          tmem_ld32(taddr + c * 64 + 32, v1);
+          tc_wait_ld();
+          uint4* d4 = reinterpret_cast<uint4*>(drow + static_cast<int64_t>(col0) * 2);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            d4[j] = make_uint4(pack_bf16(__uint_as_float(v0[8 * j]), __uint_as_float(v0[8 * j + 1])),
+                               pack_bf16(__uint_as_float(v0[8 * j + 2]), __uint_as_float(v0[8 * j + 3])),
+                               pack_bf16(__uint_as_float(v0[8 * j + 4]), __uint_as_float(v0[8 * j + 5])),
+                               pack_bf16(__uint_as_float(v0[8 * j + 6]), __uint_as_float(v0[8 * j + 7])));
+            d4[4 + j] = make_uint4(pack_bf16(__uint_as_float(v1[8 * j]), __uint_as_float(v1[8 * j + 1])),
+                                   pack_bf16(__uint_as_float(v1[8 * j + 2]), __uint_as_float(v1[8 * j + 3])),
+                                   pack_bf16(__uint_as_float(v1[8 * j + 4]), __uint_as_float(v1[8 * j + 5])),
+                                   pack_bf16(__uint_as_float(v1[8 * j + 6]), __uint_as_float(v1[8 * j + 7])));
+          }
+        }
+        tc_fence_before_sync();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) mbar_arrive(&acc_empty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < kChunks; ++c, ++chunk_it) {
         uint8_t* buf = smem_epi + (chunk_it & 1) * S::kEpiBytes;

@@ -30,6 +30,17 @@ struct GemmArgs {
   uint32_t* status = nullptr;
   int bn = 0;                  // 0 = choose
   int max_ctas = 0;            // 0 = number of SMs
+  // Fused tensor-parallel collective (dense mode, A stored [M,K], bf16 C, M = comm_world * comm_rows_per_rank,
+  // comm_rows_per_rank a multiple of 128):
+  //   1  all-gather -> GEMM: `a` is the local gathered buffer; comm_peer[r] = rank r's published shard
+  //      [rows_per_rank, K]; comm_flags = one uint32 per 128-row block (zeroed here before the launch)
+  //   2  GEMM -> reduce-scatter push: rows owned by rank r are stored into comm_peer[r] (= r's inbox,
+  //      [world][rows_per_rank, N]) at source slot comm_rank; own rows go to `c` (N a multiple of 64)
+  int comm = 0;
+  int comm_world = 1, comm_rank = 0;
+  int64_t comm_rows_per_rank = 0;
+  void* comm_peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  uint32_t* comm_flags = nullptr;
 };
 // Returns 0 on success, a negative code when an argument is rejected, a positive cudaError_t otherwise.
 int launch_gemm(const GemmArgs& args, cudaStream_t stream);

@@ -3,14 +3,18 @@
 ``allgather_gemm``      y = all_gather(x_shard) @ W      (column-parallel projections, sequence-parallel input)
 ``gemm_reduce_scatter`` y_shard = reduce_scatter(x @ W)  (row-parallel projections)
 
-Both take the peer-memory route when the symmetric heap of the group is available:
-  * all-gather -> GEMM: every rank publishes its shard in a symmetric buffer; the remote shards are pulled over
-    NVLink by a copy kernel on a side stream, chunk by chunk, while the tcgen05 GEMM already runs on the local
-    shard; the GEMM on each remote chunk is ordered after that chunk's copy by an event, so the copy of chunk
-    i+1 overlaps the math on chunk i.
-  * GEMM -> reduce-scatter: the GEMM is issued per destination shard (remote destinations first); each finished
-    shard is pushed into the owner's inbox by the copy kernel on the side stream while the next shard is being
-    computed; after a flag barrier the owner adds its inbox to the shard it computed itself.
+Each is ONE launch of the tcgen05 GEMM kernel in a communication mode (``gemm_tp``) when the shard has a whole
+number of 128-row blocks:
+  * all-gather -> GEMM: every rank publishes its shard in a symmetric buffer.  Inside the GEMM kernel one extra warp
+    per CTA pulls the peers' shards over NVLink into the local gathered buffer, 128-row block by block, and counts
+    each block complete; the TMA producer starts with the rows this rank already holds and waits (bounded) for a
+    block's count before loading tiles of it, so every remote byte crosses NVLink once and the transfer is hidden
+    behind the tiles of the local rows.
+  * GEMM -> reduce-scatter: the kernel computes the rows owned by the other ranks first and its epilogue stores
+    those tiles from registers straight into the owner's inbox (peer stores); the rank's own rows are computed last
+    and stored locally.  After a flag barrier the owner adds its inbox to its own partial rows.
+Shards that are not a multiple of 128 rows take the older route (copy kernel on a side stream ordered by events
+against per-shard GEMM launches).
 """
 from __future__ import annotations
 
@@ -35,6 +39,17 @@ def _side_stream(dev: torch.device) -> torch.cuda.Stream:
     return s
 
 
+_FLAGS: Dict[int, torch.Tensor] = {}
+
+
+def _block_flags(dev: torch.device, blocks: int) -> torch.Tensor:
+    t = _FLAGS.get(dev.index)
+    if t is None or t.numel() < blocks:
+        t = torch.zeros(max(blocks, 1024), dtype=torch.int32, device=dev)
+        _FLAGS[dev.index] = t
+    return t
+
+
 def allgather_gemm(x: torch.Tensor, w: torch.Tensor, group: Any, b_mn: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """x [T/tp, K] local shard, w [N, K] (or [K, N] when ``b_mn``).  Returns (gathered x [T, K], y [T, N])."""
     K = kernels()
@@ -51,6 +66,11 @@ def allgather_gemm(x: torch.Tensor, w: torch.Tensor, group: Any, b_mn: bool = Fa
     heap.barrier()                                   # every shard is published
     xg = torch.empty(world * rows, kdim, dtype=_BF16, device=dev)
     y = torch.empty(world * rows, n_out, dtype=_BF16, device=dev)
+    if rows % 128 == 0 and w.stride(-1) == 1:
+        xg[rank * rows:(rank + 1) * rows].copy_(x)
+        K.gemm_tp(xg, w, y, 1, pub.ptrs, _block_flags(dev, world * rows // 128), rank, rows, b_mn, 0,
+                  status_word(dev))
+        return xg, y
     side = _side_stream(dev)
     main = torch.cuda.current_stream(dev)
     side.wait_stream(main)
@@ -84,6 +104,15 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, group: Any, b_mn: bool
     inbox = heap.get("tp_rs_inbox", world * nbytes)                 # [source][rows, N]
     inbox_t = inbox.tensor(_BF16, world * rows * n_out).view(world, rows, n_out)
     heap.barrier()                                                  # owners consumed their previous inbox
+    if rows % 128 == 0 and n_out % 64 == 0 and rows * world == T and w.stride(-1) == 1:
+        full = torch.empty(T, n_out, dtype=_BF16, device=dev)
+        K.gemm_tp(x.contiguous(), w, full, 2, inbox.ptrs, None, rank, rows, b_mn, 0, status_word(dev))
+        heap.barrier()                                              # every inbox is complete
+        out = full[rank * rows:(rank + 1) * rows]
+        for s in range(world):
+            if s != rank:
+                out = out + inbox_t[s]
+        return out
     side = _side_stream(dev)
     main = torch.cuda.current_stream(dev)
     part = torch.empty(world, rows, n_out, dtype=_BF16, device=dev)

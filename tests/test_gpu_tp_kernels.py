@@ -1,0 +1,68 @@
+"""The fused tensor-parallel GEMM kernels on one GPU: the "peers" are other buffers of the same device, which is
+all the kernels need (they read or write peer memory and wait only on counters that their own CTAs advance)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2)])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("rows,K,N", [(256, 512, 384), (1024, 1024, 1536)])
+def test_allgather_gemm_single_kernel(world, rank, b_mn, rows, K, N):
+    from pisceslx_b200.ops import check_status, kernels, status_word
+    torch.manual_seed(world * 10 + rank)
+    Kn = kernels()
+    shards = [torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    wb = w.t().contiguous() if b_mn else w
+    xg = torch.zeros(world * rows, K, device=DEV, dtype=torch.bfloat16)
+    xg[rank * rows:(rank + 1) * rows] = shards[rank]
+    y = torch.empty(world * rows, N, device=DEV, dtype=torch.bfloat16)
+    ptrs = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64)
+    flags = torch.full((world * rows // 128 + 3,), 7, dtype=torch.int32, device=DEV)     # stale values are reset
+    st = status_word(torch.device(DEV, 0))
+    Kn.gemm_tp(xg, wb, y, 1, ptrs, flags, rank, rows, b_mn, 0, st)
+    torch.cuda.synchronize()
+    check_status()
+    full = torch.cat(shards)
+    assert torch.equal(xg, full)
+    assert _rel(y, full.float() @ w.float().t()) < 5e-3
+    assert int(flags[: world * rows // 128].min()) >= 0
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 3)])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gemm_reduce_scatter_push_single_kernel(world, rank, b_mn):
+    from pisceslx_b200.ops import check_status, kernels, status_word
+    torch.manual_seed(world * 10 + rank + 100)
+    Kn = kernels()
+    rows, K, N = 256, 768, 448
+    x = torch.randn(world * rows, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    wb = w.t().contiguous() if b_mn else w
+    inboxes = [torch.zeros(world, rows, N, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = torch.tensor([t.data_ptr() for t in inboxes], dtype=torch.int64)
+    full = torch.full((world * rows, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    st = status_word(torch.device(DEV, 0))
+    Kn.gemm_tp(x, wb, full, 2, ptrs, None, rank, rows, b_mn, 0, st)
+    torch.cuda.synchronize()
+    check_status()
+    ref = x.float() @ w.float().t()
+    own = slice(rank * rows, (rank + 1) * rows)
+    assert _rel(full[own], ref[own]) < 5e-3
+    for owner in range(world):
+        blk = ref[owner * rows:(owner + 1) * rows]
+        if owner == rank:
+            assert float(inboxes[owner].abs().max()) == 0.0            # nothing is pushed to oneself
+            continue
+        assert _rel(inboxes[owner][rank], blk) < 5e-3
+        others = [s for s in range(world) if s != rank]
+        assert all(float(inboxes[owner][s].abs().max()) == 0.0 for s in others)
+        assert torch.isnan(full[owner * rows:(owner + 1) * rows].float()).all()   # remote rows are not stored locally
