@@ -160,7 +160,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.comm == 1) {
     cudaError_t e = cudaMemsetAsync(a.comm_flags, 0, sizeof(uint32_t) * static_cast<size_t>(tiles_m), stream);
     if (e != cudaSuccess) return static_cast<int>(e);
-    p.comm_flag_target = static_cast<uint32_t>(grid);
+    p.comm_flag_target = static_cast<uint32_t>((static_cast<long long>(kBM) * p.comm_row_bytes) >> 4);   // vectors per block
     return bn == 256 ? dispatch_comm<256, 1>(a, p, grid, stream) : dispatch_comm<128, 1>(a, p, grid, stream);
   }
   if (a.comm == 2) {

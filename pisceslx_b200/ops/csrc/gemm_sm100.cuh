@@ -40,24 +40,25 @@ struct GemmParams {
   const int* seg_offsets;      // kGroupedK: [E+1] row offsets of the expert segments (multiples of 128)
   uint32_t* status;            // device status word (0 = ok)
   // ---- fused tensor-parallel collectives (template parameter COMM != 0; dense mode, K-major A, bf16 C) ----
-  // COMM 1, all-gather -> GEMM: A = the local gathered buffer [world * rows_per_rank, K]; one extra warp per CTA
-  //   pulls the peers' shards into it 128-row block by block and counts each block complete in comm_flags; the
+  // COMM 1, all-gather -> GEMM: A = the local gathered buffer [world * rows_per_rank, K]; extra warps in every CTA
+  //   pull the peers' shards into it and count the vectors landed per 128-row block in comm_flags; the
   //   TMA producer waits for a block's count before it loads tiles of that block.  Own rows come first.
   // COMM 2, GEMM -> reduce-scatter: tiles whose rows another rank owns are stored straight into that rank's inbox
-  //   [source rank][rows_per_rank, N] from the epilogue registers; own rows go to C as usual and come last.
+  //   [source rank][rows_per_rank, N] as 128-byte row segments; own rows go to C as usual and come last.
   int comm_world, comm_rank;
   int comm_blocks_per_rank;    // 128-row blocks per rank
   void* comm_peer[8];          // COMM 1: peers' published shards; COMM 2: peers' inboxes
   uint8_t* comm_local;         // COMM 1: base of the local gathered A
   uint32_t* comm_flags;        // COMM 1: one counter per 128-row block, zeroed before the launch
-  uint32_t comm_flag_target;   // COMM 1: count that marks a block complete (= number of CTAs)
+  uint32_t comm_flag_target;   // COMM 1: count that marks a block complete (= 16-byte vectors per block)
   long long comm_row_bytes;    // COMM 1: bytes per row of A; COMM 2: bytes per row of an inbox
 };
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
-constexpr int kGemmThreadsAllGather = 224;   // + one warp that pulls the peers' shards
+constexpr int kCopierWarps = 4;              // warps per CTA that pull the peers' shards (all-gather mode)
+constexpr int kGemmThreadsAllGather = kGemmThreads + 32 * kCopierWarps;
 constexpr int kGroupBand = 16;   // m-tiles per rasterisation band
 
 template <int BN>
@@ -275,31 +276,53 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
         }
       }
     }
-  } else if (COMM == 1 && warp == 6) {
-    // ------------------------------- all-gather copier ----------------------------------------
-    // Every CTA's copier warp takes a 1/gridDim slice of each remote 128-row block, in the order in which the
-    // tiles will need the blocks, and counts the block in its flag when its slice has landed.
+  } else if (COMM == 1 && warp >= 6) {
+    // ------------------------------- all-gather copiers ---------------------------------------
+    // The remote rows, taken in the order in which the tiles need their 128-row blocks, form one sequence of
+    // 16-byte vectors.  All copier lanes of the grid walk it in rounds of kRound vectors per lane: every load of a
+    // round is issued before the first store, so a round keeps several MB in flight over NVLink.  After its stores
+    // a warp adds, for each block the round touched, the number of vectors it landed to that block's counter; a
+    // block is complete when its counter reaches the number of vectors in a block.
+    constexpr int kRound = 16;
     const int bpr = p.comm_blocks_per_rank;
-    const int64_t vec_per_block = (static_cast<int64_t>(kBM) * p.comm_row_bytes) >> 4;
-    for (int lb = bpr; lb < tiles_m; ++lb) {
-      const int phys = (lb + p.comm_rank * bpr) % tiles_m;
-      const int owner = phys / bpr;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.comm_peer[owner]) +
-                                                        static_cast<int64_t>(phys - owner * bpr) * kBM * p.comm_row_bytes);
-      uint4* dst = reinterpret_cast<uint4*>(p.comm_local + static_cast<int64_t>(phys) * kBM * p.comm_row_bytes);
-      const int64_t stride = static_cast<int64_t>(gridDim.x) * 32;
-      int64_t i = static_cast<int64_t>(blockIdx.x) * 32 + lane;
-      for (; i + 7 * stride < vec_per_block; i += 8 * stride) {
-        uint4 v[8];
+    const int64_t vpb = (static_cast<int64_t>(kBM) * p.comm_row_bytes) >> 4;          // vectors per block
+    const int64_t total = static_cast<int64_t>(tiles_m - bpr) * vpb;
+    const int64_t lanes = static_cast<int64_t>(gridDim.x) * kCopierWarps * 32;
+    const int64_t me = (static_cast<int64_t>(blockIdx.x) * kCopierWarps + (warp - 6)) * 32 + lane;
+    for (int64_t base = 0; base < total; base += lanes * kRound) {
+      uint4 v[kRound];
+      int64_t g[kRound];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = ld_peer_v4(src + i + u * stride);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) dst[i + u * stride] = v[u];
+      for (int u = 0; u < kRound; ++u) {
+        g[u] = base + static_cast<int64_t>(u) * lanes + me;
+        if (g[u] < total) {
+          const int lb = static_cast<int>(g[u] / vpb);
+          const int phys = (lb + bpr + p.comm_rank * bpr) % tiles_m;
+          const int owner = phys / bpr;
+          const int64_t off = static_cast<int64_t>(phys - owner * bpr) * vpb + (g[u] - static_cast<int64_t>(lb) * vpb);
+          v[u] = ld_peer_v4(reinterpret_cast<const uint4*>(p.comm_peer[owner]) + off);
+        }
       }
-      for (; i < vec_per_block; i += stride) dst[i] = ld_peer_v4(src + i);
+#pragma unroll
+      for (int u = 0; u < kRound; ++u) {
+        if (g[u] < total) {
+          const int lb = static_cast<int>(g[u] / vpb);
+          const int phys = (lb + bpr + p.comm_rank * bpr) % tiles_m;
+          reinterpret_cast<uint4*>(p.comm_local)[static_cast<int64_t>(phys) * vpb + (g[u] - static_cast<int64_t>(lb) * vpb)] = v[u];
+        }
+      }
       __threadfence();
-      __syncwarp();
-      if (lane == 0) atomicAdd(p.comm_flags + phys, 1u);
+      // blocks touched by this round (identical for every lane of the grid)
+      const int lb_first = static_cast<int>(base / vpb);
+      const int64_t round_end = (base + lanes * kRound < total ? base + lanes * kRound : total) - 1;
+      const int lb_last = static_cast<int>(round_end / vpb);
+      for (int lb = lb_first; lb <= lb_last; ++lb) {
+        int mine = 0;
+#pragma unroll
+        for (int u = 0; u < kRound; ++u) mine += (g[u] < total && static_cast<int>(g[u] / vpb) == lb) ? 1 : 0;
+        const int cnt = __reduce_add_sync(0xFFFFFFFFu, mine);
+        if (lane == 0 && cnt > 0) atomicAdd(p.comm_flags + (lb + bpr + p.comm_rank * bpr) % tiles_m, static_cast<uint32_t>(cnt));
+      }
     }
   } else if (warp >= 6) {
     // no role (the kernel was launched with the all-gather block size without the all-gather mode)
@@ -334,39 +357,17 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      if (COMM == 2 && sizeof(OutT) == 2 && t.m_blk / p.comm_blocks_per_rank != p.comm_rank) {
-        // reduce-scatter push: this thread's row of the tile goes from registers into the owner's inbox,
-        // inbox[source = this rank][row inside the owner's shard][column]
+      // reduce-scatter push: tiles of rows that another rank owns leave through the staging buffer as 128-byte
+      // row segments written into the owner's inbox, inbox[source = this rank][row inside the owner's shard][column]
+      bool remote_tile = false;
+      uint8_t* remote_base = nullptr;
+      if (COMM == 2 && sizeof(OutT) == 2) {
         const int owner = t.m_blk / p.comm_blocks_per_rank;
+        remote_tile = owner != p.comm_rank;
         const int64_t rows_per_rank = static_cast<int64_t>(p.comm_blocks_per_rank) * kBM;
-        const int64_t in_row = static_cast<int64_t>(t.m_blk - owner * p.comm_blocks_per_rank) * kBM + row;
-        uint8_t* drow = static_cast<uint8_t*>(p.comm_peer[owner]) +
-                        (static_cast<int64_t>(p.comm_rank) * rows_per_rank + in_row) * p.comm_row_bytes;
-#pragma unroll 1
-        for (int c = 0; c < kChunks; ++c) {
-          const int col0 = t.c_x + c * 64;
-          if (col0 >= p.N) break;                           // N is a multiple of 64 in this mode
-          uint32_t v0[32], v1[32];
-          tmem_ld32(taddr + c * 64, v0);
-          tmem_ld32(taddr + c * 64 + 32, v1);
-          tc_wait_ld();
-          uint4* d4 = reinterpret_cast<uint4*>(drow + static_cast<int64_t>(col0) * 2);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            d4[j] = make_uint4(pack_bf16(__uint_as_float(v0[8 * j]), __uint_as_float(v0[8 * j + 1])),
-                               pack_bf16(__uint_as_float(v0[8 * j + 2]), __uint_as_float(v0[8 * j + 3])),
-                               pack_bf16(__uint_as_float(v0[8 * j + 4]), __uint_as_float(v0[8 * j + 5])),
-                               pack_bf16(__uint_as_float(v0[8 * j + 6]), __uint_as_float(v0[8 * j + 7])));
-            d4[4 + j] = make_uint4(pack_bf16(__uint_as_float(v1[8 * j]), __uint_as_float(v1[8 * j + 1])),
-                                   pack_bf16(__uint_as_float(v1[8 * j + 2]), __uint_as_float(v1[8 * j + 3])),
-                                   pack_bf16(__uint_as_float(v1[8 * j + 4]), __uint_as_float(v1[8 * j + 5])),
-                                   pack_bf16(__uint_as_float(v1[8 * j + 6]), __uint_as_float(v1[8 * j + 7])));
-          }
-        }
-        tc_fence_before_sync();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (issuer) mbar_arrive(&acc_empty[acc]);
-        continue;
+        const int64_t in_row0 = static_cast<int64_t>(t.m_blk - owner * p.comm_blocks_per_rank) * kBM;
+        remote_base = static_cast<uint8_t*>(p.comm_peer[owner]) +
+                      (static_cast<int64_t>(p.comm_rank) * rows_per_rank + in_row0) * p.comm_row_bytes;
       }
 #pragma unroll 1
       for (int c = 0; c < kChunks; ++c, ++chunk_it) {
@@ -408,7 +409,20 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
         }
         fence_proxy_async_smem();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (issuer) {
+        if (COMM == 2 && remote_tile) {
+          const int col0 = t.c_x + c * kColsPerChunk;
+          if (col0 < p.N) {
+            const int tid = threadIdx.x - 64;             // 0..127 over the epilogue warps
+            const int piece = tid & 7;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 16 + (tid >> 3);
+              const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((piece ^ (r & 7)) << 4));
+              *reinterpret_cast<uint4*>(remote_base + static_cast<int64_t>(r) * p.comm_row_bytes +
+                                        static_cast<int64_t>(col0) * 2 + (piece << 4)) = v;
+            }
+          }
+        } else if (issuer) {
           if (p.accumulate) {
             tma_reduce_add_2d(&p.tma_c, buf, t.c_x + c * kColsPerChunk, t.c_y);
           } else {

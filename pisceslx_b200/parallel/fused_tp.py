@@ -59,9 +59,12 @@ def allgather_gemm(x: torch.Tensor, w: torch.Tensor, group: Any, b_mn: bool = Fa
     n_out = w.shape[1] if b_mn else w.shape[0]
     dev = x.device
     nbytes = rows * kdim * 2
-    pub = heap.get("tp_ag_pub", nbytes)
+    # Two publication buffers used alternately: a peer may still read call i's buffer while call i+1 publishes into
+    # the other one, and the barrier of call i+1 (which every rank reaches after its kernel of call i) makes the
+    # first buffer free again for call i+2.  One barrier per call instead of two.
+    heap.tp_ag_calls = getattr(heap, "tp_ag_calls", 0) + 1
+    pub = heap.get(f"tp_ag_pub{heap.tp_ag_calls & 1}", nbytes)
     pub_t = pub.tensor(_BF16, rows * kdim).view(rows, kdim)
-    heap.barrier()                                   # peers finished reading my previous publication
     pub_t.copy_(x)
     heap.barrier()                                   # every shard is published
     xg = torch.empty(world * rows, kdim, dtype=_BF16, device=dev)
@@ -101,9 +104,10 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, group: Any, b_mn: bool
     n_out = w.shape[1] if b_mn else w.shape[0]
     dev = x.device
     nbytes = rows * n_out * 2
-    inbox = heap.get("tp_rs_inbox", world * nbytes)                 # [source][rows, N]
+    # two inboxes used alternately (same argument as for the all-gather publication buffers)
+    heap.tp_rs_calls = getattr(heap, "tp_rs_calls", 0) + 1
+    inbox = heap.get(f"tp_rs_inbox{heap.tp_rs_calls & 1}", world * nbytes)             # [source][rows, N]
     inbox_t = inbox.tensor(_BF16, world * rows * n_out).view(world, rows, n_out)
-    heap.barrier()                                                  # owners consumed their previous inbox
     if rows % 128 == 0 and n_out % 64 == 0 and rows * world == T and w.stride(-1) == 1:
         full = torch.empty(T, n_out, dtype=_BF16, device=dev)
         K.gemm_tp(x.contiguous(), w, full, 2, inbox.ptrs, None, rank, rows, b_mn, 0, status_word(dev))
