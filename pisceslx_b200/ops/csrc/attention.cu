@@ -1,6 +1,8 @@
 // Host launchers for the attention kernels: tensor-map construction, grid sizing, template dispatch.
 #include "attention_bwd.cuh"
 #include "attention_decode.cuh"
+#include "attention_decode_mma.cuh"
+#include "attention_decode_tma.cuh"
 #include "attention_fwd.cuh"
 #include "tensormap.h"
 #include "yv_ops.h"
@@ -132,6 +134,31 @@ int decode_dispatch(const PagedDecodeParams& p, int G, dim3 grid, cudaStream_t s
 }
 }  // namespace
 
+namespace {
+template <int D, int G>
+int decode_tma_launch(const PagedDecodeTmaParams& pp, dim3 grid, int smem, cudaStream_t stream) {
+  static int configured = 0;
+  if (configured < smem) {
+    int r = set_smem(paged_decode_tma_kernel<D, G>, smem);
+    if (r != 0) return r;
+    configured = smem;
+  }
+  paged_decode_tma_kernel<D, G><<<grid, 128, smem, stream>>>(pp);
+  return 0;
+}
+
+template <int D>
+int decode_tma_dispatch(const PagedDecodeTmaParams& pp, int G, dim3 grid, int smem, cudaStream_t stream) {
+  switch (G) {
+    case 1: return decode_tma_launch<D, 1>(pp, grid, smem, stream);
+    case 2: return decode_tma_launch<D, 2>(pp, grid, smem, stream);
+    case 4: return decode_tma_launch<D, 4>(pp, grid, smem, stream);
+    case 8: return decode_tma_launch<D, 8>(pp, grid, smem, stream);
+    default: return -4;
+  }
+}
+}  // namespace
+
 int launch_paged_decode(const PagedDecodeArgs& a, cudaStream_t stream) {
   if (a.batch <= 0) return 0;
   if (a.d != 64 && a.d != 128) return -1;
@@ -152,7 +179,55 @@ int launch_paged_decode(const PagedDecodeArgs& a, cudaStream_t stream) {
   p.status = a.status;
   dim3 grid(a.hk, a.batch, a.splits);
   const int G = a.hq / a.hk;
-  int r = (a.d == 128) ? decode_dispatch<128>(p, G, grid, stream) : decode_dispatch<64>(p, G, grid, stream);
+  int r;
+  // TMA-fed kernel: whole cache blocks of up to 128 tokens travel as one bulk copy each
+  const int64_t slots = static_cast<int64_t>(a.num_blocks) * a.block;
+  const bool use_tma = a.block >= 16 && a.block <= 128 && a.block % 16 == 0 && slots < (1ll << 31) && !a.force_direct;
+  const bool use_mma = use_tma && a.d == 128 && a.block == 64 && (G == 1 || G == 2 || G == 4 || G == 8);
+  if (use_mma) {
+    // tensor-core kernel: keys are the M dimension, the query heads of the group are padded to N = 16
+    PagedDecodeMmaParams pm;
+    pm.p = p;
+    r = make_tmap_3d(&pm.tma_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k_cache, 128, static_cast<uint64_t>(a.hk),
+                     static_cast<uint64_t>(slots), 256, static_cast<uint64_t>(a.hk) * 256, 64, 1, 64);
+    if (r != 0) return -40 + r;
+    r = make_tmap_3d(&pm.tma_v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.v_cache, 128, static_cast<uint64_t>(a.hk),
+                     static_cast<uint64_t>(slots), 256, static_cast<uint64_t>(a.hk) * 256, 64, 1, 64);
+    if (r != 0) return -50 + r;
+    static bool cfg = false;
+    if (!cfg) {
+      r = set_smem(paged_decode_mma_kernel<1>, kDmSmem); if (r) return r;
+      r = set_smem(paged_decode_mma_kernel<2>, kDmSmem); if (r) return r;
+      r = set_smem(paged_decode_mma_kernel<4>, kDmSmem); if (r) return r;
+      r = set_smem(paged_decode_mma_kernel<8>, kDmSmem); if (r) return r;
+      cfg = true;
+    }
+    switch (G) {
+      case 1: paged_decode_mma_kernel<1><<<grid, 128, kDmSmem, stream>>>(pm); break;
+      case 2: paged_decode_mma_kernel<2><<<grid, 128, kDmSmem, stream>>>(pm); break;
+      case 4: paged_decode_mma_kernel<4><<<grid, 128, kDmSmem, stream>>>(pm); break;
+      default: paged_decode_mma_kernel<8><<<grid, 128, kDmSmem, stream>>>(pm); break;
+    }
+    r = 0;
+  } else if (use_tma) {
+    PagedDecodeTmaParams pp;
+    pp.p = p;
+    r = make_tmap_3d(&pp.tma_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.k_cache, static_cast<uint64_t>(a.d),
+                     static_cast<uint64_t>(a.hk), static_cast<uint64_t>(slots), static_cast<uint64_t>(a.d) * 2,
+                     static_cast<uint64_t>(a.hk) * a.d * 2, static_cast<uint32_t>(a.d), 1,
+                     static_cast<uint32_t>(a.block), CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (r != 0) return -20 + r;
+    r = make_tmap_3d(&pp.tma_v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.v_cache, static_cast<uint64_t>(a.d),
+                     static_cast<uint64_t>(a.hk), static_cast<uint64_t>(slots), static_cast<uint64_t>(a.d) * 2,
+                     static_cast<uint64_t>(a.hk) * a.d * 2, static_cast<uint32_t>(a.d), 1,
+                     static_cast<uint32_t>(a.block), CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (r != 0) return -30 + r;
+    const int smem = kDecodeStages * 2 * a.block * a.d * 2 + 128;
+    r = (a.d == 128) ? decode_tma_dispatch<128>(pp, G, grid, smem, stream)
+                     : decode_tma_dispatch<64>(pp, G, grid, smem, stream);
+  } else {
+    r = (a.d == 128) ? decode_dispatch<128>(p, G, grid, stream) : decode_dispatch<64>(p, G, grid, stream);
+  }
   if (r != 0) return r;
   const int64_t heads_total = static_cast<int64_t>(a.batch) * a.hq;
   const unsigned mgrid = static_cast<unsigned>((heads_total + 3) / 4);

@@ -27,6 +27,58 @@ struct PagedDecodeParams {
   uint32_t* status;
 };
 
+// Merge of the 16 key groups of a CTA (each group holds a running max / sum / accumulator for its keys) into the
+// split's partial result in scratch.  Shared by the direct-load and the TMA-fed kernels; every thread of the CTA
+// calls it (it synchronises the CTA).
+template <int D, int G>
+__device__ __forceinline__ void decode_merge_groups(const PagedDecodeParams& p, const float (&m)[G], const float (&l)[G],
+                                                    const float (&acc)[G][D / 8], int b, int kvh, int split,
+                                                    float (*s_red_o)[G][D / 8 + 1], float (*s_m)[G], float (*s_l)[G]) {
+  constexpr int EPL = D / 8;
+  const int tid = threadIdx.x;
+  const int grp = tid >> 3, sub = tid & 7;
+  // merge the 16 key groups of the CTA
+  if (sub == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) { s_m[grp][g] = m[g]; s_l[grp][g] = l[g]; }
+  }
+  __syncthreads();
+  float mg[G], scale_me[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float mm = -1.0e29f;
+    for (int r = 0; r < 16; ++r) mm = fmaxf(mm, s_m[r][g]);
+    mg[g] = mm;
+    scale_me[g] = exp2f(m[g] - mm);
+  }
+  // each lane slice (sub) is reduced over groups through shared memory, one slice at a time
+  for (int s = 0; s < 8; ++s) {
+    if (sub == s) {
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) s_red_o[grp][g][e] = acc[g][e] * scale_me[g];
+    }
+    __syncthreads();
+    for (int i = tid; i < G * EPL; i += 128) {
+      const int g = i / EPL, e = i % EPL;
+      float t = 0.f;
+      for (int r = 0; r < 16; ++r) t += s_red_o[r][g][e];
+      const int64_t base = ((static_cast<int64_t>(b) * p.hq + kvh * G + g) * p.splits + split);
+      p.partial_o[base * D + s * EPL + e] = t;
+    }
+    __syncthreads();
+  }
+  if (tid < G) {
+    const int g = tid;
+    float lt = 0.f;
+    for (int r = 0; r < 16; ++r) lt += s_l[r][g] * exp2f(s_m[r][g] - mg[g]);
+    const int64_t base = ((static_cast<int64_t>(b) * p.hq + kvh * G + g) * p.splits + split);
+    p.partial_ml[base * 2] = mg[g];
+    p.partial_ml[base * 2 + 1] = lt;
+  }
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(128) paged_decode_kernel(const PagedDecodeParams p) {
   constexpr int EPL = D / 8;                       // elements per lane
@@ -109,46 +161,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const PagedDecodePara
     }
   }
 
-  // merge the 16 key groups of the CTA
-  if (sub == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) { s_m[grp][g] = m[g]; s_l[grp][g] = l[g]; }
-  }
-  __syncthreads();
-  float mg[G], scale_me[G];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float mm = -1.0e29f;
-    for (int r = 0; r < 16; ++r) mm = fmaxf(mm, s_m[r][g]);
-    mg[g] = mm;
-    scale_me[g] = exp2f(m[g] - mm);
-  }
-  // each lane slice (sub) is reduced over groups through shared memory, one slice at a time
-  for (int s = 0; s < 8; ++s) {
-    if (sub == s) {
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) s_red_o[grp][g][e] = acc[g][e] * scale_me[g];
-    }
-    __syncthreads();
-    for (int i = tid; i < G * EPL; i += 128) {
-      const int g = i / EPL, e = i % EPL;
-      float t = 0.f;
-      for (int r = 0; r < 16; ++r) t += s_red_o[r][g][e];
-      const int64_t base = ((static_cast<int64_t>(b) * p.hq + kvh * G + g) * p.splits + split);
-      p.partial_o[base * D + s * EPL + e] = t;
-    }
-    __syncthreads();
-  }
-  if (tid < G) {
-    const int g = tid;
-    float lt = 0.f;
-    for (int r = 0; r < 16; ++r) lt += s_l[r][g] * exp2f(s_m[r][g] - mg[g]);
-    const int64_t base = ((static_cast<int64_t>(b) * p.hq + kvh * G + g) * p.splits + split);
-    p.partial_ml[base * 2] = mg[g];
-    p.partial_ml[base * 2 + 1] = lt;
-  }
+  decode_merge_groups<D, G>(p, m, l, acc, b, kvh, split, s_red_o, s_m, s_l);
 }
 
 // merge splits: one warp per (sequence, query head)

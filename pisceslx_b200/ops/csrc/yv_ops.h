@@ -148,6 +148,7 @@ struct PagedDecodeArgs {
   int batch = 0, hq = 0, hk = 0, d = 0, block = 64, max_blocks_per_seq = 0, splits = 1, num_blocks = 0;
   float scale = 1.f;
   uint32_t* status = nullptr;
+  bool force_direct = false;       // true: the direct-load kernel (no TMA ring), whatever the block size
 };
 int launch_paged_decode(const PagedDecodeArgs& a, cudaStream_t stream);
 // k, v: [T, hk*d] rows with the given strides; caches: [num_slots, hk*d]; slot_map int32 [T] (-1 = skip)

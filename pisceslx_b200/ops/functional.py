@@ -327,8 +327,10 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         return ref.paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale)
     if splits <= 0:
         ctas = B * k_cache.shape[2]
-        splits = max(1, min(32, (2 * 148) // max(ctas, 1)))
-        splits = min(splits, max(1, block_table.shape[1]))
+        # one CTA per SM is resident: aim at four or more waves of CTAs so that the last, partial wave is a small
+        # share of the run, without cutting a sequence into pieces shorter than two 128-key tiles
+        splits = max(1, min(32, -(-(4 * 148) // max(ctas, 1))))
+        splits = min(splits, max(1, block_table.shape[1] // 4))
     o = torch.empty_like(q)
     po = torch.empty(B, hq, splits, d, dtype=torch.float32, device=q.device)
     pml = torch.empty(B, hq, splits, 2, dtype=torch.float32, device=q.device)

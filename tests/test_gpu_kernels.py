@@ -312,11 +312,13 @@ def test_cross_attention_unequal_lengths(status):
 
 @pytest.mark.parametrize("splits", [1, 4])
 @pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (4, 4, 64), (8, 1, 128)])
-def test_paged_decode(status, splits, hq, hk, d):
+@pytest.mark.parametrize("blk", [64, 24, 128])        # 64 / 128: TMA-fed ring; 24: direct-load kernel
+def test_paged_decode(status, splits, hq, hk, d, blk):
     from pisceslx_b200.ops import functional as F_, reference as ref
     torch.manual_seed(13)
     lens = [1, 63, 64, 200, 1000]
-    B, blk, nblocks, maxb = len(lens), 64, 96, 16
+    B, maxb = len(lens), (1000 + blk - 1) // blk + 1
+    nblocks = B * maxb + 5
     kc = torch.randn(nblocks, blk, hk, d, device=DEV, dtype=torch.bfloat16)
     vc = torch.randn_like(kc)
     bt = torch.randperm(nblocks)[: B * maxb].view(B, maxb).to(torch.int32).to(DEV)
