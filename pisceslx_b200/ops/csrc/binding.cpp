@@ -251,6 +251,34 @@ void add(const Tensor& a, const Tensor& b, Tensor out) {
   check_rc(yv::launch_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream()), "add");
 }
 
+// Split-K product for skinny activations: y[M,N] = a[M,K] @ b[N,K]^T (+ bias) with the K range cut into
+// seg_offsets.numel()-1 slices (offsets are multiples of 64), each reduced by its own CTAs into the fp32 workspace
+// ws [slices, ceil128(M), N]; a second kernel sums the slices in a fixed order (bit-reproducible).
+void gemm_splitk(const Tensor& a, const Tensor& b, Tensor ws, const Tensor& seg_offsets,
+                 const c10::optional<Tensor>& bias, Tensor out, const c10::optional<Tensor>& status) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_f32(ws, "ws"); check_i32(seg_offsets, "seg_offsets"); check_bf16(out, "out");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.is_contiguous() &&
+              ws.is_contiguous(), "gemm_splitk: a [M,K], b [N,K] with unit inner stride, contiguous ws and out");
+  const int slices = static_cast<int>(seg_offsets.numel()) - 1;
+  const int M = static_cast<int>(a.size(0)), K = static_cast<int>(a.size(1)), N = static_cast<int>(b.size(0));
+  const int m_pad = (M + 127) / 128 * 128;
+  TORCH_CHECK(slices >= 1 && b.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm_splitk: shape mismatch");
+  TORCH_CHECK(ws.numel() >= static_cast<int64_t>(slices) * m_pad * N, "gemm_splitk: workspace too small");
+  const c10::cuda::CUDAGuard guard(a.device());
+  yv::GemmArgs g;
+  g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = ws.data_ptr();
+  g.M = M; g.N = N; g.K = K;
+  g.lda = a.stride(0); g.ldb = b.stride(0); g.ldc = N;
+  g.out_fp32 = 1;
+  g.mode = 4;
+  g.num_groups = slices;
+  g.seg_offsets = seg_offsets.data_ptr<int>();
+  g.status = statusp(status);
+  check_rc(yv::launch_gemm(g, cur_stream()), "gemm_splitk");
+  check_rc(yv::launch_splitk_reduce(ws.data_ptr<float>(), bias.has_value() ? bias->data_ptr() : nullptr,
+                                    out.data_ptr(), slices, M, m_pad, N, cur_stream()), "splitk_reduce");
+}
+
 void l2_flush(Tensor buf) {
   check_cuda(buf, "buf");
   const c10::cuda::CUDAGuard guard(buf.device());

@@ -466,6 +466,40 @@ int launch_add(const void* a, const void* b, void* out, int64_t n, cudaStream_t 
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace {
+// out[m, n] = sum_s ws[s][m, n] (+ bias[n]); ws is fp32 [slices][m_pad, N]; four columns per thread
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, const __nv_bfloat16* __restrict__ bias,
+                                     __nv_bfloat16* __restrict__ out, int slices, int M, int m_pad, int N) {
+  const int64_t quads = static_cast<int64_t>(M) * (N >> 2);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < quads;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = i / (N >> 2);
+    const int n = static_cast<int>(i - m * (N >> 2)) << 2;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < slices; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + (static_cast<int64_t>(s) * m_pad + m) * N + n);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias != nullptr) {
+      acc.x += __bfloat162float(bias[n]); acc.y += __bfloat162float(bias[n + 1]);
+      acc.z += __bfloat162float(bias[n + 2]); acc.w += __bfloat162float(bias[n + 3]);
+    }
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(out + m * N + n);
+    o[0] = __floats2bfloat162_rn(acc.x, acc.y);
+    o[1] = __floats2bfloat162_rn(acc.z, acc.w);
+  }
+}
+}  // namespace
+
+int launch_splitk_reduce(const float* ws, const void* bias, void* out, int slices, int M, int m_pad, int N,
+                         cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((N & 3) != 0 || slices <= 0 || m_pad < M) return -1;
+  splitk_reduce_kernel<<<grid_for(static_cast<int64_t>(M) * (N >> 2), 256), 256, 0, stream>>>(
+      ws, YV_BF(bias), YV_BFM(out), slices, M, m_pad, N);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int launch_l2_flush(void* buf, int64_t bytes, cudaStream_t stream) {
   l2_flush_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<uint4*>(buf), bytes / 16);
   return static_cast<int>(cudaGetLastError());

@@ -102,6 +102,18 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     b_inner = a.N;  b_outer = a.rows_total;
     p.c_group_stride = a.M;
     c_outer = groups * static_cast<uint64_t>(a.M);
+  } else if (a.mode == 4) {
+    // split-K of a dense product with both operands stored K-inner (activations [M,K], weights [N,K]): slice g
+    // reduces over K range seg_offsets[g] .. seg_offsets[g+1] and writes its partial to rows g*Mpad.. of C, where
+    // Mpad = M rounded up to 128.  Runs the grouped-K tile loop; used for skinny M (decode), where the N tiles alone
+    // would occupy a fraction of the SMs.
+    if (a.a_mn || a.b_mn || a.seg_offsets == nullptr || a.accumulate) return -60;
+    const int m_pad = ((a.M + kBM - 1) / kBM) * kBM;
+    p.mode = kGroupedK;
+    a_inner = a.K;  a_outer = a.M;
+    b_inner = a.K;  b_outer = a.N;
+    p.c_group_stride = m_pad;
+    c_outer = groups * static_cast<uint64_t>(m_pad);
   } else if (a.mode == kBatched) {
     // every operand stacks `num_groups` equal problems along its outer dimension
     if (a.M % kBM != 0) return -18;                       // C / A row tiles must not cross batch entries
@@ -153,7 +165,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
 
   const int64_t tiles_m = (p.M + kBM - 1) / kBM;
   const int64_t tiles_n = (a.N + bn - 1) / bn;
-  int64_t tiles = tiles_m * tiles_n * ((a.mode == kGroupedK || a.mode == kBatched) ? a.num_groups : 1);
+  int64_t tiles = tiles_m * tiles_n * ((p.mode == kGroupedK || p.mode == kBatched) ? a.num_groups : 1);
   const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
 

@@ -75,6 +75,9 @@ int launch_film(const void* x, const void* scale, const void* shift, void* y, in
                 int64_t rows_per_group, cudaStream_t stream);
 int launch_add(const void* a, const void* b, void* out, int64_t n, cudaStream_t stream);
 int launch_l2_flush(void* buf, int64_t bytes, cudaStream_t stream);
+// out[M,N] (bf16) = sum over slices of ws[slice][m_pad, N] (fp32) (+ bias[N]): second half of a split-K product
+int launch_splitk_reduce(const float* ws, const void* bias, void* out, int slices, int M, int m_pad, int N,
+                         cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // MoE routing (moe.cu)

@@ -45,6 +45,49 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+_SPLITK_OFFSETS: dict = {}
+_SPLITK_WS: dict = {}
+
+
+def _splitk_plan(M: int, N: int, K: int) -> int:
+    """Number of K slices for a skinny product (0 = do not split).  With at most 128 rows the N tiles alone cover
+    a fraction of the 148 SMs and the weight matrix streams at a fraction of HBM bandwidth; slicing K multiplies
+    the CTAs that pull weight bytes.  The choice depends on (N, K) only, so a row's result does not depend on how
+    many other rows share the launch."""
+    if M > 128 or K % 64 != 0 or N % 4 != 0:
+        return 0
+    tiles_n = (N + 255) // 256
+    if tiles_n >= 74:
+        return 0
+    want = min(16, -(-148 // tiles_n))
+    slices = max(1, min(want, K // 256))
+    return slices if slices > 1 else 0
+
+
+def gemm_skinny(x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """y = x2 @ w.T through the split-K path, or None when the shape does not call for it."""
+    M, K = x2.shape
+    N = w.shape[0]
+    slices = _splitk_plan(M, N, K)
+    if slices == 0 or w.stride(1) != 1 or x2.stride(1) != 1:
+        return None
+    dev = x2.device
+    key = (dev.index, K, slices)
+    offs = _SPLITK_OFFSETS.get(key)
+    if offs is None:
+        per = -(-(K // 64) // slices) * 64
+        offs = torch.tensor([min(K, i * per) for i in range(slices + 1)], dtype=torch.int32, device=dev)
+        _SPLITK_OFFSETS[key] = offs
+    need = slices * 128 * N
+    ws = _SPLITK_WS.get(dev.index)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 16 * 128 * 8192), dtype=torch.float32, device=dev)
+        _SPLITK_WS[dev.index] = ws
+    out = torch.empty(M, N, dtype=_BF16, device=dev)
+    _k().gemm_splitk(x2, w, ws, offs, bias, out, _st(x2))
+    return out
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, out_fp32):
@@ -53,6 +96,10 @@ class _LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
+        if not out_fp32 and x2.shape[0] <= 128:
+            ys = gemm_skinny(x2, w)
+            if ys is not None:
+                return ys.view(*x.shape[:-1], w.shape[0])
         y = gemm(x2, w, out_dtype=torch.float32 if out_fp32 else _BF16)
         return y.view(*x.shape[:-1], w.shape[0])
 

@@ -66,3 +66,19 @@ def test_gemm_reduce_scatter_push_single_kernel(world, rank, b_mn):
         others = [s for s in range(world) if s != rank]
         assert all(float(inboxes[owner][s].abs().max()) == 0.0 for s in others)
         assert torch.isnan(full[owner * rows:(owner + 1) * rows].float()).all()   # remote rows are not stored locally
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 6144, 4096), (64, 4096, 5632), (100, 1408, 4096), (128, 4096, 4096)])
+def test_split_k_skinny_linear_matches_reference_and_is_batch_invariant(M, N, K):
+    from pisceslx_b200.ops import check_status, functional as F_
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.02
+    assert F_._splitk_plan(M, N, K) > 1
+    y = F_.linear(x, w)
+    torch.cuda.synchronize()
+    check_status()
+    assert _rel(y, x.float() @ w.float().t()) < 4e-3
+    assert torch.equal(y, F_.linear(x, w))                      # fixed summation order
+    assert torch.equal(F_.linear(x[:1], w), y[:1])              # a row does not depend on its neighbours
+    assert F_._splitk_plan(4096, N, K) == 0 and F_._splitk_plan(64, 154856, 4096) == 0
