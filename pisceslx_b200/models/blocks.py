@@ -75,6 +75,17 @@ class YvTransformerBlock(nn.Module):
         else:
             self.mlp = YvSwiGLUExpert(cfg.hidden_size, cfg.intermediate_size, cfg.initializer_range, None, tp, tpg)
         self.use_recompute = cfg.use_gradient_checkpointing
+        # hybrid backbone (reference default, model/core/hybrid.py:1170-1370): a sparse-gated selective SSM beside the
+        # attention branch, fused by a learned per-channel gate
+        self.ssm = self.fusion = None
+        if cfg.use_mamba3 and not cfg.backbone_allow_legacy_blocks:
+            from .ssm import YvSelectiveSSM, YvUnifiedFusion
+            assert tp == 1, "the SSM branch is not tensor-parallel"
+            ex = cfg.extra
+            self.ssm = YvSelectiveSSM(cfg.hidden_size, int(ex.get("mamba_state_dim", 16)),
+                                      int(ex.get("mamba_expand", 2)), init_std=cfg.initializer_range)
+            self.fusion = YvUnifiedFusion(cfg.hidden_size)
+            self.sparse_gate_ssm = nn.Parameter(torch.zeros(()))
 
     def _body(self, recomputing: bool, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: AttnContext,
               film: Optional[Dict[str, torch.Tensor]]):
@@ -89,6 +100,11 @@ class YvTransformerBlock(nn.Module):
         else:
             n1, h = self.norm_attention(delta, residual=h)
         a = self.attention(n1, ctx)
+        if self.ssm is not None and not ctx.decode:
+            T, H = n1.shape
+            assert T % ctx.max_len == 0, "the SSM branch needs equal-length sequences"
+            s_out = self.ssm(n1.view(T // ctx.max_len, ctx.max_len, H)).reshape(T, H)
+            a = self.fusion(a, torch.sigmoid(self.sparse_gate_ssm).to(a.dtype) * s_out, n1)
         n2, h = self.norm_mlp(a, residual=h)
         if self.is_moe:
             m, aux = self.mlp(n2)
@@ -126,10 +142,23 @@ class YvTransformerBlock(nn.Module):
         out[prefix + "norm_mlp.weight"] = self.norm_mlp.weight.detach().clone()
         self.attention.export_state(prefix + "attention.", out)
         self.mlp.export_state(prefix + "mlp.", out)
+        if self.ssm is not None:
+            for n, p in self.ssm.named_parameters():
+                out[prefix + "ssm." + n] = p.detach().clone()
+            for n, p in self.fusion.named_parameters():
+                out[prefix + "fusion." + n] = p.detach().clone()
+            out[prefix + "sparse_gate_ssm"] = self.sparse_gate_ssm.detach().clone()
 
     def import_state(self, prefix: str, sd: Dict[str, torch.Tensor]) -> None:
         with torch.no_grad():
             self.norm_attention.weight.copy_(sd[prefix + "norm_attention.weight"])
             self.norm_mlp.weight.copy_(sd[prefix + "norm_mlp.weight"])
         self.attention.import_state(prefix + "attention.", sd)
+        if self.ssm is not None and prefix + "sparse_gate_ssm" in sd:
+            with torch.no_grad():
+                for n, p in self.ssm.named_parameters():
+                    p.copy_(sd[prefix + "ssm." + n])
+                for n, p in self.fusion.named_parameters():
+                    p.copy_(sd[prefix + "fusion." + n])
+                self.sparse_gate_ssm.copy_(sd[prefix + "sparse_gate_ssm"])
         self.mlp.import_state(prefix + "mlp.", sd)

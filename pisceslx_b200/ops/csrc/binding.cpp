@@ -279,6 +279,37 @@ void gemm_splitk(const Tensor& a, const Tensor& b, Tensor ws, const Tensor& seg_
                                     out.data_ptr(), slices, M, m_pad, N, cur_stream()), "splitk_reduce");
 }
 
+void ssm_scan_fwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
+                  const Tensor& Dp, Tensor y, const c10::optional<Tensor>& hs, const c10::optional<Tensor>& h_last) {
+  check_f32(u, "u"); check_f32(delta, "delta"); check_f32(A, "A"); check_f32(Bm, "B"); check_f32(Cm, "C");
+  check_f32(Dp, "D"); check_f32(y, "y");
+  TORCH_CHECK(u.dim() == 3 && u.is_contiguous() && delta.is_contiguous() && Bm.is_contiguous() && Cm.is_contiguous() &&
+              A.is_contiguous() && y.is_contiguous(), "ssm_scan_fwd: contiguous [B,L,D] / [B,L,N] / [D,N] tensors");
+  const c10::cuda::CUDAGuard guard(u.device());
+  check_rc(yv::launch_ssm_scan_fwd(u.data_ptr<float>(), delta.data_ptr<float>(), A.data_ptr<float>(),
+                                   Bm.data_ptr<float>(), Cm.data_ptr<float>(), Dp.data_ptr<float>(), y.data_ptr<float>(),
+                                   hs.has_value() ? hs->data_ptr<float>() : nullptr,
+                                   h_last.has_value() ? h_last->data_ptr<float>() : nullptr,
+                                   static_cast<int>(u.size(0)), static_cast<int>(u.size(1)), static_cast<int>(u.size(2)),
+                                   static_cast<int>(A.size(1)), cur_stream()), "ssm_scan_fwd");
+}
+
+void ssm_scan_bwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
+                  const Tensor& Dp, const Tensor& hs, const Tensor& dy, Tensor du, Tensor ddelta, Tensor dA, Tensor dB,
+                  Tensor dC, Tensor dD) {
+  check_f32(u, "u"); check_f32(hs, "hs"); check_f32(dy, "dy"); check_f32(du, "du"); check_f32(ddelta, "ddelta");
+  check_f32(dA, "dA"); check_f32(dB, "dB"); check_f32(dC, "dC"); check_f32(dD, "dD");
+  TORCH_CHECK(u.is_contiguous() && delta.is_contiguous() && hs.is_contiguous() && dy.is_contiguous() &&
+              du.is_contiguous() && ddelta.is_contiguous(), "ssm_scan_bwd: contiguous tensors expected");
+  const c10::cuda::CUDAGuard guard(u.device());
+  check_rc(yv::launch_ssm_scan_bwd(u.data_ptr<float>(), delta.data_ptr<float>(), A.data_ptr<float>(),
+                                   Bm.data_ptr<float>(), Cm.data_ptr<float>(), Dp.data_ptr<float>(), hs.data_ptr<float>(),
+                                   dy.data_ptr<float>(), du.data_ptr<float>(), ddelta.data_ptr<float>(),
+                                   dA.data_ptr<float>(), dB.data_ptr<float>(), dC.data_ptr<float>(), dD.data_ptr<float>(),
+                                   static_cast<int>(u.size(0)), static_cast<int>(u.size(1)), static_cast<int>(u.size(2)),
+                                   static_cast<int>(A.size(1)), cur_stream()), "ssm_scan_bwd");
+}
+
 void l2_flush(Tensor buf) {
   check_cuda(buf, "buf");
   const c10::cuda::CUDAGuard guard(buf.device());

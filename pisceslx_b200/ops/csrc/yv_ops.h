@@ -75,6 +75,19 @@ int launch_film(const void* x, const void* scale, const void* shift, void* y, in
                 int64_t rows_per_group, cudaStream_t stream);
 int launch_add(const void* a, const void* b, void* out, int64_t n, cudaStream_t stream);
 int launch_l2_flush(void* buf, int64_t bytes, cudaStream_t stream);
+
+// ------------------------------------------------------------------------------------------------
+// Selective state-space scan (ssm.cu): fp32 u, delta, y [B, L, D]; A [D, 16]; Bm, Cm [B, L, 16]; Dp [D].
+// hs (optional) receives every state [B, L, D, 16] for the backward; h_last (optional, [B, D, 16]) is the initial
+// state on entry and the final state on exit (decode carries it from step to step).
+// ------------------------------------------------------------------------------------------------
+int launch_ssm_scan_fwd(const float* u, const float* delta, const float* A, const float* Bm, const float* Cm,
+                        const float* Dp, float* y, float* hs, float* h_last, int batch, int L, int D, int N,
+                        cudaStream_t stream);
+// dA [D,16], dB, dC [B,L,16] and dD [D] are accumulated into (zero them first); du, ddelta are written
+int launch_ssm_scan_bwd(const float* u, const float* delta, const float* A, const float* Bm, const float* Cm,
+                        const float* Dp, const float* hs, const float* dy, float* du, float* ddelta, float* dA,
+                        float* dB, float* dC, float* dD, int batch, int L, int D, int N, cudaStream_t stream);
 // out[M,N] (bf16) = sum over slices of ws[slice][m_pad, N] (fp32) (+ bias[N]): second half of a split-K product
 int launch_splitk_reduce(const float* ws, const void* bias, void* out, int slices, int M, int m_pad, int N,
                          cudaStream_t stream);
