@@ -116,6 +116,34 @@ def bench_decode(a: argparse.Namespace) -> Dict[str, Any]:
             "frac_of_peak": gbs / peaks()["hbm_gbs"]}
 
 
+def bench_gemm_fp8(a: argparse.Namespace) -> Dict[str, Any]:
+    """e4m3 x e4m3 GEMM (tcgen05 kind::f8f6f4) with per-tensor scales; the fraction is of the bf16 peak."""
+    K, st = kernels(), status_word(torch.device("cuda"))
+    M, N, Kd = a.m, a.n, a.k
+    A = torch.randn(M, Kd, device="cuda").to(torch.float8_e4m3fn)
+    B = torch.randn(N, Kd, device="cuda").to(torch.float8_e4m3fn)
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    sc = torch.ones(1, device="cuda")
+    ms = timeit(lambda: K.gemm_fp8(A, B, C, sc, a.bn, st), a.iters)
+    tf = 2.0 * M * N * Kd / ms / 1e9
+    return {"kernel": "gemm_sm100_fp8", "shape": [M, N, Kd], "ms": ms, "tflops": tf,
+            "frac_of_bf16_peak": tf / peaks()["bf16_tflops"]}
+
+
+def bench_ssm(a: argparse.Namespace) -> Dict[str, Any]:
+    """Selective scan forward (batch x seq x d_inner = --batch x --seq x --n, 16 states), bytes = u, delta, y."""
+    K = kernels()
+    B, L, D = a.batch, a.seq, a.n
+    u = torch.randn(B, L, D, device="cuda")
+    dl = torch.rand(B, L, D, device="cuda") * 0.1
+    A = -torch.rand(D, 16, device="cuda")
+    Bm, Cm, Dp = torch.randn(B, L, 16, device="cuda"), torch.randn(B, L, 16, device="cuda"), torch.ones(D, device="cuda")
+    y = torch.empty_like(u)
+    ms = timeit(lambda: K.ssm_scan_fwd(u, dl, A, Bm, Cm, Dp, y, None, None), a.iters)
+    return {"kernel": "ssm_scan_fwd", "shape": [B, L, D, 16], "ms": ms, "gbs": 3.0 * u.numel() * 4 / ms / 1e6,
+            "state_updates_per_s": B * L * D * 16 / ms * 1e3}
+
+
 def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
     """Batched Newton-Schulz on [batch, m, n] (the Muon orthogonalisation of a stack of expert matrices), plus the
     three batched GEMMs of one iteration timed separately."""
@@ -145,7 +173,7 @@ def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="gemm", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns"])
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm"])
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -170,9 +198,16 @@ def main() -> None:
         res.append(bench_rmsnorm(a))
         a.batch, a.seq = 64, 4096
         res.append(bench_decode(a))
+        a.m, a.n, a.k = 8192, 8192, 8192
+        res.append(bench_gemm_fp8(a))
+        a.batch, a.seq, a.n = 2, 4096, 8192
+        res.append(bench_ssm(a))
+        a.batch, a.m, a.n = 128, 1408, 4096
+        res.append(bench_newton_schulz(a))
     else:
         fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
-              "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz}[a.kernel]
+              "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz, "gemm_fp8": bench_gemm_fp8,
+              "ssm": bench_ssm}[a.kernel]
         res.append(fn(a))
     out = {"peaks": peaks(), "results": res}
     print(json.dumps(out, indent=1))

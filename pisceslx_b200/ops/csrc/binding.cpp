@@ -279,6 +279,40 @@ void gemm_splitk(const Tensor& a, const Tensor& b, Tensor ws, const Tensor& seg_
                                     out.data_ptr(), slices, M, m_pad, N, cur_stream()), "splitk_reduce");
 }
 
+inline void check_fp8(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && (t.scalar_type() == at::kFloat8_e4m3fn || t.scalar_type() == at::kByte), name,
+              " must be a CUDA float8_e4m3fn (or uint8) tensor");
+}
+
+// q = saturate_e4m3(x * scale[0]); amax[0] = max(amax[0], max|x|)
+void fp8_quantize(const Tensor& x, const Tensor& scale, Tensor q, const c10::optional<Tensor>& amax) {
+  check_bf16(x, "x"); check_f32(scale, "scale"); check_fp8(q, "q");
+  TORCH_CHECK(x.is_contiguous() && q.is_contiguous() && q.numel() == x.numel(), "fp8_quantize: contiguous, same size");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check_rc(yv::launch_fp8_quantize(x.data_ptr(), scale.data_ptr<float>(), q.data_ptr(),
+                                   amax.has_value() ? amax->data_ptr<float>() : nullptr, x.numel(), cur_stream()),
+           "fp8_quantize");
+}
+
+// c[M,N] (bf16) = (a_q[M,K] @ b_q[N,K]^T) * out_scale[0], e4m3 operands, fp32 accumulation in TMEM
+void gemm_fp8(const Tensor& a, const Tensor& b, Tensor c, const Tensor& out_scale, int64_t bn,
+              const c10::optional<Tensor>& status) {
+  check_fp8(a, "a"); check_fp8(b, "b"); check_bf16(c, "c"); check_f32(out_scale, "out_scale");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() && c.is_contiguous() &&
+              a.size(1) == b.size(1) && c.size(0) == a.size(0) && c.size(1) == b.size(0),
+              "gemm_fp8: a [M,K], b [N,K], c [M,N] contiguous");
+  TORCH_CHECK(a.size(1) % 16 == 0, "gemm_fp8: K must be a multiple of 16");
+  const c10::cuda::CUDAGuard guard(a.device());
+  yv::GemmArgs g;
+  g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = c.data_ptr();
+  g.M = static_cast<int>(a.size(0)); g.K = static_cast<int>(a.size(1)); g.N = static_cast<int>(b.size(0));
+  g.fp8 = true;
+  g.out_scale = out_scale.data_ptr<float>();
+  g.bn = static_cast<int>(bn);
+  g.status = statusp(status);
+  check_rc(yv::launch_gemm(g, cur_stream()), "gemm_fp8");
+}
+
 void ssm_scan_fwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
                   const Tensor& Dp, Tensor y, const c10::optional<Tensor>& hs, const c10::optional<Tensor>& h_last) {
   check_f32(u, "u"); check_f32(delta, "delta"); check_f32(A, "A"); check_f32(Bm, "B"); check_f32(Cm, "C");

@@ -500,6 +500,45 @@ int launch_splitk_reduce(const float* ws, const void* bias, void* out, int slice
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace {
+// eight bf16 values per thread -> eight e4m3 bytes; |x| maximum reduced per warp, one atomic per warp
+__global__ void fp8_quantize_kernel(const uint4* __restrict__ x, const float* __restrict__ scale,
+                                    uint2* __restrict__ q, float* __restrict__ amax, int64_t n8) {
+  const float sc = *scale;
+  float mx = 0.f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = x[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint32_t out[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const float2 a = __bfloat1622float2(h[2 * k]), b = __bfloat1622float2(h[2 * k + 1]);
+      mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
+      uint16_t lo, hi;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(a.y * sc), "f"(a.x * sc));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(b.y * sc), "f"(b.x * sc));
+      out[k] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+    }
+    q[i] = make_uint2(out[0], out[1]);
+  }
+  if (amax != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(mx));   // mx >= 0
+  }
+}
+}  // namespace
+
+int launch_fp8_quantize(const void* x_bf16, const float* scale, void* q_e4m3, float* amax, int64_t n,
+                        cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((n & 7) != 0) return -1;
+  fp8_quantize_kernel<<<grid_for(n >> 3, 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(x_bf16), scale,
+                                                                 reinterpret_cast<uint2*>(q_e4m3), amax, n >> 3);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int launch_l2_flush(void* buf, int64_t bytes, cudaStream_t stream) {
   l2_flush_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<uint4*>(buf), bytes / 16);
   return static_cast<int>(cudaGetLastError());

@@ -20,9 +20,9 @@ int sm_count() {
   return g_sm_count;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0>
+template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, bool FP8 = false>
 int launch_instance(const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT, COMM>;
+  auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT, COMM, FP8>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
@@ -132,12 +132,23 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   const uint64_t ldc = a.ldc ? a.ldc : static_cast<uint64_t>(a.N);
 
   int r;
-  r = make_tmap_2d(&p.tma_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.a, a_inner, a_outer, lda, 64,
-                   a.a_mn ? kBK : kBM);
-  if (r != 0) return -20 + r;
-  r = make_tmap_2d(&p.tma_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.b, b_inner, b_outer, ldb, 64,
-                   a.b_mn ? kBK : static_cast<uint32_t>(bn));
-  if (r != 0) return -30 + r;
+  p.out_scale = a.out_scale;
+  if (a.fp8) {
+    // e4m3 operands: one byte per element, 128 elements per 128-byte row of a stage
+    if (a.mode != kDense || a.a_mn || a.b_mn || a.out_fp32 || a.accumulate || a.comm != 0) return -70;
+    r = make_tmap_2d(&p.tma_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.a, a_inner, a_outer, lda, 128, kBM);
+    if (r != 0) return -20 + r;
+    r = make_tmap_2d(&p.tma_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.b, b_inner, b_outer, ldb, 128,
+                     static_cast<uint32_t>(bn));
+    if (r != 0) return -30 + r;
+  } else {
+    r = make_tmap_2d(&p.tma_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.a, a_inner, a_outer, lda, 64,
+                     a.a_mn ? kBK : kBM);
+    if (r != 0) return -20 + r;
+    r = make_tmap_2d(&p.tma_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.b, b_inner, b_outer, ldb, 64,
+                     a.b_mn ? kBK : static_cast<uint32_t>(bn));
+    if (r != 0) return -30 + r;
+  }
   r = make_tmap_2d(&p.tma_c, a.out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                    out_bytes, a.c, static_cast<uint64_t>(a.N), c_outer, ldc, 128 / out_bytes, kBM);
   if (r != 0) return -40 + r;
@@ -169,6 +180,10 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
 
+  if (a.fp8) {
+    return bn == 256 ? launch_instance<256, false, false, __nv_bfloat16, 0, true>(p, grid, stream)
+                     : launch_instance<128, false, false, __nv_bfloat16, 0, true>(p, grid, stream);
+  }
   if (a.comm == 1) {
     cudaError_t e = cudaMemsetAsync(a.comm_flags, 0, sizeof(uint32_t) * static_cast<size_t>(tiles_m), stream);
     if (e != cudaSuccess) return static_cast<int>(e);

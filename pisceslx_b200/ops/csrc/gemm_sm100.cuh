@@ -52,6 +52,9 @@ struct GemmParams {
   uint32_t* comm_flags;        // COMM 1: one counter per 128-row block, zeroed before the launch
   uint32_t comm_flag_target;   // COMM 1: count that marks a block complete (= 16-byte vectors per block)
   long long comm_row_bytes;    // COMM 1: bytes per row of A; COMM 2: bytes per row of an inbox
+  // ---- fp8 inputs (template parameter FP8): e4m3 operands, K-major, 128 elements per shared-memory row; the
+  // epilogue multiplies the fp32 accumulator by *out_scale (= scale_a * scale_b of per-tensor scaling) ----
+  const float* out_scale;
 };
 
 constexpr int kBM = 128;
@@ -82,7 +85,7 @@ struct TileCoord {
 };
 
 // Decode linear tile index -> coordinates.  Returns false when idx is past the end.
-template <int BN, bool A_MN, bool B_MN, int COMM = 0>
+template <int BN, bool A_MN, bool B_MN, int COMM = 0, bool FP8 = false>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int tiles_m, int tiles_n, TileCoord& t) {
   int m_blk, n_blk, group = 0;
   if (p.mode == kGroupedK || p.mode == kBatched) {
@@ -123,7 +126,8 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
     k_len = p.seg_offsets[group + 1] - k_begin;
     c_row_off = group * p.c_group_stride;
   }
-  t.k_iters = (k_len + kBK - 1) / kBK;
+  constexpr int kBKe = FP8 ? 2 * kBK : kBK;          // elements of K per pipeline stage (128 bytes per row)
+  t.k_iters = (k_len + kBKe - 1) / kBKe;
   if (A_MN) { t.a_x = m0; t.a_y = a_outer_off + k_begin; } else { t.a_x = k_begin; t.a_y = a_outer_off + m0; }
   if (B_MN) { t.b_x = n0; t.b_y = b_outer_off + k_begin; } else { t.b_x = k_begin; t.b_y = b_outer_off + n0; }
   t.c_x = n0;
@@ -132,14 +136,16 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0>
+template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, bool FP8 = false>
 __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   constexpr int kColsPerChunk = 128 / sizeof(OutT);       // columns covered by one 128-byte staging row
   constexpr int kChunks = BN / kColsPerChunk;
   constexpr uint32_t kTmemCols = (2 * BN <= 512) ? 2 * BN : 512;
-  constexpr uint32_t kIdesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+  static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
+  constexpr int kBKe = FP8 ? 2 * kBK : kBK;
+  constexpr uint32_t kIdesc = FP8 ? make_idesc_e4m3(kBM, BN) : make_idesc_bf16(kBM, BN, A_MN, B_MN);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -192,7 +198,7 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
       bool ok = true;
       for (int idx = blockIdx.x; ok; idx += gridDim.x) {
         TileCoord t;
-        if (!decode_tile<BN, A_MN, B_MN, COMM>(p, idx, tiles_m, tiles_n, t)) break;
+        if (!decode_tile<BN, A_MN, B_MN, COMM, FP8>(p, idx, tiles_m, tiles_n, t)) break;
         if (COMM == 1 && t.m_blk / p.comm_blocks_per_rank != p.comm_rank) {
           // rows of another rank: the copier warps of all CTAs must have landed this block in local memory
           const volatile uint32_t* flag = p.comm_flags + t.m_blk;
@@ -224,14 +230,14 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
             for (int j = 0; j < kBM / 64; ++j)
               tma_load_2d(sa + j * (kBK * 128), &p.tma_a, &full_bar[s], t.a_x + j * 64, t.a_y + k * kBK);
           } else {
-            tma_load_2d(sa, &p.tma_a, &full_bar[s], t.a_x + k * kBK, t.a_y);
+            tma_load_2d(sa, &p.tma_a, &full_bar[s], t.a_x + k * kBKe, t.a_y);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(sb + j * (kBK * 128), &p.tma_b, &full_bar[s], t.b_x + j * 64, t.b_y + k * kBK);
           } else {
-            tma_load_2d(sb, &p.tma_b, &full_bar[s], t.b_x + k * kBK, t.b_y);
+            tma_load_2d(sb, &p.tma_b, &full_bar[s], t.b_x + k * kBKe, t.b_y);
           }
         }
       }
@@ -243,7 +249,7 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
       bool ok = true;
       for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
         TileCoord t;
-        if (!decode_tile<BN, A_MN, B_MN, COMM>(p, idx, tiles_m, tiles_n, t)) break;
+        if (!decode_tile<BN, A_MN, B_MN, COMM, FP8>(p, idx, tiles_m, tiles_n, t)) break;
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1u;
         ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1u, p.status);
@@ -264,7 +270,11 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, kBK * 128, 1024)
                                      : make_smem_desc(sb + kk * 32, 16, 1024);
-            tc_mma_f16_ss(tmem_d, da, db, kIdesc, (k | kk) != 0 ? 1u : 0u);
+            if (FP8) {
+              tc_mma_f8_ss(tmem_d, da, db, kIdesc, (k | kk) != 0 ? 1u : 0u);
+            } else {
+              tc_mma_f16_ss(tmem_d, da, db, kIdesc, (k | kk) != 0 ? 1u : 0u);
+            }
           }
           tc_commit(&empty_bar[s]);     // releases the stage once these MMAs have read it
         }
@@ -335,7 +345,7 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
     bool ok = true;
     for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
       TileCoord t;
-      if (!decode_tile<BN, A_MN, B_MN, COMM>(p, idx, tiles_m, tiles_n, t)) break;
+      if (!decode_tile<BN, A_MN, B_MN, COMM, FP8>(p, idx, tiles_m, tiles_n, t)) break;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1u;
       ok = mbar_wait(&acc_full[acc], acc_ph, p.status);
@@ -386,10 +396,11 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
 #pragma unroll
             for (int i = 0; i < 32; ++i) { v0[i] = 0u; v1[i] = 0u; }
           }
+          const float osc = (FP8 && p.out_scale != nullptr) ? *p.out_scale : 1.f;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            packed[i] = pack_bf16(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
-            packed[16 + i] = pack_bf16(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
+            packed[i] = pack_bf16(__uint_as_float(v0[2 * i]) * osc, __uint_as_float(v0[2 * i + 1]) * osc);
+            packed[16 + i] = pack_bf16(__uint_as_float(v1[2 * i]) * osc, __uint_as_float(v1[2 * i + 1]) * osc);
           }
         } else {
           if (t.k_iters > 0) {

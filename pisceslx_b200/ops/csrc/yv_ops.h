@@ -41,6 +41,9 @@ struct GemmArgs {
   int64_t comm_rows_per_rank = 0;
   void* comm_peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   uint32_t* comm_flags = nullptr;
+  // fp8 (e4m3) operands, both stored K-inner, bf16 output scaled by *out_scale in the epilogue (dense mode only)
+  bool fp8 = false;
+  const float* out_scale = nullptr;
 };
 // Returns 0 on success, a negative code when an argument is rejected, a positive cudaError_t otherwise.
 int launch_gemm(const GemmArgs& args, cudaStream_t stream);
@@ -75,6 +78,10 @@ int launch_film(const void* x, const void* scale, const void* shift, void* y, in
                 int64_t rows_per_group, cudaStream_t stream);
 int launch_add(const void* a, const void* b, void* out, int64_t n, cudaStream_t stream);
 int launch_l2_flush(void* buf, int64_t bytes, cudaStream_t stream);
+// Per-tensor fp8 (e4m3) quantisation for delayed scaling: q = saturate(x * *scale), and the tensor's own absolute
+// maximum is folded into *amax (atomic max; the caller turns it into the scale of a later step).
+int launch_fp8_quantize(const void* x_bf16, const float* scale, void* q_e4m3, float* amax, int64_t n,
+                        cudaStream_t stream);
 
 // ------------------------------------------------------------------------------------------------
 // Selective state-space scan (ssm.cu): fp32 u, delta, y [B, L, D]; A [D, 16]; Bm, Cm [B, L, 16]; Dp [D].

@@ -85,6 +85,85 @@ class YvFP8Linear(nn.Module):
         return y if self.bias is None else y + self.bias
 
 
+class YvFP8DelayedScaling:
+    """Per-tensor delayed scaling (the recipe of the reference's fp8 operator, opss/train/fp8.py:381-399: amax history,
+    scale = fp8_max / max(history) / 2^margin).  The scale used at step t comes from the amax values of earlier steps,
+    so quantisation needs no extra pass over the tensor and no host synchronisation: the quantise kernel folds the
+    current tensor's amax into a device scalar that ``update()`` rolls into the history."""
+
+    def __init__(self, device: torch.device, history: int = 16, margin: int = 0, fmax: float = E4M3_MAX):
+        self.history, self.margin, self.fmax = history, margin, fmax
+        self.amax_hist = torch.zeros(history, dtype=torch.float32, device=device)
+        self.amax_now = torch.zeros(1, dtype=torch.float32, device=device)
+        self.scale = torch.ones(1, dtype=torch.float32, device=device)       # multiplies x before the cast
+        self.scale_inv = torch.ones(1, dtype=torch.float32, device=device)   # dequantisation factor
+        self.steps = 0
+
+    def update(self) -> None:
+        """Roll the amax recorded by the last quantisation into the history and derive the next scale (all on the
+        device, no synchronisation)."""
+        self.amax_hist = torch.roll(self.amax_hist, 1)
+        self.amax_hist[0] = self.amax_now[0]
+        self.amax_now.zero_()
+        amax = self.amax_hist.max().clamp_min(1e-12)
+        self.scale = (self.fmax / amax / (2.0 ** self.margin)).reshape(1)
+        self.scale_inv = (1.0 / self.scale).reshape(1)
+        self.steps += 1
+
+
+def fp8_quantize_delayed(x: torch.Tensor, meta: YvFP8DelayedScaling) -> torch.Tensor:
+    """bf16 CUDA tensor -> e4m3 with ``meta.scale``; records the tensor's amax in ``meta.amax_now``."""
+    from ..ops import kernels
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    kernels().fp8_quantize(x.contiguous(), meta.scale, q, meta.amax_now)
+    return q
+
+
+class _FP8GemmLinearFn(torch.autograd.Function):
+    """Forward on the fp8 tensor cores (tcgen05 ``kind::f8f6f4``, e4m3 x e4m3, fp32 accumulation, the product of the
+    two dequantisation factors applied in the epilogue); backward in bf16 from the saved bf16 operands."""
+
+    @staticmethod
+    def forward(ctx, x, w, mx, mw):
+        from ..ops import kernels, status_word
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        if mx.steps == 0:                      # first call: no history yet, take the scale from this tensor
+            for t, m in ((x2, mx), (w, mw)):
+                m.amax_now.copy_(t.detach().abs().max().float().reshape(1))
+                m.update()
+        xq, wq = fp8_quantize_delayed(x2, mx), fp8_quantize_delayed(w.contiguous(), mw)
+        y = torch.empty(x2.shape[0], w.shape[0], dtype=torch.bfloat16, device=x.device)
+        kernels().gemm_fp8(xq, wq, y, mx.scale_inv * mw.scale_inv, 0, status_word(x.device))
+        mx.update()
+        mw.update()
+        ctx.save_for_backward(x2, w)
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = F_.gemm(dy2, w, b_mn=True).view(ctx.shape)
+        dw = F_.gemm(dy2, x2, a_mn=True, b_mn=True)
+        return dx, dw, None, None
+
+
+class YvFP8GemmLinear(nn.Module):
+    """Linear layer whose forward runs the e4m3 GEMM kernel with delayed per-tensor scaling (CUDA, bf16 parameters;
+    in/out features multiples of 16)."""
+
+    def __init__(self, in_features: int, out_features: int, device=None, history: int = 16):
+        super().__init__()
+        device = torch.device(device or "cuda")
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=torch.bfloat16, device=device).normal_(std=0.02))
+        self.meta_x = YvFP8DelayedScaling(device, history)
+        self.meta_w = YvFP8DelayedScaling(device, history)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return _FP8GemmLinearFn.apply(x.to(torch.bfloat16), self.weight, self.meta_x, self.meta_w)
+
+
 class PiscesLxFP8QuantizationEngine:
     """PTQ entry for fp8 weights: per-tensor, per-channel or block scales; delayed scaling keeps an amax history
     (reference opss/quantize/engine.py:808-1103)."""

@@ -82,3 +82,41 @@ def test_split_k_skinny_linear_matches_reference_and_is_batch_invariant(M, N, K)
     assert torch.equal(y, F_.linear(x, w))                      # fixed summation order
     assert torch.equal(F_.linear(x[:1], w), y[:1])              # a row does not depend on its neighbours
     assert F_._splitk_plan(4096, N, K) == 0 and F_._splitk_plan(64, 154856, 4096) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1000, 1408, 4096), (4096, 4096, 4096)])
+def test_fp8_gemm_matches_dequantised_reference(M, N, K):
+    from pisceslx_b200.ops import check_status, kernels, status_word
+    torch.manual_seed(M)
+    Kn = kernels()
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    sx = (448.0 / x.abs().max().float()).reshape(1)
+    sw = (448.0 / w.abs().max().float()).reshape(1)
+    xq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=DEV)
+    wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device=DEV)
+    ax, aw = torch.zeros(1, device=DEV), torch.zeros(1, device=DEV)
+    Kn.fp8_quantize(x, sx, xq, ax)
+    Kn.fp8_quantize(w, sw, wq, aw)
+    assert abs(float(ax) - float(x.abs().max())) < 1e-6 and abs(float(aw) - float(w.abs().max())) < 1e-6
+    assert torch.equal(xq.float(), (x.float() * sx).to(torch.float8_e4m3fn).float())      # same rounding as torch
+    y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    Kn.gemm_fp8(xq, wq, y, 1.0 / (sx * sw), 0, status_word(torch.device(DEV, 0)))
+    torch.cuda.synchronize()
+    check_status()
+    ref = (xq.float() @ wq.float().t()) / (sx * sw)
+    assert _rel(y, ref) < 4e-3                                   # exact products, fp32 accumulation, bf16 output
+    assert _rel(y, x.float() @ w.float().t()) < 6e-2            # quantisation error of per-tensor e4m3
+
+
+def test_fp8_linear_module_delayed_scaling_trains():
+    from pisceslx_b200.quant.fp8 import YvFP8GemmLinear
+    torch.manual_seed(0)
+    lin = YvFP8GemmLinear(512, 256)
+    x = torch.randn(64, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    for _ in range(3):
+        y = lin(x)
+    ref = x.float() @ lin.weight.float().t()
+    assert _rel(y, ref) < 6e-2 and lin.meta_x.steps >= 3
+    y.float().pow(2).mean().backward()
+    assert x.grad is not None and lin.weight.grad is not None and torch.isfinite(lin.weight.grad.float()).all()
