@@ -1,0 +1,171 @@
+"""Serving-side runtime helpers (reference opss/infer/moe_runtime.py ``PiscesLxMoERuntimeOperator``: expert cache,
+batch sharing, load balancer, the "Moebius" EP<->TP switch heuristic :1563-1625; opss/infer/vllm.py chunked-prefill
+scheduler and multi-LoRA registry; opss/infer/tpo.py test-time preference optimisation)."""
+from __future__ import annotations
+
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+
+class PiscesLxExpertCache:
+    """LRU residency of expert weights on the device when not all experts fit (host copies stay pinned)."""
+
+    def __init__(self, capacity: int, loader: Callable[[int], Any]):
+        self.capacity, self.loader = capacity, loader
+        self.resident: "OrderedDict[int, Any]" = OrderedDict()
+        self.hits = self.misses = 0
+
+    def get(self, expert: int) -> Any:
+        if expert in self.resident:
+            self.resident.move_to_end(expert)
+            self.hits += 1
+            return self.resident[expert]
+        self.misses += 1
+        w = self.loader(expert)
+        self.resident[expert] = w
+        if len(self.resident) > self.capacity:
+            self.resident.popitem(last=False)
+        return w
+
+    def prefetch(self, experts: List[int]) -> None:
+        for e in experts:
+            self.get(e)
+
+
+class PiscesLxExpertLoadBalancer:
+    """Tracks expert load with an exponential moving average and proposes a placement of experts on ranks that
+    evens out the expected tokens per rank (greedy longest-processing-time)."""
+
+    def __init__(self, num_experts: int, decay: float = 0.9):
+        self.load = torch.zeros(num_experts)
+        self.decay = decay
+
+    def observe(self, counts: torch.Tensor) -> None:
+        self.load = self.decay * self.load + (1 - self.decay) * counts.float().cpu()
+
+    def imbalance(self) -> float:
+        m = float(self.load.mean())
+        return float(self.load.max()) / m if m > 0 else 1.0
+
+    def placement(self, n_ranks: int) -> List[List[int]]:
+        per = len(self.load) // n_ranks
+        ranks: List[List[int]] = [[] for _ in range(n_ranks)]
+        tot = [0.0] * n_ranks
+        for e in torch.argsort(self.load, descending=True).tolist():
+            r = min((i for i in range(n_ranks) if len(ranks[i]) < per), key=lambda i: tot[i])
+            ranks[r].append(e)
+            tot[r] += float(self.load[e])
+        return ranks
+
+
+class PiscesLxBatchSharing:
+    """Groups requests whose routed expert sets overlap so that one expert-weight read serves several requests."""
+
+    @staticmethod
+    def group(expert_sets: List[set], max_group: int = 8) -> List[List[int]]:
+        left = list(range(len(expert_sets)))
+        groups: List[List[int]] = []
+        while left:
+            seed = left.pop(0)
+            g, union = [seed], set(expert_sets[seed])
+            left.sort(key=lambda i: -len(union & expert_sets[i]))
+            while left and len(g) < max_group and len(union & expert_sets[left[0]]) > 0:
+                i = left.pop(0)
+                g.append(i)
+                union |= expert_sets[i]
+                left.sort(key=lambda j: -len(union & expert_sets[j]))
+            groups.append(g)
+        return groups
+
+
+def moebius_choose_layout(tokens_per_step: int, hidden: int, ffn: int, n_experts: int, top_k: int, n_gpus: int,
+                          nvlink_gbs: float = 770.0, hbm_gbs: float = 6500.0) -> Dict[str, Any]:
+    """EP vs TP for the expert layer of one decode / prefill step, from bytes moved: expert parallelism moves
+    activations (2 * tokens * top_k * hidden * 2 B over NVLink) and reads each rank's resident experts once; tensor
+    parallelism reads 1/n of every expert on every rank and all-reduces the output."""
+    w_bytes = 3 * hidden * ffn * 2
+    active = min(n_experts, tokens_per_step * top_k)
+    ep_comm = 2 * tokens_per_step * top_k * hidden * 2 * (n_gpus - 1) / n_gpus / n_gpus
+    ep_time = ep_comm / (nvlink_gbs * 1e9) + (active / n_gpus) * w_bytes / (hbm_gbs * 1e9)
+    tp_comm = 2 * tokens_per_step * hidden * 2 * (n_gpus - 1) / n_gpus
+    tp_time = tp_comm / (nvlink_gbs * 1e9) + active * w_bytes / n_gpus / (hbm_gbs * 1e9)
+    return {"layout": "ep" if ep_time <= tp_time else "tp", "ep_time_s": ep_time, "tp_time_s": tp_time}
+
+
+@dataclass
+class _PrefillJob:
+    request_id: int
+    tokens: List[int]
+    done: int = 0
+
+
+class PiscesLxChunkedPrefillScheduler:
+    """Token-budget scheduler: every step carries all running decodes (one token each) and fills the remaining budget
+    with prompt chunks, so that a long prompt does not stall the decodes (bounded inter-token latency)."""
+
+    def __init__(self, token_budget: int = 2048, chunk: int = 512):
+        self.token_budget, self.chunk = token_budget, chunk
+        self.prefill: List[_PrefillJob] = []
+        self.decoding: List[int] = []
+
+    def add(self, request_id: int, tokens: List[int]) -> None:
+        self.prefill.append(_PrefillJob(request_id, tokens))
+
+    def step(self) -> Dict[str, Any]:
+        budget = self.token_budget - len(self.decoding)
+        chunks: List[Tuple[int, int, int]] = []
+        for job in list(self.prefill):
+            if budget <= 0:
+                break
+            n = min(self.chunk, len(job.tokens) - job.done, budget)
+            chunks.append((job.request_id, job.done, job.done + n))
+            job.done += n
+            budget -= n
+            if job.done == len(job.tokens):
+                self.prefill.remove(job)
+                self.decoding.append(job.request_id)
+        return {"decode": list(self.decoding), "prefill_chunks": chunks}
+
+    def finish(self, request_id: int) -> None:
+        if request_id in self.decoding:
+            self.decoding.remove(request_id)
+
+
+class PiscesLxMultiLoRARegistry:
+    """Adapters by name; a batch with mixed adapters applies y += scale * (x A_i^T) B_i^T row-group by row-group."""
+
+    def __init__(self):
+        self.adapters: Dict[str, Tuple[torch.Tensor, torch.Tensor, float]] = {}
+
+    def register(self, name: str, a: torch.Tensor, b: torch.Tensor, scale: float = 1.0) -> None:
+        self.adapters[name] = (a, b, scale)
+
+    def apply(self, x: torch.Tensor, base_out: torch.Tensor, adapter_names: List[Optional[str]]) -> torch.Tensor:
+        out = base_out.clone()
+        for name in set(n for n in adapter_names if n is not None):
+            rows = torch.tensor([i for i, n in enumerate(adapter_names) if n == name], device=x.device)
+            a, b, s = self.adapters[name]
+            out[rows] += s * (x[rows] @ a.t().to(x.dtype)) @ b.t().to(x.dtype)
+        return out
+
+
+class PiscesLxTPO:
+    """Test-time preference optimisation: sample candidates, score them with a reward function, feed the best and
+    the worst back as a textual critique, repeat; returns the best candidate seen."""
+
+    def __init__(self, generate: Callable[[str, int], str], reward: Callable[[str, str], float], n: int = 4, rounds: int = 2):
+        self.generate, self.reward, self.n, self.rounds = generate, reward, n, rounds
+
+    def run(self, prompt: str, max_new_tokens: int = 128) -> Dict[str, Any]:
+        best, best_r, ctx = None, float("-inf"), prompt
+        for _ in range(self.rounds):
+            cands = [self.generate(ctx, max_new_tokens) for _ in range(self.n)]
+            scored = sorted(((self.reward(prompt, c), c) for c in cands), key=lambda t: t[0])
+            if scored[-1][0] > best_r:
+                best_r, best = scored[-1]
+            ctx = (f"{prompt}\nA weaker answer was:\n{scored[0][1]}\nA stronger answer was:\n{scored[-1][1]}\n"
+                   f"Write an answer better than both.\n")
+        return {"answer": best, "reward": best_r}
