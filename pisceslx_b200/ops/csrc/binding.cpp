@@ -152,6 +152,30 @@ void gemm_batched(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_
   check_rc(yv::launch_gemm(g, cur_stream()), "gemm_batched");
 }
 
+// c[g] = ec * (a[g] @ b[g]^T) + eb * cin[g] + ea * I   (square [n, n] outputs, n a multiple of 128): the
+// Newton-Schulz polynomial b A + c A^2 + a I formed in the epilogue of the A A product
+void gemm_batched_affine(const Tensor& a, const Tensor& b, const Tensor& cin, Tensor c, double ea, double eb, double ec,
+                         const c10::optional<Tensor>& status) {
+  check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(cin, "cin"); check_bf16(c, "c");
+  TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3 && a.is_contiguous() && b.is_contiguous() &&
+              c.is_contiguous() && cin.is_contiguous(), "gemm_batched_affine: contiguous 3-D operands expected");
+  TORCH_CHECK(cin.sizes() == c.sizes() && c.size(1) == c.size(2) && a.size(0) == c.size(0) && b.size(0) == c.size(0),
+              "gemm_batched_affine: square outputs with cin of the same shape expected");
+  TORCH_CHECK(c.data_ptr() != a.data_ptr() && c.data_ptr() != b.data_ptr() && c.data_ptr() != cin.data_ptr(),
+              "gemm_batched_affine: the output must not alias an input");
+  const c10::cuda::CUDAGuard guard(a.device());
+  yv::GemmArgs g;
+  g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = c.data_ptr();
+  g.mode = 3;
+  g.num_groups = static_cast<int>(a.size(0));
+  g.M = static_cast<int>(a.size(1)); g.K = static_cast<int>(a.size(2)); g.N = static_cast<int>(b.size(1));
+  TORCH_CHECK(b.size(2) == g.K && c.size(1) == g.M && c.size(2) == g.N, "gemm_batched_affine: shape mismatch");
+  g.epi_cin = cin.data_ptr();
+  g.epi_a = static_cast<float>(ea); g.epi_b = static_cast<float>(eb); g.epi_c = static_cast<float>(ec);
+  g.status = statusp(status);
+  check_rc(yv::launch_gemm(g, cur_stream()), "gemm_batched_affine");
+}
+
 // ------------------------------------------------------------------------------------------------
 // elementwise
 // ------------------------------------------------------------------------------------------------

@@ -133,6 +133,13 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
 
   int r;
   p.out_scale = a.out_scale;
+  p.epi_cin = reinterpret_cast<const __nv_bfloat16*>(a.epi_cin);
+  p.epi_a = a.epi_a; p.epi_b = a.epi_b; p.epi_c = a.epi_c;
+  if (a.epi_cin != nullptr) {
+    if (a.out_fp32 || a.accumulate || a.comm != 0 || a.fp8 || (a.N % 64) != 0 || (a.ldc != 0 && a.ldc != a.N) ||
+        (reinterpret_cast<uintptr_t>(a.epi_cin) & 15u) != 0)
+      return -80;
+  }
   if (a.fp8) {
     // e4m3 operands: one byte per element, 128 elements per 128-byte row of a stage
     if (a.mode != kDense || a.a_mn || a.b_mn || a.out_fp32 || a.accumulate || a.comm != 0) return -70;

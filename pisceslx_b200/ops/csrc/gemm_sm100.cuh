@@ -55,6 +55,10 @@ struct GemmParams {
   // ---- fp8 inputs (template parameter FP8): e4m3 operands, K-major, 128 elements per shared-memory row; the
   // epilogue multiplies the fp32 accumulator by *out_scale (= scale_a * scale_b of per-tensor scaling) ----
   const float* out_scale;
+  // ---- affine epilogue (bf16 output, no fused collective): C = epi_c * (A B) + epi_b * epi_cin + epi_a * I, with
+  // epi_cin laid out like C; the identity is per group in the batched mode ----
+  const __nv_bfloat16* epi_cin;
+  float epi_a, epi_b, epi_c;
 };
 
 constexpr int kBM = 128;
@@ -397,10 +401,33 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
             for (int i = 0; i < 32; ++i) { v0[i] = 0u; v1[i] = 0u; }
           }
           const float osc = (FP8 && p.out_scale != nullptr) ? *p.out_scale : 1.f;
+          if (!FP8 && COMM == 0 && p.epi_cin != nullptr) {
+            // out = epi_c * acc + epi_b * Cin + epi_a * I: the Newton-Schulz polynomial b A + c A^2 (+ a I) formed in
+            // the epilogue of the A * A product, Cin = A in the layout of C (N a multiple of 64)
+            const int col0 = t.c_x + c * kColsPerChunk;
+            const bool in = col0 + kColsPerChunk <= p.N;
+            const uint4* src = reinterpret_cast<const uint4*>(p.epi_cin + static_cast<int64_t>(t.c_y + row) * p.N + col0);
+            uint4 cin[8];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            packed[i] = pack_bf16(__uint_as_float(v0[2 * i]) * osc, __uint_as_float(v0[2 * i + 1]) * osc);
-            packed[16 + i] = pack_bf16(__uint_as_float(v1[2 * i]) * osc, __uint_as_float(v1[2 * i + 1]) * osc);
+            for (int j = 0; j < 8; ++j) cin[j] = in ? src[j] : make_uint4(0u, 0u, 0u, 0u);
+            const __nv_bfloat16* cb = reinterpret_cast<const __nv_bfloat16*>(cin);
+            const int lrow = (p.c_group_stride > 0 ? t.c_y % p.c_group_stride : t.c_y) + row;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int ca = col0 + 2 * i, cbk = col0 + 32 + 2 * i;
+              const float a0 = p.epi_c * __uint_as_float(v0[2 * i]) + p.epi_b * __bfloat162float(cb[2 * i]) + (lrow == ca ? p.epi_a : 0.f);
+              const float a1 = p.epi_c * __uint_as_float(v0[2 * i + 1]) + p.epi_b * __bfloat162float(cb[2 * i + 1]) + (lrow == ca + 1 ? p.epi_a : 0.f);
+              const float b0 = p.epi_c * __uint_as_float(v1[2 * i]) + p.epi_b * __bfloat162float(cb[32 + 2 * i]) + (lrow == cbk ? p.epi_a : 0.f);
+              const float b1 = p.epi_c * __uint_as_float(v1[2 * i + 1]) + p.epi_b * __bfloat162float(cb[33 + 2 * i]) + (lrow == cbk + 1 ? p.epi_a : 0.f);
+              packed[i] = pack_bf16(a0, a1);
+              packed[16 + i] = pack_bf16(b0, b1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              packed[i] = pack_bf16(__uint_as_float(v0[2 * i]) * osc, __uint_as_float(v0[2 * i + 1]) * osc);
+              packed[16 + i] = pack_bf16(__uint_as_float(v1[2 * i]) * osc, __uint_as_float(v1[2 * i + 1]) * osc);
+            }
           }
         } else {
           if (t.k_iters > 0) {

@@ -44,6 +44,9 @@ struct GemmArgs {
   // fp8 (e4m3) operands, both stored K-inner, bf16 output scaled by *out_scale in the epilogue (dense mode only)
   bool fp8 = false;
   const float* out_scale = nullptr;
+  // affine epilogue: C = epi_c * (A B) + epi_b * epi_cin + epi_a * I (epi_cin bf16, laid out like C; N % 64 == 0)
+  const void* epi_cin = nullptr;
+  float epi_a = 0.f, epi_b = 0.f, epi_c = 1.f;
 };
 // Returns 0 on success, a negative code when an argument is rejected, a positive cudaError_t otherwise.
 int launch_gemm(const GemmArgs& args, cudaStream_t stream);

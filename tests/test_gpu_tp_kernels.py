@@ -120,3 +120,33 @@ def test_fp8_linear_module_delayed_scaling_trains():
     assert _rel(y, ref) < 6e-2 and lin.meta_x.steps >= 3
     y.float().pow(2).mean().backward()
     assert x.grad is not None and lin.weight.grad is not None and torch.isfinite(lin.weight.grad.float()).all()
+
+
+@pytest.mark.parametrize("G,n", [(3, 256), (2, 1408)])
+def test_batched_gemm_affine_epilogue_forms_newton_schulz_polynomial(G, n):
+    from pisceslx_b200.ops import check_status, kernels, status_word
+    torch.manual_seed(n)
+    Kn = kernels()
+    x = torch.randn(G, n, 2 * n, device=DEV) / (2 * n) ** 0.5
+    A = (x @ x.transpose(1, 2)).to(torch.bfloat16)                     # symmetric
+    out = torch.empty_like(A)
+    a, b, c = 3.4445, -4.7750, 2.0315
+    Kn.gemm_batched_affine(A, A, A, out, a, b, c, status_word(torch.device(DEV, 0)))
+    torch.cuda.synchronize()
+    check_status()
+    Af = A.float()
+    ref = a * torch.eye(n, device=DEV) + b * Af + c * (Af @ Af.transpose(1, 2))
+    assert _rel(out, ref) < 4e-3
+
+
+def test_newton_schulz_with_fused_polynomial_matches_reference():
+    from pisceslx_b200.ops.reference import newton_schulz
+    from pisceslx_b200.optim.muon import newton_schulz_batched
+    torch.manual_seed(0)
+    for shape in [(2, 256, 512), (2, 512, 256)]:
+        g = torch.randn(*shape, device=DEV, dtype=torch.bfloat16)
+        o = newton_schulz_batched(g).float()
+        r = newton_schulz(g.float())
+        assert _rel(o, r) < 5e-2
+        s = torch.linalg.svdvals(o)
+        assert float(s.max()) < 1.3 and float(s.min()) > 0.5
