@@ -1,0 +1,127 @@
+"""Two-GPU NCCL runs of context parallelism (ring attention with the flash kernels as the local step) and pipeline
+parallelism (two stages, 1F1B, NCCL send/recv) against single-GPU references.  Skipped with fewer than two GPUs."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CP_WORKER = textwrap.dedent("""
+    import json, math, os, sys
+    sys.path.insert(0, {root!r})
+    import torch, torch.distributed as dist
+    from pisceslx_b200.parallel.state import init_parallel
+    from pisceslx_b200.parallel import cp
+    from pisceslx_b200.ops import functional as F_, check_status
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    par = init_parallel(backend="nccl", device=dev, timeout_s=120)
+    W, r = par.world_size, par.rank
+    torch.manual_seed(0)
+    hq, hk, d, S = 8, 2, 128, 1024
+    q, k, v = (torch.randn(S, h * d, device=dev, dtype=torch.bfloat16) for h in (hq, hk, hk))
+    for t in (q, k, v):
+        dist.broadcast(t, 0)
+    cu = torch.tensor([0, S], dtype=torch.int32, device=dev)
+    res = {{}}
+    L = S // W
+    sl = slice(r * L, (r + 1) * L)
+    for causal in (True, False):
+        full = F_.attention(q, k, v, cu, cu, S, S, hq, hk, d, causal)
+        o = cp.ring_attention(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), dist.group.WORLD, hq, hk, d,
+                              causal=causal)
+        res[f"ring_{{causal}}"] = float((o.float() - full[sl].float()).norm() / full[sl].float().norm())
+        o2 = cp.allgather_attention(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), dist.group.WORLD, hq, hk, d,
+                                    causal=causal)
+        res[f"ag_{{causal}}"] = float((o2.float() - full[sl].float()).norm() / full[sl].float().norm())
+    torch.cuda.synchronize()
+    check_status()
+    if r == 0:
+        json.dump(res, open(sys.argv[1], "w"))
+    dist.barrier(); dist.destroy_process_group()
+""")
+
+PP_WORKER = textwrap.dedent("""
+    import json, os, sys
+    sys.path.insert(0, {root!r})
+    import torch, torch.distributed as dist
+    from pisceslx_b200 import YvConfig
+    from pisceslx_b200.models import build_model
+    from pisceslx_b200.parallel.state import init_parallel
+    from pisceslx_b200.parallel.pp import YvPipelineStage
+    from pisceslx_b200.engine.checkpoint import load_full_into
+    from pisceslx_b200.ops import check_status
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    par = init_parallel(pp=2, backend="nccl", device=dev, timeout_s=120)
+    cfg = YvConfig.tiny_text_moe(vocab_size=512); cfg.n_layer = 4; cfg.use_gradient_checkpointing = False
+    model = build_model(cfg, dev, torch.bfloat16, parallel=par, seed=5)
+    load_full_into(model, torch.load(sys.argv[2]))
+    model.train()
+    g = torch.Generator().manual_seed(0)
+    micro = [dict(input_ids=(t := torch.randint(0, 512, (2, 128), generator=g).to(dev)), labels=t) for _ in range(4)]
+    stage = YvPipelineStage(model, par, cfg.hidden_size, torch.bfloat16)
+    loss = stage.run(micro, "1f1b")
+    torch.cuda.synchronize()
+    check_status()
+    json.dump({{"rank": par.rank, "loss": float(loss) if loss is not None else None}}, open(sys.argv[1] + f".{{par.rank}}", "w"))
+    dist.barrier(); dist.destroy_process_group()
+""")
+
+
+def _spawn(script_text, tmp_path, world, args):
+    script = tmp_path / "w.py"
+    script.write_text(script_text.format(root=ROOT))
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)] + [str(a) for a in args], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    logs = []
+    for p in procs:
+        o, _ = p.communicate(timeout=300)
+        logs.append(o.decode()[-3000:])
+    assert all(p.returncode == 0 for p in procs), "\n".join(logs)
+
+
+needs_two = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+
+
+@needs_two
+@pytest.mark.timeout(600)
+def test_ring_and_allgather_attention_on_two_gpus(tmp_path):
+    out = tmp_path / "cp.json"
+    _spawn(CP_WORKER, tmp_path, 2, [out])
+    for k, v in json.load(open(out)).items():
+        assert v < 8e-3, (k, v)
+
+
+@needs_two
+@pytest.mark.timeout(600)
+def test_pipeline_two_stages_on_two_gpus(tmp_path):
+    from pisceslx_b200 import YvConfig
+    from pisceslx_b200.models import build_model
+    cfg = YvConfig.tiny_text_moe(vocab_size=512)
+    cfg.n_layer, cfg.use_gradient_checkpointing = 4, False
+    ref = build_model(cfg, "cuda", torch.bfloat16, seed=5)
+    sd_path = tmp_path / "full.pt"
+    torch.save(ref.to_reference_state_dict(), sd_path)
+    ref.train()
+    g = torch.Generator().manual_seed(0)
+    losses = []
+    for _ in range(4):
+        t = torch.randint(0, 512, (2, 128), generator=g).cuda()
+        losses.append(float(ref(input_ids=t, labels=t)["loss"]))
+    _spawn(PP_WORKER, tmp_path, 2, [tmp_path / "pp", sd_path])
+    last = json.load(open(str(tmp_path / "pp") + ".1"))
+    assert abs(last["loss"] - sum(losses) / 4) < 3e-2 * abs(sum(losses) / 4), (last, losses)
