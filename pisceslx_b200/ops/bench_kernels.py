@@ -144,6 +144,37 @@ def bench_ssm(a: argparse.Namespace) -> Dict[str, Any]:
             "state_updates_per_s": B * L * D * 16 / ms * 1e3}
 
 
+def bench_gemm_tp(a: argparse.Namespace, mode: int) -> Dict[str, Any]:
+    """The fused tensor-parallel GEMM kernels on ONE GPU: the "peers" are other buffers of this device (the kernels
+    only read or write peer memory and wait on counters their own CTAs advance), world = --batch ranks.  Shows the
+    kernel's own cost (copier warps / inbox stores beside the MMA pipeline) without NVLink in the way; the two-GPU
+    numbers come from ``parallel/bench_tp.py``."""
+    K, st = kernels(), status_word(torch.device("cuda"))
+    world, rank = max(2, a.batch), 0
+    M, N, Kd = a.m, a.n, a.k
+    rows = M // world
+    w = torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16) * 0.02
+    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    if mode == 1:
+        shards = [torch.randn(rows, Kd, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+        xg = torch.empty(M, Kd, device="cuda", dtype=torch.bfloat16)
+        xg[:rows] = shards[0]
+        ptrs = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64)
+        flags = torch.zeros(M // 128 + 8, dtype=torch.int32, device="cuda")
+        fn = lambda: K.gemm_tp(xg, w, y, 1, ptrs, flags, rank, rows, False, 0, st)
+        name = "gemm_tp_allgather"
+    else:
+        x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+        inboxes = [torch.empty(world, rows, N, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+        ptrs = torch.tensor([t.data_ptr() for t in inboxes], dtype=torch.int64)
+        fn = lambda: K.gemm_tp(x, w, y, 2, ptrs, None, rank, rows, False, 0, st)
+        name = "gemm_tp_reduce_scatter_push"
+    ms = timeit(fn, a.iters)
+    tf = 2.0 * M * N * Kd / ms / 1e9
+    return {"kernel": name, "shape": [M, N, Kd], "world": world, "ms": ms, "tflops": tf,
+            "frac_of_peak": tf / peaks()["bf16_tflops"]}
+
+
 def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
     """Batched Newton-Schulz on [batch, m, n] (the Muon orthogonalisation of a stack of expert matrices), plus the
     three batched GEMMs of one iteration timed separately."""
@@ -173,7 +204,7 @@ def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm"])
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs"])
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -207,7 +238,8 @@ def main() -> None:
     else:
         fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
               "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz, "gemm_fp8": bench_gemm_fp8,
-              "ssm": bench_ssm}[a.kernel]
+              "ssm": bench_ssm, "gemm_tp_ag": lambda x: bench_gemm_tp(x, 1),
+              "gemm_tp_rs": lambda x: bench_gemm_tp(x, 2)}[a.kernel]
         res.append(fn(a))
     out = {"peaks": peaks(), "results": res}
     print(json.dumps(out, indent=1))

@@ -191,6 +191,11 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
       tc_fence_after_sync();
       const uint32_t tS = tmem_base + lane_off + kColS, tDP = tmem_base + lane_off + kColDP;
       const int kbase = j * 128;
+      // the select per element is only needed on tiles that touch the causal diagonal, the end of the keys or a
+      // query row past the end (uniform over the warp except for q_valid, which is folded in)
+      const bool need_mask = !q_valid || (kbase + 127 > key_limit) || (kbase + 128 > k_len);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-delta, -delta);
       uint32_t pk[64];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -198,17 +203,21 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tDP + c * 32, dv);
         tc_wait_ld();
+        // two keys per step: packed FMA -> bf16x2 -> one ex2 on the pair; dS = P * (dP - delta) in packed fp32
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float r[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kidx = kbase + c * 32 + 2 * i + u;
-            const bool vis = q_valid && kidx <= key_limit && kidx < k_len;
-            const float pr = vis ? exp2f(__uint_as_float(sv[2 * i + u]) * p.scale_log2 - lse2) : 0.f;
-            r[u] = pr * (__uint_as_float(dv[2 * i + u]) - delta);
+          const int kidx = kbase + c * 32 + 2 * i;
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), sc2, nl2);
+          if (need_mask) {
+            if (!(q_valid && kidx <= key_limit && kidx < k_len)) x.x = -INFINITY;
+            if (!(q_valid && kidx + 1 <= key_limit && kidx + 1 < k_len)) x.y = -INFINITY;
           }
-          pk[c * 16 + i] = pack_bf16(r[0], r[1]);
+          const __nv_bfloat162 e = h2exp2(__float22bfloat162_rn(x));
+          const uint32_t bits = *reinterpret_cast<const uint32_t*>(&e);
+          const float2 pf = make_float2(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
+          const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), nd2);
+          const float2 r = __fmul2_rn(pf, dd);
+          pk[c * 16 + i] = pack_bf16(r.x, r.y);
         }
       }
       {

@@ -160,8 +160,9 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         const int qpos = qb + tix;
         const bool v = qpos < q_len;
         const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
-        lse_b[tix] = v ? p.lse[idx] * kLog2e : INFINITY;     // +inf -> probability 0 for rows past the end
-        del_b[tix] = v ? p.delta[idx] : 0.f;
+        // stored negated so that the consumers fold them into packed fused multiply-adds
+        lse_b[tix] = v ? -p.lse[idx] * kLog2e : -INFINITY;   // -inf -> probability 0 for rows past the end
+        del_b[tix] = v ? -p.delta[idx] : 0.f;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = mbar_wait(sdp_full, it & 1u, p.status);
@@ -184,6 +185,9 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       const uint32_t tST = tmem_base + lane_off + kColST, tDPT = tmem_base + lane_off + kColDPT;
       // a query column c is visible to this key iff key <= (qb + c) + shift
       const int first_vis_c = p.causal ? (key - causal_shift - qb) : 0;
+      // every (key, query) pair of this tile is visible: no per-element selects (uniform over the CTA)
+      const bool full_vis = (!p.causal || qb >= k0 + 127 - causal_shift) && (k0 + 127 < k_len);
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       uint32_t pp[64], ds[64];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -191,19 +195,25 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         tmem_ld32(tST + c * 32, sv);
         tmem_ld32(tDPT + c * 32, dv);
         tc_wait_ld();
+        // Two queries per step: P = 2^(s * scale - lse) through one packed FMA, one bf16x2 conversion and one
+        // special-function instruction whose result is the packed P operand; dS = P * (dP - delta) in packed fp32.
 #pragma unroll
         for (int i2 = 0; i2 < 16; ++i2) {
-          float pr[2], dsv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + 2 * i2 + u;
-            const bool vis = key_valid && col >= first_vis_c;
-            const float prob = vis ? exp2f(__uint_as_float(sv[2 * i2 + u]) * p.scale_log2 - lse_b[col]) : 0.f;
-            pr[u] = prob;
-            dsv[u] = prob * (__uint_as_float(dv[2 * i2 + u]) - del_b[col]);
+          const int col = c * 32 + 2 * i2;
+          const float2 nl = *reinterpret_cast<const float2*>(lse_b + col);
+          const float2 nd = *reinterpret_cast<const float2*>(del_b + col);
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i2]), __uint_as_float(sv[2 * i2 + 1])), sc2, nl);
+          if (!full_vis) {
+            if (!(key_valid && col >= first_vis_c)) x.x = -INFINITY;
+            if (!(key_valid && col + 1 >= first_vis_c)) x.y = -INFINITY;
           }
-          pp[c * 16 + i2] = pack_bf16(pr[0], pr[1]);
-          ds[c * 16 + i2] = pack_bf16(dsv[0], dsv[1]);
+          const __nv_bfloat162 e = h2exp2(__float22bfloat162_rn(x));
+          const uint32_t bits = *reinterpret_cast<const uint32_t*>(&e);
+          pp[c * 16 + i2] = bits;
+          const float2 pf = make_float2(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
+          const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dv[2 * i2]), __uint_as_float(dv[2 * i2 + 1])), nd);
+          const float2 dsf = __fmul2_rn(pf, dd);
+          ds[c * 16 + i2] = pack_bf16(dsf.x, dsf.y);
         }
       }
       {

@@ -214,14 +214,21 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
       }
       const int kbase = j * kAttnBlock;
       const bool need_mask = (kbase + kAttnBlock - 1 > key_limit) || (kbase + kAttnBlock > k_len);
+      // The row maximum is taken over the raw scores (the scale is positive); scaling and the subtraction of the
+      // reference maximum are one fused multiply-add per pair of scores further down.
       float mx = kMaskValue;
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        float v = __uint_as_float(sreg[i]) * p.scale_log2;
-        if (need_mask && (kbase + i > key_limit || kbase + i >= k_len)) v = kMaskValue;
-        sreg[i] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int i = 0; i < 128; ++i) {
+          if (kbase + i > key_limit || kbase + i >= k_len) sreg[i] = 0xFF800000u;      // -inf: 2^(-inf) = 0
+          mx = fmaxf(mx, __uint_as_float(sreg[i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; i += 2)
+          mx = fmaxf(mx, fmaxf(__uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1])));
       }
+      mx = (mx > 0.5f * kMaskValue) ? mx * p.scale_log2 : kMaskValue;
       // lazy rescale: keep the old reference max unless the new one is much larger
       float alpha = 1.f;
       bool rescale = false;
@@ -230,15 +237,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_fwd_kernel(const __grid_
         m_used = mx;
         rescale = (j > 0);
       }
-      float rs = 0.f;
+      // p = 2^(s * scale - m) two scores at a time: one packed fp32 FMA, one conversion to bf16x2 and ONE
+      // special-function instruction (ex2 on a bf16 pair) whose result already is the packed P operand.  The row sum
+      // adds the rounded values that the tensor core will multiply, unpacked with two logic ops and a packed add.
+      float2 rs2 = make_float2(0.f, 0.f);
       uint32_t pk[64];
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(-m_used, -m_used);
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        const float a = exp2f(__uint_as_float(sreg[2 * i]) - m_used);
-        const float c = exp2f(__uint_as_float(sreg[2 * i + 1]) - m_used);
-        rs += a + c;
-        pk[i] = pack_bf16(a, c);
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[2 * i]), __uint_as_float(sreg[2 * i + 1])), sc2, nm2);
+        const __nv_bfloat162 e = h2exp2(__float22bfloat162_rn(x));
+        const uint32_t bits = *reinterpret_cast<const uint32_t*>(&e);
+        pk[i] = bits;
+        rs2 = __fadd2_rn(rs2, make_float2(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u)));
       }
+      const float rs = rs2.x + rs2.y;
       l_sum = l_sum * alpha + rs;
       if (__any_sync(0xFFFFFFFFu, rescale)) {
         // O holds sums relative to the old max: wait for the previous P V product, then scale the row
