@@ -51,7 +51,11 @@ class YvRecomputePlanner:
         if self.stage >= 3:
             return
         peak = torch.cuda.max_memory_allocated(self.device)
-        limit = int(self.budget * self.total)
+        # Memory that the caching allocator does not see (symmetric heaps of the peer-memory kernels, NCCL buffers,
+        # the CUDA context) comes off the budget: device-wide usage minus what the allocator holds.
+        free_now, total_now = torch.cuda.mem_get_info(self.device)
+        outside = max(0, (total_now - free_now) - torch.cuda.memory_reserved(self.device))
+        limit = int(self.budget * self.total) - outside
         if self.stage == 0:
             room = self._agree(1 if limit - peak > self.min_headroom else 0)
             if not room:
@@ -70,7 +74,7 @@ class YvRecomputePlanner:
             self.layer_bytes = a
             n = 0
             if a > 0:
-                n = max(0, (limit - peak) // a)
+                n = max(0, (limit - peak) // a - 1)          # one layer's worth kept back for allocator fragmentation
             n = self._agree(min(int(n), len(self.layers) - 1))
             for l in self.layers[len(self.layers) - 1 - n:]:
                 l.use_recompute = False

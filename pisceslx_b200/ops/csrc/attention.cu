@@ -203,10 +203,10 @@ int launch_paged_decode(const PagedDecodeArgs& a, cudaStream_t stream) {
       cfg = true;
     }
     switch (G) {
-      case 1: paged_decode_mma_kernel<1><<<grid, 128, kDmSmem, stream>>>(pm); break;
-      case 2: paged_decode_mma_kernel<2><<<grid, 128, kDmSmem, stream>>>(pm); break;
-      case 4: paged_decode_mma_kernel<4><<<grid, 128, kDmSmem, stream>>>(pm); break;
-      default: paged_decode_mma_kernel<8><<<grid, 128, kDmSmem, stream>>>(pm); break;
+      case 1: paged_decode_mma_kernel<1><<<grid, kDmThreads, kDmSmem, stream>>>(pm); break;
+      case 2: paged_decode_mma_kernel<2><<<grid, kDmThreads, kDmSmem, stream>>>(pm); break;
+      case 4: paged_decode_mma_kernel<4><<<grid, kDmThreads, kDmSmem, stream>>>(pm); break;
+      default: paged_decode_mma_kernel<8><<<grid, kDmThreads, kDmSmem, stream>>>(pm); break;
     }
     r = 0;
   } else if (use_tma) {
