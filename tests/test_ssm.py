@@ -93,3 +93,17 @@ def test_model_with_hybrid_backbone_trains_on_cpu():
     out = m(input_ids=ids, labels=ids)
     out["loss"].backward()
     assert m.model.layers[0].ssm.A_log.grad is not None and torch.isfinite(out["loss"])
+
+
+@pytest.mark.gpu
+def test_hybrid_backbone_trains_on_gpu_with_recompute():
+    from pisceslx_b200.engine.trainer import YvTrainer, YvTrainerConfig
+    from pisceslx_b200.models import build_model
+    cfg = YvConfig.tiny_text_moe(vocab_size=512)
+    cfg.n_layer = 2
+    cfg.use_mamba3, cfg.backbone_allow_legacy_blocks, cfg.use_gradient_checkpointing = True, False, True
+    m = build_model(cfg, "cuda", torch.bfloat16, seed=1)
+    tr = YvTrainer(m, YvTrainerConfig(micro_batch_size=2, optimizer="adamw", lr=2e-3, max_steps=50, clip_grad_norm=1.0))
+    ids = torch.randint(0, 512, (2, 128), generator=torch.Generator().manual_seed(0))
+    losses = [tr.train_step({"input_ids": ids, "labels": ids})["loss"] for _ in range(6)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0]
