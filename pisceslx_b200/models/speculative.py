@@ -154,6 +154,69 @@ class YvSpeculativeDecoder:
         return ids[:, : input_ids.shape[1] + max_new_tokens], stats
 
 
+class YvParallelVerifier:
+    """Verifies a whole draft (or several candidate drafts of equal length) in one forward pass of the target model
+    (reference model/generation/speculative.py:468).  Returns, per candidate, the number of leading draft tokens that
+    the target model agrees with and the token it would emit after them."""
+
+    def __init__(self, model: Any, threshold: float = 0.0):
+        self.model, self.threshold = model, threshold
+
+    @torch.no_grad()
+    def verify(self, input_ids: torch.Tensor, drafts: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """input_ids [1, S]; drafts [C, n] -> accepted [C], next_token [C], probs [C, n]."""
+        C, n = drafts.shape
+        cand = torch.cat([input_ids.expand(C, -1), drafts], 1)
+        logits = self.model(input_ids=cand).logits[:, -(n + 1):, :].float()
+        probs = torch.softmax(logits, -1)
+        p_draft = torch.gather(probs[:, :n], 2, drafts[..., None]).squeeze(-1)          # [C, n]
+        if self.threshold > 0:
+            ok = p_draft >= self.threshold
+        else:
+            ok = logits[:, :n].argmax(-1) == drafts
+        accepted = ok.long().cumprod(1).sum(1)
+        nxt = torch.gather(logits.argmax(-1), 1, accepted[:, None]).squeeze(1)
+        return {"accepted": accepted, "next_token": nxt, "probs": p_draft}
+
+    def best(self, input_ids: torch.Tensor, drafts: torch.Tensor) -> Tuple[List[int], int]:
+        r = self.verify(input_ids, drafts)
+        c = int(r["accepted"].argmax())
+        k = int(r["accepted"][c])
+        return drafts[c, :k].tolist() + [int(r["next_token"][c])], k
+
+
+class YvAdaptiveSpeculativeDecoder(YvSpeculativeDecoder):
+    """Adjusts the draft length between generation calls from the measured acceptance rate (reference :1335): a high
+    rate means drafts are cheap wins, so they get longer; a low rate shortens them.  The expected tokens per target
+    forward for acceptance rate a and length n is (1 - a^(n+1)) / (1 - a); the length that maximises it per unit cost
+    ``1 + n * draft_cost`` is chosen."""
+
+    def __init__(self, model: Any, cfg: Optional[YvSpeculativeConfig] = None, draft_cost: float = 0.05,
+                 min_len: int = 1, max_len: int = 16, ema: float = 0.7, **kw: Any):
+        super().__init__(model, cfg, **kw)
+        self.draft_cost, self.min_len, self.max_len, self.ema = draft_cost, min_len, max_len, ema
+        self.rate: Optional[float] = None
+        self.history: List[Dict[str, float]] = []
+
+    def best_length(self, a: float) -> int:
+        a = min(max(a, 1e-3), 0.999)
+        score = lambda n: (1 - a ** (n + 1)) / (1 - a) / (1 + n * self.draft_cost)
+        return max(range(self.min_len, self.max_len + 1), key=score)
+
+    def observe(self, acceptance_rate: float) -> int:
+        self.rate = acceptance_rate if self.rate is None else self.ema * self.rate + (1 - self.ema) * acceptance_rate
+        self.cfg.draft_length = self.best_length(self.rate)
+        self.history.append({"rate": self.rate, "draft_length": self.cfg.draft_length})
+        return self.cfg.draft_length
+
+    def speculative_generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32,
+                             eos_token_id: Optional[int] = None) -> Tuple[torch.Tensor, Dict[str, Any]]:
+        out, stats = super().speculative_generate(input_ids, max_new_tokens, eos_token_id)
+        if stats["drafted"]:
+            stats["next_draft_length"] = self.observe(stats["acceptance_rate"])
+        return out, stats
+
+
 @torch.no_grad()
 def beam_search(model: Any, input_ids: torch.Tensor, num_beams: int = 4, max_new_tokens: int = 32,
                 length_penalty: float = 1.0, eos_token_id: Optional[int] = None) -> torch.Tensor:
