@@ -34,6 +34,7 @@ def main() -> None:
     ap.add_argument("--block-size", type=int, default=64)
     ap.add_argument("--model", default="yv_7b_moe")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result is then not a benchmark)")
+    ap.add_argument("--no-graphs", action="store_true", help="decode through the eager step instead of CUDA graph replay")
     args = ap.parse_args()
 
     from pisceslx_b200 import YvConfig
@@ -49,7 +50,8 @@ def main() -> None:
     model = build_model(cfg, device=dev, dtype=torch.bfloat16, seed=0).eval()
     per_seq = (max(args.prompt_len, args.ttft_prompt_len) + args.new_tokens + args.block_size - 1) // args.block_size + 1
     eng = YvInferenceEngine(model, cfg=YvEngineConfig(max_num_seqs=args.batch, num_blocks=per_seq * args.batch + 8,
-                                                      block_size=args.block_size, eos_token_id=-1))
+                                                      block_size=args.block_size, eos_token_id=-1,
+                                                      use_cuda_graphs=not args.no_graphs))
     gen = torch.Generator().manual_seed(0)
 
     def prompt(n: int):
@@ -108,6 +110,7 @@ def main() -> None:
                    "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.new_tokens,
                    "kv_block": args.block_size, "parallelism": "tp1"},
         "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9,
+        "decode_graphs": eng.graph.stats(),
     }
     print(json.dumps(out))
 

@@ -50,6 +50,8 @@ class YvEngineConfig:
     block_size: int = 64
     max_model_len: int = 131072
     eos_token_id: Optional[int] = None
+    use_cuda_graphs: bool = True          # replay decode steps from CUDA graphs (one graph per batch bucket)
+    graph_max_seq_len: int = 8192         # sequences longer than this decode through the eager step
 
 
 class YvInferenceEngine:
@@ -62,6 +64,9 @@ class YvInferenceEngine:
         self.cache: YvPagedKVCache = cache_for_model(model.cfg, self.device, self.cfg.num_blocks, self.cfg.block_size,
                                                      tp_size=tp, n_layer=len(model.model.layers), dtype=p.dtype)
         self.cache.layer_offset = model.model.layer_lo
+        from .graph_decode import YvDecodeGraphRunner
+        self.graph = YvDecodeGraphRunner(model, self.cache, min(self.cfg.max_model_len, self.cfg.graph_max_seq_len),
+                                         enabled=self.cfg.use_cuda_graphs)
         self.waiting: Deque[YvRequest] = deque()
         self.running: List[YvRequest] = []
         self._next_id = 0
@@ -133,8 +138,7 @@ class YvInferenceEngine:
             return
         # decode: one token for every running sequence in a single batched step
         seq_ids = [r.request_id for r in self.running]
-        last = torch.tensor([r.output_ids[-1] for r in self.running], dtype=torch.long, device=self.device)
-        logits = _decode_step(self.model, last, self.cache, seq_ids)
+        logits = self.graph.step([r.output_ids[-1] for r in self.running], seq_ids)
         greedy = all(r.sampling.strategy == "greedy" for r in self.running)
         if greedy:
             toks = logits.argmax(-1).tolist()
@@ -190,6 +194,7 @@ class YvInferenceEngine:
         s["mean_latency"] = sum(lat) / len(lat) if lat else None
         s["running"], s["waiting"] = len(self.running), len(self.waiting)
         s["free_blocks"] = self.cache.alloc.available()
+        s["decode_graphs"] = self.graph.stats()
         return s
 
 

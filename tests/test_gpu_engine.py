@@ -73,3 +73,32 @@ def test_serving_engine_on_gpu_matches_generate():
     for p, r in zip(prompts, reqs):
         ref, _ = m.generate(torch.tensor([p], device="cuda"), max_new_tokens=5, eos_token_id=-1)
         assert r.output_ids == ref[0, len(p):].tolist()
+    g = eng.get_stats()["decode_graphs"]
+    assert g["disabled_reason"] is None and g["graph_replays"] >= 4 and g["eager_steps"] == 0 and g["buckets"] == [4]
+
+
+def test_graph_decode_equals_eager_decode_across_buckets_and_block_boundaries():
+    from pisceslx_b200.serve.engine import YvEngineConfig, YvInferenceEngine
+    m = build_model(_tiny(), "cuda", torch.bfloat16, seed=5).eval()
+    outs = []
+    for graphs in (True, False):
+        eng = YvInferenceEngine(m, cfg=YvEngineConfig(max_num_seqs=8, num_blocks=64, block_size=64, eos_token_id=-1,
+                                                      use_cuda_graphs=graphs, graph_max_seq_len=256))
+        # different lengths: requests finish at different steps, so the batch shrinks through buckets 8 -> 4 -> 2 -> 1;
+        # the 60-token prompt crosses a cache-block boundary while decoding
+        reqs = [eng.add_request([3 + i] * n, max_new_tokens=k) for i, (n, k) in
+                enumerate([(60, 12), (5, 3), (9, 7), (17, 9), (2, 2)])]
+        eng.run_until_done()
+        outs.append([r.output_ids for r in reqs])
+        st = eng.get_stats()["decode_graphs"]
+        if graphs:
+            assert st["disabled_reason"] is None and st["graph_replays"] > 0 and len(st["buckets"]) >= 3
+        else:
+            assert st["graph_replays"] == 0 and st["eager_steps"] > 0
+    assert outs[0] == outs[1]
+    # a sequence longer than the graph's table width falls back to the eager step
+    eng = YvInferenceEngine(m, cfg=YvEngineConfig(max_num_seqs=2, num_blocks=64, block_size=64, eos_token_id=-1,
+                                                  graph_max_seq_len=256))
+    r = eng.add_request([7] * 300, max_new_tokens=3)
+    eng.run_until_done()
+    assert len(r.output_ids) == 3 and eng.get_stats()["decode_graphs"]["eager_steps"] > 0

@@ -99,3 +99,18 @@ def test_seal_and_solar():
     assert sol.scale[0] > 2.0                       # gradients kept their sign: the step size grew
     plain = torch.tensor([5.0, -3.0]) * (1 - 0.02) ** 10
     assert w.detach().abs().sum() < plain.abs().sum()
+
+
+def test_graph_decode_runner_falls_back_on_cpu():
+    from pisceslx_b200.serve.engine import YvEngineConfig, YvInferenceEngine
+    m = build_model(tiny())
+    m.eval()
+    eng = YvInferenceEngine(m, cfg=YvEngineConfig(max_num_seqs=2, num_blocks=16, block_size=16, eos_token_id=-1))
+    free0 = eng.cache.alloc.available()
+    r = eng.add_request([5, 6, 7], max_new_tokens=4)
+    eng.run_until_done()
+    ref, _ = m.generate(torch.tensor([[5, 6, 7]]), max_new_tokens=4, eos_token_id=-1)
+    st = eng.get_stats()["decode_graphs"]
+    assert r.output_ids == ref[0, 3:].tolist()
+    assert st["disabled_reason"] == "no CUDA device" and st["eager_steps"] == 3 and st["graph_replays"] == 0
+    assert eng.cache.alloc.available() == free0          # nothing reserved for padding when graphs are off
