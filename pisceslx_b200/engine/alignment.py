@@ -281,3 +281,88 @@ def grow_depth(model: Any, positions: Sequence[int]) -> None:
     model.model.layers = torch.nn.ModuleList(layers)
     model.cfg.n_layer = len(layers)
     model.model.layer_hi = len(layers)
+
+
+def grow_expert_width(layer: Any, new_ffn: int) -> None:
+    """Width growth of the routed experts (function preserving): the FFN dimension grows from F to ``new_ffn``; new
+    gate/up rows are small random, the matching new columns of the down projection are zero, so the layer's output is
+    unchanged until training moves them."""
+    w13, w2 = layer.experts_w13.data, layer.experts_w2.data          # [E, 2F, H], [E, H, F]
+    E, twoF, H = w13.shape
+    F = twoF // 2
+    assert new_ffn >= F
+    g13 = torch.zeros(E, 2 * new_ffn, H, dtype=w13.dtype, device=w13.device)
+    g13[:, :F], g13[:, new_ffn:new_ffn + F] = w13[:, :F], w13[:, F:]
+    g13[:, F:new_ffn].normal_(std=0.02)
+    g13[:, new_ffn + F:].normal_(std=0.02)
+    g2 = torch.zeros(E, H, new_ffn, dtype=w2.dtype, device=w2.device)
+    g2[:, :, :F] = w2
+    layer.experts_w13, layer.experts_w2 = torch.nn.Parameter(g13), torch.nn.Parameter(g2)
+    layer.ffn = new_ffn
+
+
+# --------------------------------------------------------------------------------------------------
+# self-play and weak-to-strong (reference opss/train: self-play fine-tuning, weak-to-strong generalisation)
+# --------------------------------------------------------------------------------------------------
+def spin_loss(pi_real: torch.Tensor, pi_synth: torch.Tensor, ref_real: torch.Tensor, ref_synth: torch.Tensor,
+              beta: float = 0.1) -> torch.Tensor:
+    """Self-play fine-tuning: the current policy must prefer the data's response over the one its previous iterate
+    (the opponent, also the reference) generated for the same prompt: logistic loss on the margin of log-ratios."""
+    margin = beta * ((pi_real - ref_real) - (pi_synth - ref_synth))
+    return -torch.nn.functional.logsigmoid(margin).mean()
+
+
+class PiscesLxSelfPlayTrainer:
+    """Iterated self-play: each round freezes a copy of the policy as opponent, has it answer the prompts
+    (``generate_fn(opponent, prompt_ids) -> response_ids``), and trains the policy with ``spin_loss`` to tell the
+    data's responses from the opponent's.  ``logprob_fn(model, prompt_ids, response_ids) -> summed log-prob``."""
+
+    def __init__(self, policy: torch.nn.Module, optimizer: torch.optim.Optimizer, generate_fn, logprob_fn,
+                 beta: float = 0.1):
+        self.policy, self.opt, self.generate_fn, self.logprob_fn, self.beta = policy, optimizer, generate_fn, logprob_fn, beta
+        self.opponent: Optional[torch.nn.Module] = None
+        self.round = 0
+
+    def start_round(self) -> None:
+        self.opponent = copy.deepcopy(self.policy).eval()
+        for p in self.opponent.parameters():
+            p.requires_grad_(False)
+        self.round += 1
+
+    def step(self, prompts: Sequence[torch.Tensor], responses: Sequence[torch.Tensor]) -> Dict[str, float]:
+        if self.opponent is None:
+            self.start_round()
+        with torch.no_grad():
+            synth = [self.generate_fn(self.opponent, p) for p in prompts]
+            ref_real = torch.stack([self.logprob_fn(self.opponent, p, r) for p, r in zip(prompts, responses)])
+            ref_synth = torch.stack([self.logprob_fn(self.opponent, p, s) for p, s in zip(prompts, synth)])
+        pi_real = torch.stack([self.logprob_fn(self.policy, p, r) for p, r in zip(prompts, responses)])
+        pi_synth = torch.stack([self.logprob_fn(self.policy, p, s) for p, s in zip(prompts, synth)])
+        loss = spin_loss(pi_real, pi_synth, ref_real, ref_synth, self.beta)
+        self.opt.zero_grad(set_to_none=True)
+        loss.backward()
+        self.opt.step()
+        return {"loss": float(loss.detach()), "margin": float(((pi_real - ref_real) - (pi_synth - ref_synth)).mean().detach()),
+                "round": self.round}
+
+
+class PiscesLxWeakToStrongTrainer:
+    """Weak-to-strong generalisation: a strong student is trained on a weak supervisor's labels with the auxiliary
+    confidence loss (``weak_to_strong_loss``): as training proceeds the student's own hardened predictions get weight
+    ``alpha`` (warmed up linearly), so it can overrule the supervisor's mistakes."""
+
+    def __init__(self, student: torch.nn.Module, optimizer: torch.optim.Optimizer, alpha_max: float = 0.5,
+                 warmup_steps: int = 100):
+        self.student, self.opt, self.alpha_max, self.warmup = student, optimizer, alpha_max, warmup_steps
+        self.steps = 0
+
+    def step(self, inputs: torch.Tensor, weak_labels: torch.Tensor) -> Dict[str, float]:
+        alpha = self.alpha_max * min(1.0, self.steps / max(1, self.warmup))
+        logits = self.student(inputs)
+        loss = weak_to_strong_loss(logits, weak_labels, alpha)
+        self.opt.zero_grad(set_to_none=True)
+        loss.backward()
+        self.opt.step()
+        self.steps += 1
+        agree = float((logits.argmax(-1) == weak_labels).float().mean())
+        return {"loss": float(loss.detach()), "alpha": alpha, "agreement_with_weak": agree}
