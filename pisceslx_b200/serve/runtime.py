@@ -169,3 +169,96 @@ class PiscesLxTPO:
             ctx = (f"{prompt}\nA weaker answer was:\n{scored[0][1]}\nA stronger answer was:\n{scored[-1][1]}\n"
                    f"Write an answer better than both.\n")
         return {"answer": best, "reward": best_r}
+
+
+class PiscesLxTriRouteDecision(torch.nn.Module):
+    """One small router that decides three things per token from its hidden state (reference
+    opss/infer/moe_runtime.py:1391): the attention mode per head (full / sparse / linear), an additive adjustment of the
+    expert logits, and the KV-cache bit width for the token (one of ``bit_options``)."""
+
+    def __init__(self, hidden: int, n_head: int, n_experts: int, n_modes: int = 3,
+                 bit_options: Tuple[int, ...] = (2, 4, 8, 16), bottleneck: int = 64):
+        super().__init__()
+        self.n_head, self.n_modes, self.bit_options = n_head, n_modes, tuple(bit_options)
+        self.trunk = torch.nn.Sequential(torch.nn.Linear(hidden, bottleneck), torch.nn.GELU())
+        self.mode_head = torch.nn.Linear(bottleneck, n_head * n_modes)
+        self.expert_head = torch.nn.Linear(bottleneck, n_experts)
+        self.bit_head = torch.nn.Linear(bottleneck, len(bit_options))
+        torch.nn.init.zeros_(self.expert_head.weight)
+        torch.nn.init.zeros_(self.expert_head.bias)
+
+    def forward(self, h: torch.Tensor) -> Dict[str, torch.Tensor]:
+        z = self.trunk(h.float())
+        mode_logits = self.mode_head(z).view(*h.shape[:-1], self.n_head, self.n_modes)
+        bit_logits = self.bit_head(z)
+        bits = torch.tensor(self.bit_options, device=h.device)[bit_logits.argmax(-1)]
+        return {"attention_mode": mode_logits.argmax(-1), "mode_logits": mode_logits,
+                "expert_logit_delta": self.expert_head(z), "kv_bits": bits, "bit_logits": bit_logits}
+
+    def cost(self, out: Dict[str, torch.Tensor], mode_cost: Tuple[float, ...] = (1.0, 0.35, 0.1)) -> torch.Tensor:
+        """Differentiable expected compute / memory cost (for training the router against a quality loss)."""
+        pm = torch.softmax(out["mode_logits"], -1)
+        pb = torch.softmax(out["bit_logits"], -1)
+        mc = torch.tensor(mode_cost[: self.n_modes], device=pm.device)
+        bc = torch.tensor(self.bit_options, device=pb.device, dtype=torch.float32) / 16.0
+        return (pm * mc).sum(-1).mean() + (pb * bc).sum(-1).mean()
+
+
+class PiscesLxBrownoutMoEGrouper:
+    """Experts are clustered into co-activation groups (experts that fire together go together); at run time groups
+    whose running importance falls under ``threshold`` are switched off and the router's logits for their experts
+    are masked, trading a little quality for throughput under load (reference :1451-1560)."""
+
+    def __init__(self, n_experts: int, group_size: int = 4, threshold: float = 0.3, ema: float = 0.1,
+                 min_active_groups: int = 1):
+        self.E, self.gs, self.thr, self.ema, self.min_active = n_experts, group_size, threshold, ema, min_active_groups
+        self.groups: List[List[int]] = [list(range(i, min(i + group_size, n_experts))) for i in range(0, n_experts, group_size)]
+        self.importance = [1.0] * len(self.groups)
+        self.active = [True] * len(self.groups)
+
+    def fit(self, idx: torch.Tensor) -> None:
+        """Greedy grouping from routing decisions idx [T, k]: repeatedly seed a group with the busiest unassigned
+        expert and add the unassigned experts that co-occur with the group most."""
+        onehot = torch.zeros(idx.shape[0], self.E).scatter_(1, idx.long().cpu(), 1.0)
+        co = onehot.t() @ onehot
+        load = co.diagonal().clone()
+        co.fill_diagonal_(0)
+        free = set(range(self.E))
+        groups = []
+        while free:
+            seed = max(free, key=lambda e: float(load[e]))
+            g = [seed]
+            free.discard(seed)
+            while len(g) < self.gs and free:
+                nxt = max(free, key=lambda e: float(co[g, e].sum()))
+                g.append(nxt)
+                free.discard(nxt)
+            groups.append(sorted(g))
+        self.groups = groups
+        self.importance, self.active = [1.0] * len(groups), [True] * len(groups)
+
+    def observe(self, weights: torch.Tensor, idx: torch.Tensor) -> None:
+        """Updates group importance from one batch of routing (share of the routed weight that went to the group,
+        relative to a uniform share)."""
+        mass = torch.zeros(self.E).scatter_add_(0, idx.flatten().long().cpu(), weights.flatten().float().cpu())
+        total = float(mass.sum()) or 1.0
+        for g, members in enumerate(self.groups):
+            rel = float(mass[members].sum()) / total * len(self.groups)
+            self.importance[g] = (1 - self.ema) * self.importance[g] + self.ema * rel
+
+    def brownout(self, load_factor: float) -> List[int]:
+        """Switches groups off while the server is overloaded (``load_factor`` > 1 scales the threshold up); returns the
+        ids of inactive groups.  The ``min_active_groups`` most important groups always stay on."""
+        thr = self.thr * max(0.0, load_factor)
+        order = sorted(range(len(self.groups)), key=lambda g: -self.importance[g])
+        keep = set(order[: self.min_active])
+        self.active = [g in keep or self.importance[g] >= thr for g in range(len(self.groups))]
+        return [g for g, a in enumerate(self.active) if not a]
+
+    def logit_mask(self, device=None) -> torch.Tensor:
+        """Additive mask [E] for the router logits: -inf on experts of inactive groups."""
+        m = torch.zeros(self.E, device=device)
+        for g, members in enumerate(self.groups):
+            if not self.active[g]:
+                m[members] = float("-inf")
+        return m

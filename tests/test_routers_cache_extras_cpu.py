@@ -72,6 +72,34 @@ def test_modal_aware_and_ultra_sparse_gates():
     assert us.scorer[0].weight.grad is not None
 
 
+def test_triroute_and_brownout_grouper():
+    from pisceslx_b200.serve.runtime import PiscesLxBrownoutMoEGrouper, PiscesLxTriRouteDecision
+    torch.manual_seed(5)
+    tr = PiscesLxTriRouteDecision(32, n_head=4, n_experts=8)
+    out = tr(torch.randn(6, 32))
+    assert out["attention_mode"].shape == (6, 4) and int(out["attention_mode"].max()) < 3
+    assert set(out["kv_bits"].tolist()) <= {2, 4, 8, 16} and float(out["expert_logit_delta"].abs().max()) == 0.0
+    c = tr.cost(out)
+    c.backward()
+    assert tr.mode_head.weight.grad is not None and 0 < float(c) < 2
+    g = PiscesLxBrownoutMoEGrouper(8, group_size=2, threshold=0.5)
+    # experts (0, 5), (1, 4), (2, 7), (3, 6) always fire together
+    pairs = torch.tensor([[0, 5], [1, 4], [2, 7], [3, 6]])
+    idx = pairs[torch.randint(0, 4, (200,))]
+    g.fit(idx)
+    assert sorted(map(tuple, g.groups)) == [(0, 5), (1, 4), (2, 7), (3, 6)]
+    hot = pairs[torch.tensor([0] * 150 + [1] * 45 + [2] * 5)]          # pair (3, 6) never used, (2, 7) rarely
+    for _ in range(40):
+        g.observe(torch.full((200, 2), 0.5), hot)
+    off = g.brownout(load_factor=1.0)
+    off_groups = sorted(tuple(g.groups[i]) for i in off)
+    assert off_groups == [(2, 7), (3, 6)]
+    m = g.logit_mask()
+    assert torch.isinf(m[[2, 7, 3, 6]]).all() and (m[[0, 5, 1, 4]] == 0).all()
+    assert g.brownout(load_factor=0.0) == []                            # no load: everything stays on
+    assert len(g.brownout(load_factor=100.0)) == 3                      # the most important group always stays
+
+
 def test_kv_ring_and_lynx_quantizer():
     from pisceslx_b200.models.cache_extras import YvKVCacheRing, YvLynxKVQuantizer
     torch.manual_seed(3)
