@@ -92,6 +92,89 @@ class PiscesLxTWLAQuantizer:
         return (q["alpha"] * q["ternary"].float() + q["A"] @ q["B"]).to(dtype)
 
 
+class YvQuantizationConfig:
+    """quantization_type: int8 | int4 | fp8 | fp16 | bf16 (reference model/utils/quantization.py:100-290);
+    per_channel scales along the output dimension; symmetric or with a zero point."""
+
+    def __init__(self, quantization_type: str = "int8", per_channel: bool = True, symmetric: bool = True,
+                 skip_modules: Tuple[str, ...] = ("lm_head", "embed", "router", "norm")):
+        if quantization_type not in ("int8", "int4", "fp8", "fp16", "bf16"):
+            raise ValueError(f"unsupported quantization type {quantization_type!r}")
+        self.quantization_type, self.per_channel, self.symmetric = quantization_type, per_channel, symmetric
+        self.skip_modules = tuple(skip_modules)
+
+
+class _YvQuantizedLinear(torch.nn.Module):
+    """Weight-only quantised linear: integer (or fp8) weights + scale (+ zero point), dequantised per call."""
+
+    def __init__(self, q_weight, scale, zero_point, bias, kind: str):
+        super().__init__()
+        self.register_buffer("q_weight", q_weight)
+        self.register_buffer("scale", scale)
+        self.register_buffer("zero_point", zero_point if zero_point is not None else torch.zeros(()))
+        self.bias, self.kind = bias, kind
+
+    def weight(self, dtype: torch.dtype) -> torch.Tensor:
+        return ((self.q_weight.float() - self.zero_point) * self.scale).to(dtype)
+
+    def forward(self, x):
+        return torch.nn.functional.linear(x, self.weight(x.dtype), None if self.bias is None else self.bias.to(x.dtype))
+
+
+class YvQuantizer:
+    """Tensor / module / model level weight quantisation (reference ``YvQuantizer`` :292-485)."""
+
+    def __init__(self, config: Optional[YvQuantizationConfig] = None):
+        self.config = config or YvQuantizationConfig()
+        self.records: Dict[str, Dict[str, torch.Tensor]] = {}
+
+    def quantize_tensor(self, w: torch.Tensor) -> Dict[str, torch.Tensor]:
+        c, t = self.config, self.config.quantization_type
+        x = w.float()
+        if t in ("fp16", "bf16"):
+            return {"q": x.to(torch.float16 if t == "fp16" else torch.bfloat16), "scale": torch.ones(()), "zero": torch.zeros(())}
+        dim = tuple(range(1, x.dim())) if c.per_channel and x.dim() > 1 else None
+        if t == "fp8":
+            amax = x.abs().amax(dim, keepdim=True) if dim else x.abs().max()
+            s = amax.clamp_min(1e-12) / 448.0
+            return {"q": (x / s).to(torch.float8_e4m3fn), "scale": s, "zero": torch.zeros(())}
+        bits = 8 if t == "int8" else 4
+        if c.symmetric:
+            qmax = 2 ** (bits - 1) - 1
+            amax = x.abs().amax(dim, keepdim=True) if dim else x.abs().max()
+            s = amax.clamp_min(1e-12) / qmax
+            return {"q": torch.round(x / s).clamp(-qmax - 1, qmax).to(torch.int8), "scale": s, "zero": torch.zeros(())}
+        lo = x.amin(dim, keepdim=True) if dim else x.min()
+        hi = x.amax(dim, keepdim=True) if dim else x.max()
+        s = ((hi - lo) / (2 ** bits - 1)).clamp_min(1e-12)
+        z = torch.round(-lo / s)
+        return {"q": (torch.round(x / s) + z).clamp(0, 2 ** bits - 1).to(torch.uint8), "scale": s, "zero": z}
+
+    @staticmethod
+    def dequantize_tensor(r: Dict[str, torch.Tensor], dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        return ((r["q"].float() - r["zero"]) * r["scale"]).to(dtype)
+
+    def quantize_linear(self, lin: torch.nn.Linear) -> _YvQuantizedLinear:
+        r = self.quantize_tensor(lin.weight.data)
+        return _YvQuantizedLinear(r["q"], r["scale"], r["zero"], lin.bias, self.config.quantization_type)
+
+    def quantize_model(self, model: torch.nn.Module) -> int:
+        """Replaces every ``nn.Linear`` not matched by ``skip_modules`` in place; returns how many were replaced."""
+        n = 0
+        for name, mod in list(model.named_modules()):
+            for cname, child in list(mod.named_children()):
+                full = f"{name}.{cname}" if name else cname
+                if isinstance(child, torch.nn.Linear) and not any(s in full for s in self.config.skip_modules):
+                    q = self.quantize_linear(child)
+                    setattr(mod, cname, q)
+                    self.records[full] = {"q": q.q_weight, "scale": q.scale, "zero": q.zero_point}
+                    n += 1
+        return n
+
+    def get_state_dict(self) -> Dict[str, torch.Tensor]:
+        return {f"{k}.{f}": v for k, r in self.records.items() for f, v in r.items()}
+
+
 class PiscesLxSTARKVQuantizer:
     """KV-cache quantisation that keeps the ``keep`` most attended tokens (by accumulated attention mass) in full
     precision and stores the rest as per-token int``bits`` with a scale and a zero point."""

@@ -143,6 +143,34 @@ def test_twla_and_star_kv():
     assert float((d - kv).abs().max()) < float((kv[torch.arange(64) != 5].abs().max())) / 7
 
 
+def test_yv_quantizer_types_and_model_swap():
+    from pisceslx_b200.quant.extras import YvQuantizationConfig, YvQuantizer
+    torch.manual_seed(0)
+    w = torch.randn(16, 64)
+    err = {}
+    for t in ("int4", "int8", "fp8", "bf16", "fp16"):
+        q = YvQuantizer(YvQuantizationConfig(t))
+        r = q.quantize_tensor(w)
+        err[t] = float((q.dequantize_tensor(r) - w).norm() / w.norm())
+    assert err["int4"] > err["int8"] > err["fp16"] and err["fp8"] < 0.05 and err["int8"] < 0.01
+    asym = YvQuantizer(YvQuantizationConfig("int8", symmetric=False))
+    shifted = w + 3.0
+    ea = float((asym.dequantize_tensor(asym.quantize_tensor(shifted)) - shifted).norm() / shifted.norm())
+    sym = YvQuantizer(YvQuantizationConfig("int8"))
+    es = float((sym.dequantize_tensor(sym.quantize_tensor(shifted)) - shifted).norm() / shifted.norm())
+    assert ea < es                                  # a zero point pays off on shifted data
+    net = nn.Sequential()
+    net.add_module("proj", nn.Linear(64, 32))
+    net.add_module("lm_head", nn.Linear(32, 10))
+    x = torch.randn(4, 64)
+    ref = net(x)
+    qz = YvQuantizer(YvQuantizationConfig("int8"))
+    assert qz.quantize_model(net) == 1 and isinstance(net.lm_head, nn.Linear)
+    assert float((net(x) - ref).abs().max()) < 0.05 and "proj.q" in qz.get_state_dict()
+    with pytest.raises(ValueError):
+        YvQuantizationConfig("int3")
+
+
 def test_kfac_preconditioner_whitens_gradient():
     from pisceslx_b200.optim.kfac import PiscesLxKFACPreconditioner
     torch.manual_seed(0)
