@@ -303,39 +303,47 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
     const int64_t total = static_cast<int64_t>(tiles_m - bpr) * vpb;
     const int64_t lanes = static_cast<int64_t>(gridDim.x) * kCopierWarps * 32;
     const int64_t me = (static_cast<int64_t>(blockIdx.x) * kCopierWarps + (warp - 6)) * 32 + lane;
+    // 64-bit divisions cost a few hundred instructions each on this machine: the block index of a vector is taken
+    // with a shift when the block holds a power-of-two number of vectors (K a power of two), and is computed once
+    // per vector and kept in registers for the store and the counting below.
+    const int vshift = (vpb & (vpb - 1)) == 0 ? 63 - __clzll(vpb) : -1;
+    const int rot = bpr + p.comm_rank * bpr;               // < tiles_m: one conditional subtraction wraps lb + rot
     for (int64_t base = 0; base < total; base += lanes * kRound) {
       uint4 v[kRound];
-      int64_t g[kRound];
+      int lbv[kRound];                                     // block of vector u in copy order, -1 past the end
+      int64_t dst[kRound];                                 // its offset (in vectors) in the local gathered matrix
 #pragma unroll
       for (int u = 0; u < kRound; ++u) {
-        g[u] = base + static_cast<int64_t>(u) * lanes + me;
-        if (g[u] < total) {
-          const int lb = static_cast<int>(g[u] / vpb);
-          const int phys = (lb + bpr + p.comm_rank * bpr) % tiles_m;
+        const int64_t g = base + static_cast<int64_t>(u) * lanes + me;
+        lbv[u] = -1;
+        if (g < total) {
+          const int lb = vshift >= 0 ? static_cast<int>(g >> vshift) : static_cast<int>(g / vpb);
+          const int64_t within = g - static_cast<int64_t>(lb) * vpb;
+          int phys = lb + rot;
+          if (phys >= tiles_m) phys -= tiles_m;
           const int owner = phys / bpr;
-          const int64_t off = static_cast<int64_t>(phys - owner * bpr) * vpb + (g[u] - static_cast<int64_t>(lb) * vpb);
-          v[u] = ld_peer_v4(reinterpret_cast<const uint4*>(p.comm_peer[owner]) + off);
+          lbv[u] = lb;
+          dst[u] = static_cast<int64_t>(phys) * vpb + within;
+          v[u] = ld_peer_v4(reinterpret_cast<const uint4*>(p.comm_peer[owner]) +
+                            (static_cast<int64_t>(phys - owner * bpr) * vpb + within));
         }
       }
 #pragma unroll
-      for (int u = 0; u < kRound; ++u) {
-        if (g[u] < total) {
-          const int lb = static_cast<int>(g[u] / vpb);
-          const int phys = (lb + bpr + p.comm_rank * bpr) % tiles_m;
-          reinterpret_cast<uint4*>(p.comm_local)[static_cast<int64_t>(phys) * vpb + (g[u] - static_cast<int64_t>(lb) * vpb)] = v[u];
-        }
-      }
+      for (int u = 0; u < kRound; ++u)
+        if (lbv[u] >= 0) reinterpret_cast<uint4*>(p.comm_local)[dst[u]] = v[u];
       __threadfence();
       // blocks touched by this round (identical for every lane of the grid)
-      const int lb_first = static_cast<int>(base / vpb);
       const int64_t round_end = (base + lanes * kRound < total ? base + lanes * kRound : total) - 1;
-      const int lb_last = static_cast<int>(round_end / vpb);
+      const int lb_first = vshift >= 0 ? static_cast<int>(base >> vshift) : static_cast<int>(base / vpb);
+      const int lb_last = vshift >= 0 ? static_cast<int>(round_end >> vshift) : static_cast<int>(round_end / vpb);
       for (int lb = lb_first; lb <= lb_last; ++lb) {
         int mine = 0;
 #pragma unroll
-        for (int u = 0; u < kRound; ++u) mine += (g[u] < total && static_cast<int>(g[u] / vpb) == lb) ? 1 : 0;
+        for (int u = 0; u < kRound; ++u) mine += (lbv[u] == lb) ? 1 : 0;
         const int cnt = __reduce_add_sync(0xFFFFFFFFu, mine);
-        if (lane == 0 && cnt > 0) atomicAdd(p.comm_flags + (lb + bpr + p.comm_rank * bpr) % tiles_m, static_cast<uint32_t>(cnt));
+        int phys = lb + rot;
+        if (phys >= tiles_m) phys -= tiles_m;
+        if (lane == 0 && cnt > 0) atomicAdd(p.comm_flags + phys, static_cast<uint32_t>(cnt));
       }
     }
   } else if (warp >= 6) {

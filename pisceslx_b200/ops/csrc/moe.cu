@@ -195,25 +195,32 @@ __global__ void gate_topk_bwd_kernel(const float* __restrict__ dweights, const f
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ seg_offsets,
                                 int* __restrict__ tile_expert, int* __restrict__ num_m_tiles,
                                 int* __restrict__ cursor, int E, int max_tiles) {
+  // launched with 256 threads and E <= 256: thread e owns expert e; the padded sizes are scanned in shared memory
   __shared__ int s_off[257];
-  if (threadIdx.x == 0) {
-    int off = 0;
-    for (int e = 0; e < E; ++e) {
-      s_off[e] = off;
-      off += ((counts[e] + 127) / 128) * 128;
-    }
-    s_off[E] = off;
-    int tiles = off / 128;
+  __shared__ int s_scan[256];
+  const int tid = threadIdx.x;
+  s_scan[tid] = tid < E ? ((counts[tid] + 127) / 128) * 128 : 0;
+  __syncthreads();
+  for (int d = 1; d < 256; d <<= 1) {
+    const int v = tid >= d ? s_scan[tid - d] : 0;
+    __syncthreads();
+    s_scan[tid] += v;
+    __syncthreads();
+  }
+  if (tid == 0) s_off[0] = 0;
+  if (tid < E) s_off[tid + 1] = s_scan[tid];
+  __syncthreads();
+  if (tid == 0) {
+    const int tiles = s_off[E] / 128;
     *num_m_tiles = tiles < max_tiles ? tiles : max_tiles;
   }
-  __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+  for (int e = tid; e <= E; e += blockDim.x) {
     seg_offsets[e] = s_off[e];
     if (e < E) cursor[e] = s_off[e];
   }
-  for (int e = 0; e < E; ++e) {
-    const int t0 = s_off[e] / 128, t1 = s_off[e + 1] / 128;
-    for (int t = t0 + threadIdx.x; t < t1 && t < max_tiles; t += blockDim.x) tile_expert[t] = e;
+  if (tid < E) {
+    const int t0 = s_off[tid] / 128, t1 = s_off[tid + 1] / 128;
+    for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = tid;
   }
 }
 

@@ -59,7 +59,9 @@ def _splitk_plan(M: int, N: int, K: int) -> int:
     tiles_n = (N + 255) // 256
     if tiles_n >= 74:
         return 0
-    want = min(16, -(-148 // tiles_n))
+    # the kernel is persistent with one CTA per SM and a static round-robin over work items: tiles_n * slices must not
+    # exceed 148, or a second, nearly empty wave doubles the time
+    want = min(16, 148 // tiles_n)
     slices = max(1, min(want, K // 256))
     return slices if slices > 1 else 0
 

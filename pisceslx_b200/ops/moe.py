@@ -81,8 +81,10 @@ def padded_rows_bound(num_assignments: int, num_experts: int) -> int:
 
 
 def permute_tokens(x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor, num_experts: int,
-                   deterministic: bool = False) -> Tuple[torch.Tensor, DispatchPlan]:
-    """Scatter token rows into expert-sorted order.  Returns (xp [max_rows, H], plan)."""
+                   deterministic: bool = False, zero_pad: bool = True) -> Tuple[torch.Tensor, DispatchPlan]:
+    """Scatter token rows into expert-sorted order.  Returns (xp [max_rows, H], plan).  The pad rows of every expert
+    segment are zeroed unless ``zero_pad`` is off: the weight-gradient GEMMs sum over whole segments, so training
+    needs zeros there; inference never reads what the pad rows produce."""
     T, H = x.shape
     k = idx.shape[1]
     dev = x.device
@@ -107,20 +109,21 @@ def permute_tokens(x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor, num
         K.moe_permute(x, idx, None, row_map, xp)
     else:
         K.moe_permute(x, idx, cursor, row_map, xp)
-    K.moe_zero_pad(xp, seg, counts)
+    if zero_pad:
+        K.moe_zero_pad(xp, seg, counts)
     return xp, DispatchPlan(seg, tile_expert, num_tiles, row_map, counts, max_rows, k)
 
 
 class _MoEExpertsFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w13, w2, weights, idx, counts, deterministic):
+    def forward(ctx, x, w13, w2, weights, idx, counts, deterministic, training=True):
         K = _k()
         st = status_word(x.device)
         T, H = x.shape
         E, twoF, _ = w13.shape
         F = twoF // 2
         x = x.contiguous()
-        xp, plan = permute_tokens(x, idx, counts, E, deterministic)
+        xp, plan = permute_tokens(x, idx, counts, E, deterministic, zero_pad=training)
         y1 = torch.empty(plan.max_rows, twoF, dtype=_BF16, device=x.device)
         K.gemm_grouped_m(xp, w13, y1, plan.tile_expert, plan.num_m_tiles, False, 0, st)
         act = torch.empty(plan.max_rows, F, dtype=_BF16, device=x.device)
@@ -166,7 +169,7 @@ class _MoEExpertsFn(torch.autograd.Function):
         K.gemm_grouped_k(dy1, xp, dw13, seg, False, 0, st)
         dx = torch.empty(T, H, dtype=_BF16, device=dev)
         K.moe_unpermute_sum(dxp, row_map, dx, k)
-        return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None
+        return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None, None
 
 
 def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor,
@@ -180,7 +183,9 @@ def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: t
     E = w13.shape[0]
     if counts is None:
         counts = torch.bincount(idx.flatten().long(), minlength=E).int()
-    return _MoEExpertsFn.apply(x.to(_BF16), w13, w2, weights, idx.int(), counts.int(), deterministic)
+    # without autograd (inference) nothing reads what the pad rows of the expert segments produce: skip zeroing them
+    return _MoEExpertsFn.apply(x.to(_BF16), w13, w2, weights, idx.int(), counts.int(), deterministic,
+                               torch.is_grad_enabled())
 
 
 def update_gate_bias(bias: torch.Tensor, counts: torch.Tensor, rate: float, clamp: float = 2.0) -> None:
