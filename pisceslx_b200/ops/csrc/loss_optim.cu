@@ -123,6 +123,69 @@ __global__ void adamw_kernel(AdamWArgs a) {
   }
 }
 
+// Eight bf16 values per 16-byte access: the optimizer's streaming kernels below move tens of GB per step and are
+// bound by memory, which 2-byte accesses per thread do not saturate.  Rounding is the same as in the scalar kernels.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return u;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// vector form of momentum_kernel over nvec = n / 8 vectors (the launcher runs the scalar kernel on the tail)
+__global__ void momentum_vec_kernel(uint4* __restrict__ m, const uint4* __restrict__ g, uint4* __restrict__ out,
+                                    int64_t nvec, float mu, float gscale, int nesterov, int first_fold) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float gv[8], mv[8], ov[8];
+    unpack8(g[i], gv);
+    unpack8(m[i], mv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gv[j] *= gscale;
+      if (first_fold) mv[j] *= mu;
+      mv[j] += gv[j];
+    }
+    const uint4 packed = pack8(mv);
+    m[i] = packed;
+    if (out != nullptr) {
+      if (nesterov) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ov[j] = gv[j] + mu * mv[j];      // unrounded momentum, as in the scalar kernel
+        out[i] = pack8(ov);
+      } else {
+        out[i] = packed;
+      }
+    }
+  }
+}
+
+__global__ void muon_apply_vec_kernel(uint4* __restrict__ p, const uint4* __restrict__ u, int64_t nvec, float lr,
+                                      float wd, float scale) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float pv[8], uv[8];
+    unpack8(p[i], pv);
+    unpack8(u[i], uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) pv[j] = pv[j] * (1.f - lr * wd) - lr * scale * uv[j];
+    p[i] = pack8(pv);
+  }
+}
+
 // m <- (first_fold ? mu * m : m) + gscale * g ;   out <- nesterov ? gscale*g + mu*m : m   (out optional)
 __global__ void momentum_kernel(__nv_bfloat16* __restrict__ m, const __nv_bfloat16* __restrict__ g,
                                 __nv_bfloat16* __restrict__ out, int64_t n, float mu, float gscale, int nesterov,
@@ -168,6 +231,35 @@ __global__ void frob_scale_kernel(__nv_bfloat16* __restrict__ x, const float* __
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < per_matrix;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     xm[i] = __float2bfloat16(__bfloat162float(xm[i]) * inv);
+  }
+}
+
+// vector forms of the two Frobenius kernels (per_matrix a multiple of 8, x 16-byte aligned)
+__global__ void frob_sumsq_vec_kernel(const uint4* __restrict__ x, float* __restrict__ norms, int64_t vec_per_matrix) {
+  const uint4* xm = x + static_cast<int64_t>(blockIdx.y) * vec_per_matrix;
+  float s = 0.f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < vec_per_matrix;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float v[8];
+    unpack8(xm[i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[j] * v[j];
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&norms[blockIdx.y], s);
+}
+
+__global__ void frob_scale_vec_kernel(uint4* __restrict__ x, const float* __restrict__ norms, int64_t vec_per_matrix,
+                                      float eps) {
+  uint4* xm = x + static_cast<int64_t>(blockIdx.y) * vec_per_matrix;
+  const float inv = 1.f / fmaxf(sqrtf(norms[blockIdx.y]), eps);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < vec_per_matrix;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float v[8];
+    unpack8(xm[i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= inv;
+    xm[i] = pack8(v);
   }
 }
 
@@ -337,20 +429,48 @@ int launch_adamw(const AdamWArgs& a, cudaStream_t stream) {
 int launch_momentum(void* m, const void* g, void* out, int64_t n, float mu, float gscale, int nesterov,
                     int first_fold, cudaStream_t stream) {
   if (n <= 0) return 0;
-  momentum_kernel<<<grid_for(n, 256), 256, 0, stream>>>(YV_BFM(m), YV_BF(g), YV_BFM(out), n, mu, gscale, nesterov,
-                                                        first_fold);
+  int64_t done = 0;
+  if (n >= 8 && aligned16(m) && aligned16(g) && aligned16(out)) {
+    const int64_t nvec = n / 8;
+    momentum_vec_kernel<<<grid_for(nvec, 256), 256, 0, stream>>>(
+        static_cast<uint4*>(m), static_cast<const uint4*>(g), static_cast<uint4*>(out), nvec, mu, gscale, nesterov,
+        first_fold);
+    done = nvec * 8;
+  }
+  if (done < n) {
+    momentum_kernel<<<grid_for(n - done, 256), 256, 0, stream>>>(
+        YV_BFM(m) + done, YV_BF(g) + done, out != nullptr ? YV_BFM(out) + done : nullptr, n - done, mu, gscale,
+        nesterov, first_fold);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
 int launch_muon_apply(void* p, const void* u, int64_t n, float lr, float wd, float scale, cudaStream_t stream) {
   if (n <= 0) return 0;
-  muon_apply_kernel<<<grid_for(n, 256), 256, 0, stream>>>(YV_BFM(p), YV_BF(u), n, lr, wd, scale);
+  int64_t done = 0;
+  if (n >= 8 && aligned16(p) && aligned16(u)) {
+    const int64_t nvec = n / 8;
+    muon_apply_vec_kernel<<<grid_for(nvec, 256), 256, 0, stream>>>(static_cast<uint4*>(p),
+                                                                   static_cast<const uint4*>(u), nvec, lr, wd, scale);
+    done = nvec * 8;
+  }
+  if (done < n)
+    muon_apply_kernel<<<grid_for(n - done, 256), 256, 0, stream>>>(YV_BFM(p) + done, YV_BF(u) + done, n - done, lr, wd,
+                                                                   scale);
   return static_cast<int>(cudaGetLastError());
 }
 
 int launch_frob_normalize(void* x, float* norms, int batch, int64_t per_matrix, float eps, cudaStream_t stream) {
   if (batch <= 0 || per_matrix <= 0) return 0;
   cudaMemsetAsync(norms, 0, sizeof(float) * batch, stream);
+  if ((per_matrix & 7) == 0 && aligned16(x)) {
+    const int64_t vpm = per_matrix / 8;
+    // enough CTAs in total to fill the machine a few times over, whatever the batch
+    int gx = grid_for(vpm, 256, batch >= 64 ? 32 : (148 * 8 + batch - 1) / batch);
+    frob_sumsq_vec_kernel<<<dim3(gx, batch), 256, 0, stream>>>(static_cast<const uint4*>(x), norms, vpm);
+    frob_scale_vec_kernel<<<dim3(gx, batch), 256, 0, stream>>>(static_cast<uint4*>(x), norms, vpm, eps);
+    return static_cast<int>(cudaGetLastError());
+  }
   int gx = grid_for(per_matrix, 256, 64);
   frob_sumsq_kernel<<<dim3(gx, batch), 256, 0, stream>>>(YV_BF(x), norms, per_matrix);
   frob_scale_kernel<<<dim3(gx, batch), 256, 0, stream>>>(YV_BFM(x), norms, per_matrix, eps);

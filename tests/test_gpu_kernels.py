@@ -387,6 +387,40 @@ def test_adamw_kernel(Y, pdt, sdt):
     assert rel(p, pr) < tol
 
 
+@pytest.mark.parametrize("n,offset", [(8 * 4096, 0), (10007, 0), (10007, 3), (5, 0)])
+@pytest.mark.parametrize("nesterov,first", [(True, True), (False, False), (True, False)])
+def test_muon_streaming_kernels_vector_and_tail(Y, n, offset, nesterov, first):
+    # 16-byte vector path, its scalar tail (n not a multiple of 8) and the scalar fallback (unaligned views)
+    torch.manual_seed(21)
+    base_m = torch.randn(n + 8, device=DEV).bfloat16()
+    base_g = torch.randn(n + 8, device=DEV).bfloat16()
+    base_o = torch.zeros(n + 8, device=DEV, dtype=torch.bfloat16)
+    m, g, out = base_m[offset:offset + n], base_g[offset:offset + n], base_o[offset:offset + n]
+    mu, gs = 0.95, 0.5
+    gv = g.float() * gs
+    mr = (m.float() * mu if first else m.float()) + gv
+    outr = gv + mu * mr if nesterov else mr
+    Y.momentum_fold(m, g, out, mu, gs, nesterov, first)
+    close = lambda a, b: torch.allclose(a.float(), b, rtol=2 ** -7, atol=1e-3)      # one bf16 ulp (FMA contraction)
+    assert close(m, mr) and close(out, outr)
+    assert float(base_o[offset + n:].abs().sum()) == 0 and float(base_o[:offset].abs().sum()) == 0
+    p = base_m[offset:offset + n].clone() if offset == 0 else base_m[offset:offset + n]
+    p0 = p.float().clone()
+    Y.muon_apply(p, g, 1e-2, 0.1, 0.7)
+    assert close(p, p0 * (1 - 1e-2 * 0.1) - 1e-2 * 0.7 * g.float())
+
+
+def test_frob_normalize_vector_and_scalar(Y):
+    torch.manual_seed(22)
+    for shape in ((5, 64, 96), (5, 7, 143)):
+        x = torch.randn(*shape, device=DEV).bfloat16()
+        ref = x.float() / x.float().flatten(1).norm(dim=1).view(-1, 1, 1)
+        sq = x.float().pow(2).sum((1, 2))
+        norms = torch.empty(5, device=DEV)
+        Y.frob_normalize(x, norms, 1e-7)
+        assert rel(x, ref) < 5e-3 and rel(norms, sq) < 1e-4
+
+
 def test_pq_gather_and_argmax(Y):
     from pisceslx_b200.ops import reference as ref
     torch.manual_seed(16)
