@@ -109,7 +109,8 @@ class YvModel(nn.Module):
             film = film_source.film_params(blk.layer_idx, h if delta is None else h + delta) \
                 if film_source is not None else None
             h, delta, aux = blk(h, delta, ctx, film)
-            aux_total = aux_total + aux.float()
+            if torch.is_grad_enabled():          # serving never reads the auxiliary loss: no add kernel per layer
+                aux_total = aux_total + aux.float()
         if film_source is not None:
             film_source.end()
         return (h, delta), aux_total

@@ -84,11 +84,24 @@ class YvStableMoEGate(nn.Module):
             pred = torch.softmax(self.load_head(h[:, -1]), -1).squeeze(0)
             return 0.1 * (pred - self.routing_history.mean(0))
 
+    def _gate_weight(self) -> torch.Tensor:
+        """The gate weight as the GEMM reads it.  Without autograd (serving) an fp32 gate is cast to bf16 once and
+        the copy reused until the parameter changes, instead of one cast kernel per layer per decode step."""
+        w = self.gate.weight
+        if torch.is_grad_enabled() or w.dtype == torch.bfloat16 or not w.is_cuda:
+            return w
+        key = (w.data_ptr(), w._version)
+        cached = getattr(self, "_gate_bf16", None)
+        if cached is None or cached[0] != key:
+            cached = (key, w.detach().to(torch.bfloat16))
+            self._gate_bf16 = cached
+        return cached[1]
+
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """x [..., H] -> weights [T,k] (rows sum to 1, or 0 for fully dropped tokens), idx [T,k], aux."""
         x2 = x.reshape(-1, x.shape[-1])
         T = x2.shape[0]
-        logits = F_.linear(x2, self.gate.weight, out_fp32=True)
+        logits = F_.linear(x2, self._gate_weight(), out_fp32=True)
         adj = self._predicted_adjustment()
         if adj is not None:
             logits = logits + adj.to(logits.dtype)

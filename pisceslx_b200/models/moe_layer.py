@@ -86,7 +86,18 @@ class YvDeepSeekMoELayer(nn.Module):
         T = y1.shape[0]
         act = F_.swiglu(y1.view(T * S, 2 * Fs)).view(T, S, Fs)
         if S > 1 or self.shared_expert_weight.requires_grad:
-            mix = torch.softmax(self.shared_expert_weight.float(), 0).to(act.dtype)
+            sw = self.shared_expert_weight
+            if torch.is_grad_enabled():
+                mix = torch.softmax(sw.float(), 0).to(act.dtype)
+            else:
+                # serving: the mixing weights change only when the parameter does; keep them instead of running a
+                # softmax and two casts per layer per decode step
+                key = (sw.data_ptr(), sw._version, act.dtype)
+                cached = getattr(self, "_mix_cache", None)
+                if cached is None or cached[0] != key:
+                    cached = (key, torch.softmax(sw.detach().float(), 0).to(act.dtype))
+                    self._mix_cache = cached
+                mix = cached[1]
             act = act * mix.view(1, S, 1)
         act = act.reshape(T, S * Fs)
         if self.tp_size > 1:
