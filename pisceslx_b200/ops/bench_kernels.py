@@ -101,6 +101,25 @@ def bench_rmsnorm(a: argparse.Namespace) -> Dict[str, Any]:
     return {"kernel": "rmsnorm_fwd(+residual)", "shape": [T, H], "ms": ms, "gbs": gbs, "frac_of_peak": gbs / peaks()["hbm_gbs"]}
 
 
+def bench_muon_fold(a: argparse.Namespace) -> Dict[str, Any]:
+    """The streaming kernels of the Muon step on one stack of expert matrices [batch, m, n]: gradient fold into the
+    momentum (read g, read-modify-write m), Frobenius normalisation (two passes) and the parameter update."""
+    K = kernels()
+    G, m_, n_ = a.batch, a.m, a.n
+    mom = torch.randn(G, m_, n_, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn_like(mom)
+    p = torch.randn_like(mom)
+    norms = torch.empty(G, device="cuda")
+    nbytes = mom.numel() * 2
+    t_fold = timeit(lambda: K.momentum_fold(mom, g, None, 0.95, 1.0, True, False), a.iters)
+    t_frob = timeit(lambda: K.frob_normalize(g, norms, 1e-7), a.iters)
+    t_apply = timeit(lambda: K.muon_apply(p, g, 1e-3, 0.0, 1.0), a.iters)
+    gbs = {"fold": 3.0 * nbytes / t_fold / 1e6, "frob_normalize": 3.0 * nbytes / t_frob / 1e6,
+           "apply": 3.0 * nbytes / t_apply / 1e6}
+    return {"kernel": "muon_streaming", "shape": [G, m_, n_], "ms": {"fold": t_fold, "frob_normalize": t_frob, "apply": t_apply},
+            "gbs": gbs, "frac_of_peak": {k: v / peaks()["hbm_gbs"] for k, v in gbs.items()}}
+
+
 def bench_decode(a: argparse.Namespace) -> Dict[str, Any]:
     from . import functional as F_
     B, hq, hk, d, blk, ctx = a.batch, a.hq, a.hk, a.d, 64, a.seq
@@ -204,7 +223,7 @@ def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs"])
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs", "muon_fold"])
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -239,7 +258,7 @@ def main() -> None:
         fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
               "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz, "gemm_fp8": bench_gemm_fp8,
               "ssm": bench_ssm, "gemm_tp_ag": lambda x: bench_gemm_tp(x, 1),
-              "gemm_tp_rs": lambda x: bench_gemm_tp(x, 2)}[a.kernel]
+              "gemm_tp_rs": lambda x: bench_gemm_tp(x, 2), "muon_fold": bench_muon_fold}[a.kernel]
         res.append(fn(a))
     out = {"peaks": peaks(), "results": res}
     print(json.dumps(out, indent=1))
