@@ -183,7 +183,147 @@ class PiscesLxInferService:
                     for i, t in enumerate(texts)]
             return {"object": "list", "data": data, "model": body.model}
 
+        svc._add_extended_routes(app)
         return app
+
+    # ---- tools, agents, runs, media (reference tools/infer/server.py:312-405) -----------------------------
+    def _generate_text(self, prompt: str, max_new_tokens: int = 256) -> str:
+        req = self.submit(prompt, max_new_tokens, 0.0, 0, 1.0)
+        while not req.finished:
+            time.sleep(0.002)
+        return self.engine.tokenizer.decode(req.output_ids)
+
+    def _add_extended_routes(self, app) -> None:
+        from fastapi.responses import JSONResponse
+
+        from ..engine.runstore import PiscesLxRunStore
+        from ..models.reasoning import YvAgentic, YvToolRegistry
+        svc = self
+        if not hasattr(self, "tools"):
+            self.tools = YvToolRegistry()
+        if not hasattr(self, "runs"):
+            self.runs = PiscesLxRunStore()
+        if not hasattr(self, "media"):
+            self.media: Dict[str, Any] = {}       # "image" / "video" / "audio": callables attached by the deployment
+
+        @app.get("/v1/tools/list")
+        async def tools_list():
+            return {"object": "list", "data": [{"name": t.name, "description": t.description, "parameters": t.parameters}
+                                               for t in svc.tools.tools.values()]}
+
+        @app.post("/v1/tools/search")
+        async def tools_search(body: Dict[str, Any]):
+            q = str(body.get("query", "")).lower()
+            hits = [t for t in svc.tools.tools.values() if q in t.name.lower() or q in t.description.lower()]
+            return {"object": "list", "data": [{"name": t.name, "description": t.description} for t in hits]}
+
+        @app.post("/v1/tools/execute")
+        async def tools_execute(body: Dict[str, Any]):
+            name, args = body.get("name", ""), body.get("arguments", {}) or {}
+            try:
+                return {"name": name, "result": svc.tools.call(name, args), "error": None}
+            except KeyError as e:
+                return JSONResponse({"name": name, "result": None, "error": str(e)}, status_code=404)
+            except Exception as e:
+                return JSONResponse({"name": name, "result": None, "error": f"{type(e).__name__}: {e}"}, status_code=400)
+
+        @app.get("/v1/agents/list")
+        async def agents_list():
+            return {"object": "list", "data": [{"id": "react", "description": "ReAct loop over the registered tools"}]}
+
+        @app.post("/v1/agents/execute")
+        async def agents_execute(body: Dict[str, Any]):
+            agent = YvAgentic(lambda p, n: svc._generate_text(p, n), svc.tools, max_turns=int(body.get("max_turns", 4)),
+                              max_new_tokens=int(body.get("max_tokens", 128)))
+            out = await asyncio.get_event_loop().run_in_executor(None, agent.run, str(body.get("task", "")))
+            return {"agent": "react", "result": out}
+
+        @app.post("/v1/agents/swarm")
+        async def agents_swarm(body: Dict[str, Any]):
+            tasks = [str(t) for t in body.get("tasks", [])]
+            loop = asyncio.get_event_loop()
+
+            def one(task: str):
+                return YvAgentic(lambda p, n: svc._generate_text(p, n), svc.tools, max_turns=int(body.get("max_turns", 3)),
+                                 max_new_tokens=int(body.get("max_tokens", 96))).run(task)
+            results = await asyncio.gather(*[loop.run_in_executor(None, one, t) for t in tasks])
+            return {"results": [{"task": t, "result": r} for t, r in zip(tasks, results)]}
+
+        @app.get("/v1/runs")
+        async def runs_list():
+            return {"object": "list", "data": svc.runs.list_runs()}
+
+        @app.get("/v1/runs/{run_id}")
+        async def runs_get(run_id: str):
+            try:
+                return {"run_id": run_id, "state": svc.runs.read_state(run_id),
+                        "events": svc.runs.read_jsonl(run_id, "events.jsonl")[-20:]}
+            except Exception as e:
+                return JSONResponse({"error": f"{type(e).__name__}: {e}"}, status_code=404)
+
+        @app.post("/v1/runs/{run_id}/control")
+        async def runs_control(run_id: str, body: Dict[str, Any]):
+            cmd = str(body.get("command", ""))
+            if cmd not in ("pause", "resume", "stop", "checkpoint"):
+                return JSONResponse({"error": f"unknown command {cmd!r}"}, status_code=400)
+            if run_id not in svc.runs.list_runs():
+                return JSONResponse({"error": f"unknown run {run_id!r}"}, status_code=404)
+            svc.runs.send_control(run_id, cmd)
+            return {"run_id": run_id, "command": cmd, "accepted": True}
+
+        def _media(kind: str):
+            async def handler(body: Dict[str, Any]):
+                fn = svc.media.get(kind)
+                if fn is None:
+                    return JSONResponse({"error": f"no {kind} generator is attached to this deployment "
+                                                  f"(attach one with service.media[{kind!r}] = callable)"}, status_code=501)
+                out = await asyncio.get_event_loop().run_in_executor(None, fn, body)
+                return {"created": int(time.time()), "data": out}
+            return handler
+
+        app.post("/v1/images/generations")(_media("image"))
+        app.post("/v1/images/edits")(_media("image"))
+        app.post("/v1/videos/generations")(_media("video"))
+        app.post("/v1/audio/speech")(_media("audio"))
+
+
+class PiscesLxModelRouter:
+    """Resolves a request's model id to a model size and a fallback chain (reference tools/infer/model_router.py:91):
+    ``piscesl1-7b``, ``7B``, ``yv-0.5b`` -> size; unknown or unavailable sizes fall back to the next smaller one."""
+
+    ORDER = ["0.01B", "0.1B", "0.5B", "1.5B", "7B", "32B", "64B", "70B", "128B", "314B", "671B", "1T"]
+
+    def __init__(self, available: Optional[List[str]] = None, default_size: str = "7B"):
+        self.available = list(available) if available else [default_size]
+        self.default = default_size
+        self.load: Dict[str, int] = {s: 0 for s in self.available}
+
+    @classmethod
+    def parse_size(cls, model_id: str) -> Optional[str]:
+        import re
+        m = re.match(r"^(?:[a-z0-9]+[-_])?([0-9.]+)\s*([bmt])$", model_id.strip().lower())
+        if not m:
+            return None
+        num, unit = m.group(1), m.group(2).upper()
+        cand = f"{num}{unit}"
+        for s in cls.ORDER:
+            if s.lower() == cand.lower():
+                return s
+        return None
+
+    def resolve(self, model_id: str) -> Dict[str, Any]:
+        size = self.parse_size(model_id)
+        strategy = "explicit"
+        if size is None:
+            size, strategy = self.default, "auto"
+        chain = [s for s in reversed(self.ORDER[: self.ORDER.index(size)]) if s in self.available] \
+            if size in self.ORDER else []
+        if size not in self.available:
+            strategy = "fallback"
+            size = chain[0] if chain else (self.default if self.default in self.available else self.available[0])
+            chain = chain[1:]
+        self.load[size] = self.load.get(size, 0) + 1
+        return {"model_id": model_id, "model_size": size, "strategy": strategy, "fallback_chain": chain}
 
 
 class PiscesLxBackendServer:

@@ -320,6 +320,45 @@ def test_openai_server_endpoints():
     svc.stop()
 
 
+def test_server_tools_agents_runs_media_and_model_router(tmp_path, monkeypatch):
+    from fastapi.testclient import TestClient
+    from pisceslx_b200.engine.runstore import PiscesLxRunStore
+    from pisceslx_b200.serve.engine import YvEngineConfig, YvInferenceEngine
+    from pisceslx_b200.serve.server import PiscesLxInferService, PiscesLxModelRouter
+    m = build_model(tiny())
+    svc = PiscesLxInferService(YvInferenceEngine(m, cfg=YvEngineConfig(num_blocks=64, block_size=16, eos_token_id=-1)))
+    svc.runs = PiscesLxRunStore(tmp_path / "runs")
+    svc.runs.init_run("run-1", {"stage": "pretrain"}, {"step": 3})
+    svc.media = {"audio": lambda body: {"samples": len(body.get("input", "")) * 100}}
+    app = svc.build_app()
+    svc.tools.register("add", "adds two integers", {"a": "int", "b": "int"})(lambda a, b: a + b)
+    with TestClient(app) as c:
+        assert [t["name"] for t in c.get("/v1/tools/list").json()["data"]] == ["add"]
+        assert c.post("/v1/tools/search", json={"query": "integers"}).json()["data"][0]["name"] == "add"
+        assert c.post("/v1/tools/execute", json={"name": "add", "arguments": {"a": 2, "b": 5}}).json()["result"] == 7
+        assert c.post("/v1/tools/execute", json={"name": "nope"}).status_code == 404
+        assert c.post("/v1/tools/execute", json={"name": "add", "arguments": {"a": 1}}).status_code == 400
+        assert c.get("/v1/agents/list").json()["data"][0]["id"] == "react"
+        r = c.post("/v1/agents/execute", json={"task": "say hi", "max_turns": 1, "max_tokens": 4})
+        assert r.status_code == 200 and "result" in r.json()
+        assert c.get("/v1/runs").json()["data"] == ["run-1"]
+        assert c.get("/v1/runs/run-1").json()["state"]["step"] == 3
+        assert c.post("/v1/runs/run-1/control", json={"command": "pause"}).json()["accepted"]
+        assert c.post("/v1/runs/run-1/control", json={"command": "explode"}).status_code == 400
+        assert c.post("/v1/runs/none/control", json={"command": "stop"}).status_code == 404
+        assert c.post("/v1/images/generations", json={"prompt": "a cat"}).status_code == 501
+        assert c.post("/v1/audio/speech", json={"input": "hello"}).json()["data"]["samples"] == 500
+    svc.stop()
+    assert svc.runs.read_jsonl("run-1", "control.jsonl")[-1]["command"] == "pause"
+    router = PiscesLxModelRouter(available=["0.5B", "7B"], default_size="7B")
+    assert router.resolve("piscesl1-7b") == {"model_id": "piscesl1-7b", "model_size": "7B", "strategy": "explicit",
+                                             "fallback_chain": ["0.5B"]}
+    r = router.resolve("671B")
+    assert r["strategy"] == "fallback" and r["model_size"] == "7B" and r["fallback_chain"] == ["0.5B"]
+    assert router.resolve("whatever")["strategy"] == "auto" and router.load["7B"] == 3
+    assert PiscesLxModelRouter.parse_size("yv_0.5b") == "0.5B" and PiscesLxModelRouter.parse_size("1T") == "1T"
+
+
 # ------------------------------------------------------------------------------------------------ CLI
 def test_manage_cli_train_infer_dry_run_and_short_train(tmp_path):
     env = dict(os.environ, PISCESLX_HOME=str(tmp_path / "home"), PYTHONPATH=ROOT)
