@@ -287,6 +287,45 @@ class PiscesLxInferService:
         app.post("/v1/audio/speech")(_media("audio"))
 
 
+class PiscesLxAgentInterceptor:
+    """Sits between a chat request and the engine (reference tools/infer/agent_interceptor.py:112).  Modes: ``off``
+    passes the completion through; ``auto`` looks for ``<tool_call>`` blocks in the completion, runs the named tools,
+    appends their results as a tool message and asks the model to continue, up to ``max_rounds``; ``forced`` does the
+    same but first prepends the tool catalogue to the prompt."""
+
+    def __init__(self, generate, tools, mode: str = "auto", max_rounds: int = 3):
+        if mode not in ("off", "auto", "forced"):
+            raise ValueError(mode)
+        self.generate, self.tools, self.mode, self.max_rounds = generate, tools, mode, max_rounds
+
+    def run(self, prompt: str, max_new_tokens: int = 256) -> Dict[str, Any]:
+        from ..models.reasoning import parse_tool_calls
+        if self.mode == "forced":
+            prompt = f"You may call these tools with <tool_call> blocks:\n{self.tools.describe()}\n\n{prompt}"
+        text = self.generate(prompt, max_new_tokens)
+        trace: List[Dict[str, Any]] = []
+        if self.mode == "off":
+            return {"content": text, "tool_calls": trace, "rounds": 0}
+        rounds = 0
+        while rounds < self.max_rounds:
+            calls = parse_tool_calls(text)
+            if not calls:
+                break
+            rounds += 1
+            results = []
+            for name, args in calls:
+                try:
+                    res = self.tools.call(name, args)
+                    err = None
+                except Exception as e:
+                    res, err = None, f"{type(e).__name__}: {e}"
+                trace.append({"name": name, "arguments": args, "result": res, "error": err})
+                results.append(f"<tool_result name=\"{name}\">{res if err is None else err}</tool_result>")
+            prompt = f"{prompt}\n{text}\n" + "\n".join(results) + "\n"
+            text = self.generate(prompt, max_new_tokens)
+        return {"content": text, "tool_calls": trace, "rounds": rounds}
+
+
 class PiscesLxModelRouter:
     """Resolves a request's model id to a model size and a fallback chain (reference tools/infer/model_router.py:91):
     ``piscesl1-7b``, ``7B``, ``yv-0.5b`` -> size; unknown or unavailable sizes fall back to the next smaller one."""

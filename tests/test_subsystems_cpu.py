@@ -350,6 +350,19 @@ def test_server_tools_agents_runs_media_and_model_router(tmp_path, monkeypatch):
         assert c.post("/v1/audio/speech", json={"input": "hello"}).json()["data"]["samples"] == 500
     svc.stop()
     assert svc.runs.read_jsonl("run-1", "control.jsonl")[-1]["command"] == "pause"
+    from pisceslx_b200.serve.server import PiscesLxAgentInterceptor
+    script = iter(['I need a sum. <tool_call><name>add</name><arguments>{"a": 40, "b": 2}</arguments></tool_call>',
+                   "The answer is 42."])
+    seen = []
+    icpt = PiscesLxAgentInterceptor(lambda p, n: seen.append(p) or next(script), svc.tools, mode="auto")
+    out = icpt.run("what is 40 + 2?")
+    assert out["content"] == "The answer is 42." and out["rounds"] == 1 and out["tool_calls"][0]["result"] == 42
+    assert '<tool_result name="add">42</tool_result>' in seen[1]
+    off = PiscesLxAgentInterceptor(lambda p, n: "<tool_call><name>add</name><arguments>{}</arguments></tool_call>", svc.tools, "off")
+    assert off.run("x")["rounds"] == 0
+    forced = PiscesLxAgentInterceptor(lambda p, n: seen.append(p) or "done", svc.tools, "forced")
+    forced.run("task")
+    assert "add(a, b)" in seen[-1]
     router = PiscesLxModelRouter(available=["0.5B", "7B"], default_size="7B")
     assert router.resolve("piscesl1-7b") == {"model_id": "piscesl1-7b", "model_size": "7B", "strategy": "explicit",
                                              "fallback_chain": ["0.5B"]}
