@@ -101,6 +101,18 @@ def init_weights(tmp_path_factory):
 
 
 @pytest.mark.timeout(900)
+@pytest.mark.parametrize("tp,ep", [(1, 4), (2, 2)])
+def test_four_rank_layouts_match_single_process(tmp_path, init_weights, tp, ep):
+    # the layouts of a four-GPU node: tp1 x ep4 x dp4 (experts over all ranks) and tp2 x ep2 x dp2
+    steps = 3
+    single = _run(tmp_path, 1, 1, 1, steps, init_weights, "single4")
+    multi = _run(tmp_path, 4, tp, ep, steps, init_weights, f"w4tp{tp}ep{ep}")
+    assert len(single) == len(multi) == steps
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
+
+
+@pytest.mark.timeout(900)
 @pytest.mark.parametrize("tp,ep", [(1, 2), (2, 1)])
 def test_parallel_matches_single_process(tmp_path, init_weights, tp, ep):
     steps = 4
