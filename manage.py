@@ -137,10 +137,19 @@ def cmd_action(args, argv) -> int:
         pid = PiscesLxRunController(store).spawn(run_id, child)
         print(json.dumps({"run_id": run_id, "pid": pid}))
         return 0
+    if sub == "clean":
+        from pisceslx_b200.engine.runmgmt import PiscesLxRunCleaner
+        victims = PiscesLxRunCleaner(store).clean(dry_run=bool(args.dry_run))
+        print(json.dumps({"removed" if not args.dry_run else "would_remove": victims}))
+        return 0
     run_id = args.target or args.run_id
     if not run_id:
         print("run id required", file=sys.stderr)
         return 2
+    if sub == "attach":
+        from pisceslx_b200.engine.runmgmt import PiscesLxRunAttacher
+        PiscesLxRunAttacher(store, run_id).attach(lambda kind, rec: print(f"[{kind}] {json.dumps(rec, default=str)}", flush=True))
+        return 0
     if sub == "status":
         print(json.dumps(store.read_state(run_id), indent=1))
     elif sub == "logs":
