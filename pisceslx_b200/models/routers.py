@@ -178,3 +178,113 @@ class YvUltraSparseGate(nn.Module):
         # the scorer learns through a straight-through factor on the weights
         w = w / w.sum(-1, keepdim=True).clamp_min(1e-9) * (1 + imp - imp.detach())[:, None]
         return w, idx, {"tier_k": tier_k, "mean_k": tier_k.float().mean()}
+
+
+class YvDGEncoder(nn.Module):
+    """Sparse pattern separator (reference model/moe/hicl_router.py:44): project to ``expansion`` x hidden, keep the
+    ``sparsity_k`` largest activations per token, L2-normalise."""
+
+    def __init__(self, hidden: int, expansion: int = 4, sparsity_k: int = 32):
+        super().__init__()
+        self.proj = nn.Parameter(torch.empty(hidden * expansion, hidden).normal_(std=hidden ** -0.5))
+        self.k = min(sparsity_k, hidden * expansion)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        z = torch.relu(F_.linear(x, self.proj.to(x.dtype)).float())
+        thr = z.topk(self.k, -1).values[..., -1:]
+        return F.normalize(torch.where(z >= thr, z, torch.zeros_like(z)), dim=-1)
+
+
+class YvHiClRouter(nn.Module):
+    """Prototype router (reference :89): tokens are sparse-coded by ``YvDGEncoder`` and matched by cosine similarity
+    against one prototype per expert; prototypes follow the codes routed to them by an EMA (no gradient), so the
+    router has no trained gate matrix."""
+
+    def __init__(self, hidden: int, n_experts: int, top_k: int = 2, dg_expansion: int = 4, dg_sparsity_k: int = 32,
+                 momentum: float = 0.99, temperature: float = 0.1):
+        super().__init__()
+        self.enc = YvDGEncoder(hidden, dg_expansion, dg_sparsity_k)
+        self.k, self.m, self.t = top_k, momentum, temperature
+        self.register_buffer("prototypes", F.normalize(torch.randn(n_experts, hidden * dg_expansion), dim=-1))
+
+    def forward(self, x: torch.Tensor):
+        code = self.enc(x)
+        sim = code @ self.prototypes.t()
+        w, idx = _topk_renorm(torch.softmax(sim / self.t, -1), self.k)
+        if self.training:
+            with torch.no_grad():
+                top1 = idx[:, 0]
+                sums = torch.zeros_like(self.prototypes).index_add_(0, top1, code.detach())
+                cnt = torch.zeros(self.prototypes.shape[0], device=x.device).index_add_(0, top1, torch.ones_like(top1, dtype=torch.float))
+                seen = cnt > 0
+                upd = F.normalize(sums[seen] / cnt[seen, None], dim=-1)
+                self.prototypes[seen] = F.normalize(self.m * self.prototypes[seen] + (1 - self.m) * upd, dim=-1)
+        return w, idx, {"similarity": sim}
+
+
+class YvTokenGraphBuilder(nn.Module):
+    """Token affinity graph (reference model/moe/graph_of_tokens.py:59): cosine similarity of projected tokens times a
+    positional decay exp(-decay |i - j|), thresholded by a learned value; clusters are the connected runs of the
+    thresholded chain (adjacent tokens whose affinity passes the threshold share a cluster)."""
+
+    def __init__(self, hidden: int, dim: int = 64, pos_decay: float = 0.1, max_clusters: int = 8):
+        super().__init__()
+        self.proj = nn.Parameter(torch.empty(dim, hidden).normal_(std=hidden ** -0.5))
+        self.threshold = nn.Parameter(torch.tensor(0.3))
+        self.decay, self.max_clusters = pos_decay, max_clusters
+
+    def affinity(self, x: torch.Tensor) -> torch.Tensor:
+        z = F.normalize(F_.linear(x, self.proj.to(x.dtype)).float(), dim=-1)
+        pos = torch.arange(x.shape[0], device=x.device, dtype=torch.float32)
+        return (z @ z.t()) * torch.exp(-self.decay * (pos[:, None] - pos[None, :]).abs())
+
+    def clusters(self, x: torch.Tensor) -> torch.Tensor:
+        """x [T, H] (one sequence) -> cluster id per token [T], at most ``max_clusters`` clusters."""
+        A = self.affinity(x)
+        link = torch.diagonal(A, 1) >= self.threshold                    # token t+1 joins token t's cluster
+        cid = torch.cat([torch.zeros(1, dtype=torch.long, device=x.device), (~link).long().cumsum(0)])
+        return cid.clamp_max(self.max_clusters - 1)
+
+
+class YvRoMARegularizer(nn.Module):
+    """Routing manifold alignment (reference :127): samples whose task embeddings are neighbours should route alike.
+    Loss = mean over each sample's ``n_neighbors`` nearest neighbours (in embedding space) of the squared distance
+    between their routing distributions."""
+
+    def __init__(self, hidden: int, n_neighbors: int = 8):
+        super().__init__()
+        self.embed = nn.Linear(hidden, hidden)
+        self.n_neighbors = n_neighbors
+
+    def forward(self, pooled_hidden: torch.Tensor, routing_probs: torch.Tensor) -> torch.Tensor:
+        e = F.normalize(self.embed(pooled_hidden.float()), dim=-1)
+        sim = e @ e.t()
+        sim.fill_diagonal_(float("-inf"))
+        k = min(self.n_neighbors, max(1, e.shape[0] - 1))
+        nbr = sim.topk(k, -1).indices                                    # [N, k]
+        diff = routing_probs.float()[:, None, :] - routing_probs.float()[nbr]
+        return diff.pow(2).sum(-1).mean()
+
+
+class YvGraphOfTokensRouter(nn.Module):
+    """Two-stage routing (reference :196): tokens are clustered along the sequence; every cluster picks its top-k
+    experts from the mean of its tokens' logits, and each token then takes its own softmax weights restricted to its
+    cluster's experts, so that a phrase is processed by one set of experts."""
+
+    def __init__(self, hidden: int, n_experts: int, top_k: int = 2, max_clusters: int = 8):
+        super().__init__()
+        self.graph = YvTokenGraphBuilder(hidden, max_clusters=max_clusters)
+        self.w = nn.Parameter(torch.empty(n_experts, hidden).normal_(std=0.02))
+        self.k = top_k
+
+    def forward(self, x: torch.Tensor):
+        """x [T, H]: the tokens of one sequence, in order."""
+        logits = F_.linear(x, self.w.to(x.dtype)).float()
+        cid = self.graph.clusters(x)
+        n_c = int(cid.max()) + 1
+        onehot = F.one_hot(cid, n_c).float()
+        mean_logits = (onehot.t() @ logits) / onehot.sum(0).clamp_min(1)[:, None]      # [C, E]
+        c_idx = mean_logits.topk(self.k, -1).indices                                    # [C, k]
+        idx = c_idx[cid]                                                                # [T, k]
+        w = torch.softmax(torch.gather(logits, 1, idx), -1)
+        return w, idx, {"clusters": cid, "n_clusters": n_c}

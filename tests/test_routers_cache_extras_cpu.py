@@ -72,6 +72,39 @@ def test_modal_aware_and_ultra_sparse_gates():
     assert us.scorer[0].weight.grad is not None
 
 
+def test_hicl_prototype_router_and_graph_of_tokens_router():
+    from pisceslx_b200.models.routers import (YvDGEncoder, YvGraphOfTokensRouter, YvHiClRouter, YvRoMARegularizer,
+                                              YvTokenGraphBuilder)
+    torch.manual_seed(6)
+    enc = YvDGEncoder(16, expansion=4, sparsity_k=5)
+    c = enc(torch.randn(7, 16))
+    assert c.shape == (7, 64) and ((c != 0).sum(-1) <= 5).all() and torch.allclose(c.norm(dim=-1), torch.ones(7), atol=1e-5)
+    r = YvHiClRouter(16, 4, top_k=2, dg_sparsity_k=8, momentum=0.5)
+    # two well separated token populations end up on different prototypes after a few EMA updates
+    a, b = torch.randn(1, 16) + torch.zeros(40, 16), -(torch.randn(1, 16) + torch.zeros(40, 16))
+    a, b = a + 0.05 * torch.randn_like(a), b + 0.05 * torch.randn_like(b)
+    r.train()
+    p0 = r.prototypes.clone()
+    for _ in range(10):
+        w, idx, aux = r(torch.cat([a, b]))
+    assert not torch.equal(p0, r.prototypes) and torch.allclose(w.sum(-1), torch.ones(80), atol=1e-5)
+    top = idx[:, 0]
+    assert len(set(top[:40].tolist())) == 1 and len(set(top[40:].tolist())) == 1 and top[0] != top[40]
+    assert aux["similarity"].abs().max() <= 1 + 1e-5
+    # graph clustering: two constant phrases -> two clusters, each routed as a unit
+    g = YvTokenGraphBuilder(16, max_clusters=4)
+    x = torch.cat([torch.randn(1, 16).expand(5, -1), torch.randn(1, 16).expand(6, -1)])
+    cid = g.clusters(x)
+    assert cid[:5].unique().numel() == 1 and cid[5:].unique().numel() == 1 and cid[0] != cid[5]
+    got = YvGraphOfTokensRouter(16, 8, top_k=2, max_clusters=4)
+    w, idx, aux = got(x)
+    assert aux["n_clusters"] == 2 and (idx[:5] == idx[0]).all() and (idx[5:] == idx[5]).all()
+    assert torch.allclose(w.sum(-1), torch.ones(11), atol=1e-5)
+    roma = YvRoMARegularizer(16, n_neighbors=2)
+    probs = torch.softmax(torch.randn(6, 8), -1)
+    assert float(roma(torch.randn(6, 16), probs)) > 0 and float(roma(torch.randn(6, 16), probs[:1].expand(6, -1))) < 1e-12
+
+
 def test_triroute_and_brownout_grouper():
     from pisceslx_b200.serve.runtime import PiscesLxBrownoutMoEGrouper, PiscesLxTriRouteDecision
     torch.manual_seed(5)
