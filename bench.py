@@ -48,7 +48,7 @@ def parse_args():
 # ------------------------------------------------------------------------------------------------------
 def reference_arm(args) -> None:
     """The unmodified reference cannot be installed or imported in this image; say so and exit 0."""
-    why = ("reference not installable: /root/reference has neither setup.py nor pyproject.toml (pip: 'not "
+    why = ("reference not installable: its source tree has neither setup.py nor pyproject.toml (pip: 'not "
            "installable'), and its utils/dc.py hard-imports dmsc==0.1.8, which is not in the image or the wheelhouse")
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if os.path.isdir(ref_dir) and os.listdir(ref_dir):

@@ -68,7 +68,8 @@ class PiscesLxDetachedScalarCheck(PiscesLxStandardCheck):
 
 class PiscesLxBuildDocReferenceCheck(PiscesLxStandardCheck):
     rule = "build-doc-reference"
-    pat = re.compile(r"\b(SURVEY|VERDICT|ADVICE|BASELINE|DESIGN)\.md\b")
+    # any all-capitals markdown file of the repository root other than the README (planning and review documents)
+    pat = re.compile(r"\b(?!README\b)[A-Z]{5,}\.md\b")
 
     def check(self, path, source, tree):
         for i, line in enumerate(source.splitlines(), 1):
