@@ -42,18 +42,86 @@ def parse_args():
     ap.add_argument("--ep", type=int, default=0)
     ap.add_argument("--no-fused-comm", action="store_true", help="NCCL-only collectives (the stated baseline mode)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--ref-limit", type=int, default=1000, help="seconds given to the reference's full-size attempt")
+    ap.add_argument("--no-ref-context", action="store_true", help="skip the reduced-layer context run of the reference")
     return ap.parse_args()
 
 
 # ------------------------------------------------------------------------------------------------------
+def _run_reference_child(extra, out_path, limit_s, port_shift=0):
+    """Run ``baseline/run_reference.py`` as a child of this rank (same RANK / LOCAL_RANK / WORLD_SIZE, so the N
+    children form the reference's own process group) and return its JSON line, or a reason string."""
+    env = dict(os.environ)
+    if port_shift and env.get("MASTER_PORT"):
+        env["MASTER_PORT"] = str(int(env["MASTER_PORT"]) + port_shift)
+    env.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    cmd = [sys.executable, os.path.join(ROOT, "baseline", "run_reference.py"), "--out", out_path] + extra
+    log = open(out_path + ".log", "w")
+    proc = subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT, env=env, cwd=ROOT)
+    try:
+        proc.wait(timeout=limit_s)
+    except subprocess.TimeoutExpired:
+        proc.kill()                                          # the exact child this rank started
+        proc.wait()
+        return f"stock reference path did not finish within {limit_s} s (killed)"
+    finally:
+        log.close()
+    try:
+        with open(out_path) as f:
+            return json.loads(f.read().strip().splitlines()[-1])
+    except Exception:
+        tail = ""
+        try:
+            tail = open(out_path + ".log").read()[-400:].replace("\n", " ")
+        except OSError:
+            pass
+        return f"stock reference path exited with code {proc.returncode} and no result: {tail}"
+
+
 def reference_arm(args) -> None:
-    """The unmodified reference cannot be installed or imported in this image; say so and exit 0."""
-    why = ("reference not installable: its source tree has neither setup.py nor pyproject.toml (pip: 'not "
-           "installable'), and its utils/dc.py hard-imports dmsc==0.1.8, which is not in the image or the wheelhouse")
+    """Train the UNMODIFIED reference (plain copy under ``baseline/_ref``) through its own trainer on the benchmark's
+    model and data shape (``baseline/run_reference.py`` says which reference calls are driven), first at the full
+    configuration; when that fails on its own (its model does not fit host or device memory), the captured reason is
+    reported as ``unavailable`` together with a labelled context run of the same path at 4 of the 32 layers, which is
+    NOT the benchmark configuration and carries ``same_config: false``."""
+    import tempfile
+    rank = int(os.environ.get("RANK", "0"))
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if os.path.isdir(ref_dir) and os.listdir(ref_dir):
-        why = "reference present under baseline/_ref but its hard dependency dmsc is missing"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if not os.path.isdir(os.path.join(ref_dir, "tools")):
+        src = "/root/reference"
+        if os.path.isdir(os.path.join(src, "tools")):        # a plain copy is the whole installation: pure Python
+            import shutil
+            for name in ("manage.py", "configs", "utils", "third_party", "opss", "tools", "model", "tokenizer"):
+                s_, d_ = os.path.join(src, name), os.path.join(ref_dir, name)
+                (shutil.copytree if os.path.isdir(s_) else shutil.copy)(s_, d_)
+        else:
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "no copy of the reference under baseline/_ref "
+                                  "and no /root/reference to copy it from"}))
+            return
+    tmp = tempfile.mkdtemp(prefix="yv_ref_arm_")
+    seqs = args.seqs_per_gpu or 64
+    full = ["--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup),
+            "--seqs-per-gpu", str(seqs), "--micro-batch", "1"]
+    if args.layers != 32:
+        full += ["--layers", str(args.layers)]
+    res = _run_reference_child(full, os.path.join(tmp, f"full_{rank}.json"), limit_s=args.ref_limit)
+    if isinstance(res, dict) and "unavailable" not in res:
+        if rank == 0:
+            print(json.dumps(res))
+        return
+    reason = res if isinstance(res, str) else res.get("unavailable", "unknown")
+    out = {"impl": "reference", "unavailable": reason}
+    if not args.no_ref_context and args.layers == 32:
+        ctx = _run_reference_child(["--gpus", str(args.gpus), "--steps", str(min(args.steps, 2)), "--warmup", "1",
+                                    "--seqs-per-gpu", "8", "--micro-batch", "1", "--layers", "4"],
+                                   os.path.join(tmp, f"ctx_{rank}.json"), limit_s=600, port_shift=7)
+        out["context_reduced"] = {"note": "same reference path at 4 of 32 layers, 8 sequences per GPU per step: "
+                                  "context only, not the benchmark configuration; compare with "
+                                  "`bench.py --layers 4 --seqs-per-gpu 8` of this framework",
+                                  "result": ctx}
+    if rank == 0:
+        print(json.dumps(out))
 
 
 class ClockSampler:

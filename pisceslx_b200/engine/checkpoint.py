@@ -66,9 +66,30 @@ def checkpoint_dict(trainer: Any, metadata: Optional[Dict[str, Any]] = None) -> 
         "materialized_components": list(getattr(getattr(model, "model", model), "materialized_components", [])),
         "timestamp": time.time(),
         "metadata": metadata or {},
-        "rng_state": {"cpu": torch.get_rng_state(),
-                      "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else []},
+        "rng_state": _rng_state(),
     }
+
+
+def _rng_state() -> Dict[str, Any]:
+    return {"cpu": torch.get_rng_state(),
+            "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else []}
+
+
+def _restore_rng(state: Optional[Dict[str, Any]]) -> None:
+    """Put the generators back where the checkpoint left them (dropout masks, sampled routing noise and data
+    order then continue as in the uninterrupted run).  A state from a machine with another device count is
+    restored as far as it matches."""
+    if not state:
+        return
+    try:
+        if state.get("cpu") is not None:
+            torch.set_rng_state(state["cpu"])
+        cuda = state.get("cuda") or []
+        if cuda and torch.cuda.is_available():
+            for i, st in enumerate(cuda[:torch.cuda.device_count()]):
+                torch.cuda.set_rng_state(st, i)
+    except Exception as e:                                  # a foreign or damaged state must not block a resume
+        print(f"[checkpoint] warning: random-generator state not restored: {e}")
 
 
 def prune_checkpoints(directory: str, keep: int = 3) -> List[str]:
@@ -84,7 +105,10 @@ def prune_checkpoints(directory: str, keep: int = 3) -> List[str]:
 
 def save_checkpoint(trainer: Any, path: str, metadata: Optional[Dict[str, Any]] = None, keep: int = 3) -> str:
     par = getattr(trainer, "parallel", None)
-    if par is not None and par.world_size > 1 and (par.tp_size > 1 or par.ep_size > 1 or par.pp_size > 1):
+    # Any multi-rank run writes per-rank shards: under tensor / expert / pipeline parallelism the weights differ
+    # per rank, and under plain data parallelism the optimizer state does (ZeRO-1: the momentum and Adam moments
+    # of a tensor exist only on its owner), so rank 0's state alone would silently restart (dp-1)/dp of it.
+    if par is not None and par.world_size > 1:
         return save_sharded(trainer, os.path.splitext(path)[0] + "_sharded", metadata)
     if par is None or par.rank == 0:
         _atomic_save(checkpoint_dict(trainer, metadata), path)
@@ -95,6 +119,8 @@ def save_checkpoint(trainer: Any, path: str, metadata: Optional[Dict[str, Any]] 
 def load_checkpoint(trainer: Any, path: str, reset_lr: bool = False, strict: bool = True) -> Dict[str, Any]:
     """Strict model load; optimizer / scheduler state is skipped with a warning when the parameter groups do
     not match (reference core.py:3065-3122, contract pinned by tools/test/test_resume_contract.py)."""
+    if not os.path.exists(path) and os.path.isdir(os.path.splitext(path)[0] + "_sharded"):
+        path = os.path.splitext(path)[0] + "_sharded"
     if os.path.isdir(path):
         return load_sharded(trainer, path, reset_lr)
     ck = torch.load(path, map_location="cpu", weights_only=False)
@@ -127,6 +153,7 @@ def load_checkpoint(trainer: Any, path: str, reset_lr: bool = False, strict: boo
         trainer.best_metric = ck.get("best_metric", trainer.best_metric)
         if ck.get("training_stats"):
             trainer.training_stats = ck["training_stats"]
+        _restore_rng(ck.get("rng_state"))
     for w in warnings:
         print(f"[checkpoint] warning: {w}")
     return {"warnings": warnings, "global_step": trainer.global_step}
@@ -142,7 +169,8 @@ def save_sharded(trainer: Any, directory: str, metadata: Optional[Dict[str, Any]
     local = {k: v.cpu() for k, v in model.to_reference_state_dict().items()}
     shard = {"model_state_dict": local, "optimizer_state_dict": trainer.optimizer.state_dict(),
              "rank": par.rank, "tp_rank": par.tp_rank, "ep_rank": par.ep_rank, "pp_rank": par.pp_rank,
-             "dp_rank": par.dp_rank}
+             "dp_rank": par.dp_rank, "rng_state": _rng_state(),
+             "best_metric": trainer.best_metric}
     _atomic_save(shard, os.path.join(directory, f"shard_rank{par.rank}.pt"))
     if par.rank == 0:
         index = {"world_size": par.world_size, "tp": par.tp_size, "ep": par.ep_size, "pp": par.pp_size,
@@ -193,20 +221,28 @@ def load_sharded(trainer: Any, directory: str, reset_lr: bool = False) -> Dict[s
     par = getattr(trainer, "parallel", None)
     index = json.load(open(os.path.join(directory, "index.json")))
     same_mesh = par is not None and all(index[k] == getattr(par, k + "_size") for k in ("tp", "ep", "pp", "dp"))
+    warnings: List[str] = []
     if same_mesh:
         sh = torch.load(os.path.join(directory, f"shard_rank{par.rank}.pt"), map_location="cpu", weights_only=False)
         trainer.model.load_reference_state_dict(sh["model_state_dict"], strict=False)
         try:
             trainer.optimizer.load_state_dict(sh["optimizer_state_dict"])
         except Exception as e:  # mismatch degrades with a warning, like the consolidated path
-            print(f"[checkpoint] warning: optimizer state skipped: {e}")
+            warnings.append(f"optimizer state skipped: {e}")
+        _restore_rng(sh.get("rng_state"))
+        trainer.best_metric = sh.get("best_metric", trainer.best_metric)
     else:
         full = consolidate_sharded(directory)
         load_full_into(trainer.model, full)
+        warnings.append(f"optimizer state dropped: the checkpoint's mesh (tp {index['tp']} ep {index['ep']} pp "
+                        f"{index['pp']} dp {index['dp']}) differs from the current one, and optimizer state is "
+                        "stored per owner rank; momentum and Adam moments restart from zero")
+    for w in warnings:
+        print(f"[checkpoint] warning: {w}")
     trainer.global_step = int(index.get("global_step", 0))
     if index.get("scheduler_state_dict") and trainer.scheduler is not None:
         trainer.scheduler.load_state_dict(index["scheduler_state_dict"], reset_lr=reset_lr)
-    return {"warnings": [], "global_step": trainer.global_step, "resharded": not same_mesh}
+    return {"warnings": warnings, "global_step": trainer.global_step, "resharded": not same_mesh}
 
 
 def load_full_into(model: Any, full: Dict[str, torch.Tensor]) -> None:

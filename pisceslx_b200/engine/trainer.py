@@ -152,7 +152,15 @@ class YvTrainer:
             if cfg.clip_grad_norm and cfg.clip_grad_norm > 0:
                 grad_norm = self._clip(cfg.clip_grad_norm)
         elif getattr(self.optimizer, "sq_norm", None) is not None:
-            grad_norm = self.optimizer.sq_norm.sqrt() / n_micro
+            # streaming: gradients were folded into the optimizer state as they were produced, so nothing is left
+            # to clip; the norm is reported.  Locally consumed tensors contribute the sum of their per-micro-batch
+            # squared norms (an upper estimate of the norm of the mean), data-parallel ones the exact reduced norm.
+            sq = self.optimizer.sq_norm / float(n_micro * n_micro)
+            if self.dp is not None:
+                if self.dp.consumed_sq is not None:
+                    sq = sq + self.dp.consumed_sq.to(sq.device)
+                sq = self.dp.global_sq_norm(sq)
+            grad_norm = sq.sqrt()
         self.optimizer.step()
         if self.dp is not None:
             self.dp.after_step()
@@ -187,23 +195,40 @@ class YvTrainer:
         return res
 
     def _clip(self, max_norm: float) -> torch.Tensor:
+        """Global-norm clipping (reference: ``clip_grad_norm_`` at 1.0, tools/train/core.py:2857-2862).  After the
+        data-parallel reduction a rank sees ``p.grad`` only for the tensors it owns plus the tensors unique to it,
+        so the squared norms are summed over ALL ranks and one coefficient is applied everywhere."""
         params = [p for p in self.model.parameters() if p.grad is not None]
-        if not params:
+        distributed = self.parallel is not None and getattr(self.parallel, "world_size", 1) > 1
+        if not params and not distributed:
             return torch.zeros(())
+        sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        sq_rep = torch.zeros(1, dtype=torch.float32, device=self.device)     # copies shared by the tp ranks
+        K = None
         if self.device.type == "cuda":
             from ..ops import kernels
-            sq = torch.zeros(1, dtype=torch.float32, device=self.device)
             K = kernels()
-            for p in params:
-                K.sumsq(p.grad.contiguous(), sq)
-            if self.parallel is not None and getattr(self.parallel, "model_parallel_group", None) is not None:
-                torch.distributed.all_reduce(sq, group=self.parallel.model_parallel_group)
-            norm = sq.sqrt()
-            coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
-            for p in params:
+        for p in params:
+            acc = sq_rep if (self.dp is not None and self.dp.norm_weight(p) != 1.0) else sq
+            if K is not None:
+                K.sumsq(p.grad.contiguous(), acc)
+            else:
+                acc += p.grad.detach().float().pow(2).sum()
+        if self.dp is not None:
+            sq = sq + sq_rep / float(self.dp.tp_size)
+        if distributed:
+            if self.dp is not None:
+                sq = self.dp.global_sq_norm(sq)
+            else:
+                torch.distributed.all_reduce(sq)
+        norm = sq.sqrt()
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        for p in params:
+            if K is not None:
                 K.scale_(p.grad, coef, 1.0)
-            return norm[0]
-        return torch.nn.utils.clip_grad_norm_(params, max_norm)
+            else:
+                p.grad.mul_(coef.to(p.grad.dtype))
+        return norm[0]
 
     # ------------------------------------------------------------------------------------------------
     def fit(self, batches: Iterable[Dict[str, torch.Tensor]], max_steps: Optional[int] = None) -> Dict[str, Any]:

@@ -1,4 +1,5 @@
 // Host launchers for the attention kernels: tensor-map construction, grid sizing, template dispatch.
+#include "per_device.h"
 #include "attention_bwd.cuh"
 #include "attention_decode.cuh"
 #include "attention_decode_mma.cuh"
@@ -50,12 +51,12 @@ int launch_attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.status = a.status;
   dim3 grid((a.max_q + 127) / 128, a.hq, a.batch);
   if (a.d == 128) {
-    static bool cfg = false;
-    if (!cfg) { r = set_smem(attn_fwd_kernel<128>, AttnFwdSmem<128>::kTotal); if (r) return r; cfg = true; }
+    static PerDeviceInt cfg;
+    if (!cfg.cur()) { r = set_smem(attn_fwd_kernel<128>, AttnFwdSmem<128>::kTotal); if (r) return r; cfg.cur() = 1; }
     attn_fwd_kernel<128><<<grid, kAttnThreads, AttnFwdSmem<128>::kTotal, stream>>>(p);
   } else {
-    static bool cfg = false;
-    if (!cfg) { r = set_smem(attn_fwd_kernel<64>, AttnFwdSmem<64>::kTotal); if (r) return r; cfg = true; }
+    static PerDeviceInt cfg;
+    if (!cfg.cur()) { r = set_smem(attn_fwd_kernel<64>, AttnFwdSmem<64>::kTotal); if (r) return r; cfg.cur() = 1; }
     attn_fwd_kernel<64><<<grid, kAttnThreads, AttnFwdSmem<64>::kTotal, stream>>>(p);
   }
   return static_cast<int>(cudaGetLastError());
@@ -99,20 +100,20 @@ int launch_attn_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
   dim3 grid_q((a.max_q + 127) / 128, a.hq, a.batch);
   dim3 grid_k((a.max_k + 127) / 128, a.hk, a.batch);
   if (a.d == 128) {
-    static bool cfg = false;
-    if (!cfg) {
+    static PerDeviceInt cfg;
+    if (!cfg.cur()) {
       r = set_smem(attn_bwd_dq_kernel<128>, AttnBwdSmem<128>::kTotal); if (r) return r;
       r = set_smem(attn_bwd_dkv_kernel<128>, AttnBwdSmem<128>::kTotal); if (r) return r;
-      cfg = true;
+      cfg.cur() = 1;
     }
     attn_bwd_dkv_kernel<128><<<grid_k, 192, AttnBwdSmem<128>::kTotal, stream>>>(p);
     attn_bwd_dq_kernel<128><<<grid_q, 192, AttnBwdSmem<128>::kTotal, stream>>>(p);
   } else {
-    static bool cfg = false;
-    if (!cfg) {
+    static PerDeviceInt cfg;
+    if (!cfg.cur()) {
       r = set_smem(attn_bwd_dq_kernel<64>, AttnBwdSmem<64>::kTotal); if (r) return r;
       r = set_smem(attn_bwd_dkv_kernel<64>, AttnBwdSmem<64>::kTotal); if (r) return r;
-      cfg = true;
+      cfg.cur() = 1;
     }
     attn_bwd_dkv_kernel<64><<<grid_k, 192, AttnBwdSmem<64>::kTotal, stream>>>(p);
     attn_bwd_dq_kernel<64><<<grid_q, 192, AttnBwdSmem<64>::kTotal, stream>>>(p);
@@ -137,11 +138,11 @@ int decode_dispatch(const PagedDecodeParams& p, int G, dim3 grid, cudaStream_t s
 namespace {
 template <int D, int G>
 int decode_tma_launch(const PagedDecodeTmaParams& pp, dim3 grid, int smem, cudaStream_t stream) {
-  static int configured = 0;
-  if (configured < smem) {
+  static PerDeviceInt configured;
+  if (configured.cur() < smem) {
     int r = set_smem(paged_decode_tma_kernel<D, G>, smem);
     if (r != 0) return r;
-    configured = smem;
+    configured.cur() = smem;
   }
   paged_decode_tma_kernel<D, G><<<grid, 128, smem, stream>>>(pp);
   return 0;
@@ -194,13 +195,13 @@ int launch_paged_decode(const PagedDecodeArgs& a, cudaStream_t stream) {
     r = make_tmap_3d(&pm.tma_v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.v_cache, 128, static_cast<uint64_t>(a.hk),
                      static_cast<uint64_t>(slots), 256, static_cast<uint64_t>(a.hk) * 256, 64, 1, 64);
     if (r != 0) return -50 + r;
-    static bool cfg = false;
-    if (!cfg) {
+    static PerDeviceInt cfg;
+    if (!cfg.cur()) {
       r = set_smem(paged_decode_mma_kernel<1>, kDmSmem); if (r) return r;
       r = set_smem(paged_decode_mma_kernel<2>, kDmSmem); if (r) return r;
       r = set_smem(paged_decode_mma_kernel<4>, kDmSmem); if (r) return r;
       r = set_smem(paged_decode_mma_kernel<8>, kDmSmem); if (r) return r;
-      cfg = true;
+      cfg.cur() = 1;
     }
     switch (G) {
       case 1: paged_decode_mma_kernel<1><<<grid, kDmThreads, kDmSmem, stream>>>(pm); break;

@@ -27,6 +27,18 @@ struct PagedDecodeParams {
   uint32_t* status;
 };
 
+// Sequence length of batch row b, clamped to what its block-table row can describe.  A longer length would walk past
+// the row (into the next sequence's table or out of the tensor): it is cut to the row's capacity and reported.
+__device__ __forceinline__ int decode_seq_len(const PagedDecodeParams& p, int b) {
+  int n = p.seq_lens[b];
+  const int64_t cap = static_cast<int64_t>(p.max_blocks_per_seq) * p.block;
+  if (n < 0 || n > cap) {
+    if (p.status != nullptr && threadIdx.x == 0) atomicOr(p.status, kStatusIndexOutOfRange);
+    n = n < 0 ? 0 : static_cast<int>(cap);
+  }
+  return n;
+}
+
 // Merge of the 16 key groups of a CTA (each group holds a running max / sum / accumulator for its keys) into the
 // split's partial result in scratch.  Shared by the direct-load and the TMA-fed kernels; every thread of the CTA
 // calls it (it synchronises the CTA).
@@ -88,7 +100,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const PagedDecodePara
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x;
   const int grp = tid >> 3, sub = tid & 7;
-  const int seq_len = p.seq_lens[b];
+  const int seq_len = decode_seq_len(p, b);
   // keys of this split: whole cache blocks
   const int n_blocks = (seq_len + p.block - 1) / p.block;
   const int blocks_per_split = (n_blocks + p.splits - 1) / p.splits;

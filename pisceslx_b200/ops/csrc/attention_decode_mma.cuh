@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(kDmThreads, 1) paged_decode_mma_kernel(const _
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq_len = p.seq_lens[b];
+  const int seq_len = decode_seq_len(p, b);
   const int n_blocks = (seq_len + p.block - 1) / p.block;                 // p.block == 64
   const int blocks_per_split = (n_blocks + p.splits - 1) / p.splits;
   const int blk0 = split * blocks_per_split;
@@ -312,7 +312,18 @@ __global__ void __launch_bounds__(kDmThreads, 1) paged_decode_mma_kernel(const _
         }
       }
     } else {
-      // a wait ran out: let copies that may still be in flight land before shared memory and TMEM are released
+      // A wait ran out (status bit set).  The split's slots in the scratch are still written, as an empty partial
+      // (max = -1e29, sum = 0, zeros): the merge kernel then never reads what an earlier launch left there.
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int64_t base = (static_cast<int64_t>(b) * p.hq + kvh * G + g) * p.splits + split;
+        p.partial_o[base * kDmD + tid] = 0.f;
+        if (tid == 0) {
+          p.partial_ml[base * 2] = -1.0e29f;
+          p.partial_ml[base * 2 + 1] = 0.f;
+        }
+      }
+      // let copies that may still be in flight land before shared memory and TMEM are released
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
     }

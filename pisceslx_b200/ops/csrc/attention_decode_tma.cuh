@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(128) paged_decode_tma_kernel(const __grid_cons
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x;
   const int grp = tid >> 3, sub = tid & 7;
-  const int seq_len = p.seq_lens[b];
+  const int seq_len = decode_seq_len(p, b);
   const int n_blocks = (seq_len + p.block - 1) / p.block;
   const int blocks_per_split = (n_blocks + p.splits - 1) / p.splits;
   const int blk0 = split * blocks_per_split;

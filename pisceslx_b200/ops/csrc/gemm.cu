@@ -1,5 +1,6 @@
 // Host launcher of the tcgen05 GEMM: builds the three tensor maps, picks the template instance and
 // launches one persistent CTA per SM.
+#include "per_device.h"
 #include "gemm_sm100.cuh"
 #include "tensormap.h"
 #include "yv_ops.h"
@@ -23,11 +24,11 @@ int sm_count() {
 template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, bool FP8 = false>
 int launch_instance(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT, COMM, FP8>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceInt configured;
+  if (!configured.cur()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.cur() = 1;
   }
   kern<<<grid, COMM == 1 ? kGemmThreadsAllGather : kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
   return static_cast<int>(cudaGetLastError());

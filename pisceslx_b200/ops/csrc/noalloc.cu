@@ -14,12 +14,16 @@ namespace {
 // cudaGetSymbolAddress; the device address is looked up once per device below.
 static __device__ __align__(256) float g_decode_scratch[YV_NOALLOC_SCRATCH_FLOATS];
 
+// Status word of this entry point (bit mask, see yv_noalloc_status); the kernels set bits with atomicOr.
+static __device__ uint32_t g_decode_status;
+
 constexpr int kMaxDevices = 64;
 float* g_scratch_ptr[kMaxDevices] = {nullptr};
+uint32_t* g_status_ptr[kMaxDevices] = {nullptr};
 std::mutex g_setup_mutex;
 
 // Device address of the scratch array on the current device (resolved on first use per device).
-int scratch_for_current_device(float** out) {
+int scratch_for_current_device(float** out, uint32_t** status_out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return YV_NOALLOC_SETUP_FAILED;
@@ -32,9 +36,18 @@ int scratch_for_current_device(float** out) {
               cudaGetErrorString(e));
       return YV_NOALLOC_SETUP_FAILED;
     }
+    uint32_t* st = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st), g_decode_status);
+    if (e != cudaSuccess || st == nullptr) {
+      fprintf(stderr, "pisceslx_b200: cudaGetSymbolAddress(decode status) failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return YV_NOALLOC_SETUP_FAILED;
+    }
+    g_status_ptr[dev] = st;
     g_scratch_ptr[dev] = p;
   }
   *out = g_scratch_ptr[dev];
+  *status_out = g_status_ptr[dev];
   return YV_NOALLOC_OK;
 }
 
@@ -62,7 +75,8 @@ extern "C" int yv_paged_decode_noalloc(const void* q, const void* k_cache, const
     return YV_NOALLOC_TOO_LARGE;
   }
   float* scratch = nullptr;
-  const int rc = scratch_for_current_device(&scratch);
+  uint32_t* status = nullptr;
+  const int rc = scratch_for_current_device(&scratch, &status);
   if (rc != YV_NOALLOC_OK) return rc;
 
   yv::PagedDecodeArgs a;
@@ -74,8 +88,21 @@ extern "C" int yv_paged_decode_noalloc(const void* q, const void* k_cache, const
   a.batch = batch; a.hq = hq; a.hk = hk; a.d = d; a.block = block;
   a.max_blocks_per_seq = max_blocks_per_seq; a.splits = splits; a.num_blocks = num_blocks;
   a.scale = scale;
-  a.status = nullptr;
-  return yv::launch_paged_decode(a, reinterpret_cast<cudaStream_t>(stream));
+  a.status = status;
+  const int lrc = yv::launch_paged_decode(a, reinterpret_cast<cudaStream_t>(stream));
+  return lrc < 0 ? YV_NOALLOC_LAUNCHER_BASE + lrc : lrc;
+}
+
+extern "C" int yv_noalloc_status(int reset, void* stream) {
+  float* scratch = nullptr;
+  uint32_t* status = nullptr;
+  if (scratch_for_current_device(&scratch, &status) != YV_NOALLOC_OK) return YV_NOALLOC_SETUP_FAILED;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  uint32_t bits = 0;
+  if (cudaMemcpyAsync(&bits, status, sizeof(bits), cudaMemcpyDeviceToHost, s) != cudaSuccess) return YV_NOALLOC_SETUP_FAILED;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return YV_NOALLOC_SETUP_FAILED;
+  if (reset && bits != 0 && cudaMemsetAsync(status, 0, sizeof(bits), s) != cudaSuccess) return YV_NOALLOC_SETUP_FAILED;
+  return static_cast<int>(bits);
 }
 
 extern "C" const char* yv_noalloc_strerror(int code) {
@@ -84,6 +111,10 @@ extern "C" const char* yv_noalloc_strerror(int code) {
     case YV_NOALLOC_TOO_LARGE: return "problem exceeds the built-in scratch capacity";
     case YV_NOALLOC_BAD_ARGUMENT: return "unsupported shape or null pointer";
     case YV_NOALLOC_SETUP_FAILED: return "could not resolve the scratch array on this device";
-    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown";
+    default:
+      if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+      if (code <= YV_NOALLOC_LAUNCHER_BASE + (-1) && code > 2 * YV_NOALLOC_LAUNCHER_BASE)
+        return "the kernel launcher rejected the problem (code - YV_NOALLOC_LAUNCHER_BASE is its own code)";
+      return "unknown";
   }
 }

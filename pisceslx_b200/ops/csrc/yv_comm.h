@@ -47,6 +47,7 @@ struct ZeroFoldArgs {
   void* p; void* m; void* v;    // tensors of the owned parameter (bf16 or fp32 per *_fp32 flags)
   int p_fp32, s_fp32;
   float mu, lr, beta1, beta2, eps, wd, bc1, bc2;
+  float* sumsq = nullptr;       // optional: += squared norm of the reduced, scaled gradient (fp32 scalar)
 };
 int launch_zero_reduce_fold(const ZeroFoldArgs& a, cudaStream_t stream);
 int launch_peer_copy(void* dst, const void* src, int64_t bytes, cudaStream_t stream);

@@ -263,7 +263,7 @@ def symmetric_flat_buffers(group: Any, name: str, numel: int, dtype: torch.dtype
     return (pb, pb.tensor(dtype, numel)), (gb, gb.tensor(dtype, numel))
 
 
-def reduce_scatter_grads(g: Any, scale: float, optimizer: Any = None) -> List[str]:
+def reduce_scatter_grads(g: Any, scale: float, optimizer: Any = None, sumsq: Any = None) -> List[str]:
     """Owner-side pull reduction of flat-group ``g``.  Tensors whose optimizer update could be fused into the
     reduction are returned by name (their gradients need no further handling)."""
     K = kernels()
@@ -281,14 +281,14 @@ def reduce_scatter_grads(g: Any, scale: float, optimizer: Any = None) -> List[st
             state = optimizer._state_for(p, group)
             if group["use_muon"]:
                 K.zero_reduce_fold(ptrs, g.rank, off, numel, scale, 1, None, state["momentum_buffer"].view(-1), None,
-                                   group["momentum"], 0.0, 0.0, 0.0, 0.0, 0.0, 1)
+                                   group["momentum"], 0.0, 0.0, 0.0, 0.0, 0.0, 1, sumsq)
                 fused_done = True
             elif p.is_contiguous():
                 state["adam_step"] += 1
                 b1, b2 = group["betas"]
                 K.zero_reduce_fold(ptrs, g.rank, off, numel, scale, 2, p.data.view(-1), state["adam_exp_avg"].view(-1),
                                    state["adam_exp_avg_sq"].view(-1), 0.0, group["lr"], b1, b2, group["eps"],
-                                   group["weight_decay"], state["adam_step"])
+                                   group["weight_decay"], state["adam_step"], sumsq)
                 fused_done = True
         if fused_done:
             handled.append(n)

@@ -33,6 +33,13 @@ def _is_sequence_parallel_param(name: str) -> bool:
     return ("norm" in name) or ("router." in name) or name.endswith("shared_expert_weight")
 
 
+def _is_tp_sharded_param(name: str) -> bool:
+    """Matrices that tensor parallelism splits (each rank holds a distinct slice); every other dense parameter
+    (embeddings, LM head, MTP heads) is computed on the full sequence by every tensor-parallel rank and is
+    therefore replicated, gradient included."""
+    return name.endswith(("attention.qkv_proj", "attention.o_proj", "mlp.shared_w13", "mlp.shared_w2"))
+
+
 class _FlatGroup:
     """One replicated parameter set + its process group."""
 
@@ -89,8 +96,14 @@ class YvGradientSynchronizer:
     replicated parameters are diverted into the flat buffer instead of being folded immediately)."""
 
     def __init__(self, model: torch.nn.Module, parallel: Any, optimizer: torch.optim.Optimizer,
-                 streaming: bool = False, fused: Optional[bool] = None):
+                 streaming: bool = False, fused: Optional[bool] = None, prescaled: Optional[bool] = None):
         self.parallel, self.optimizer, self.streaming = parallel, optimizer, streaming
+        # ``prescaled``: backward already ran on loss / micro-batches (the non-streaming trainer does), so the
+        # accumulated gradient only needs 1 / dp; otherwise it needs 1 / (dp * micro-batches).
+        self.prescaled = (not streaming) if prescaled is None else bool(prescaled)
+        # squared norm of the reduced gradients that were consumed here (fused fold or consume_external_grad)
+        # and are therefore no longer visible as ``p.grad``; reset at the first micro-batch of a step
+        self.consumed_sq: Optional[torch.Tensor] = None
         # three replication classes (the gradient scale is 1 / (dp * micro-batches) for all of them):
         #   routed experts            replicated over tp x edp   (tensor-parallel peers hold different tokens)
         #   sequence-parallel params  replicated over tp x dp    (norm weights, router, shared-expert mix)
@@ -126,6 +139,17 @@ class YvGradientSynchronizer:
         for g in self.groups:
             for n, p in g.named:
                 self._managed[id(p)] = (g, n)
+        # Routed experts that no group manages (expert-data-parallel size 1) still receive tokens from every
+        # data-parallel rank through the dispatch, and each rank's loss is its LOCAL mean: their gradient is the
+        # sum over ranks and needs the same 1 / dp as the reduced ones.
+        self._local_experts = [p for n, p in expert if id(p) not in self._managed] if parallel.ep_size > 1 else []
+        # unmanaged parameters that are identical on all tensor-parallel ranks: their squared norm is weighted
+        # 1 / tp when the ranks' contributions are summed
+        self._tp_replicated = set()
+        if parallel.tp_size > 1:
+            self._tp_replicated = {id(p) for n, p in dense if id(p) not in self._managed
+                                   and not _is_tp_sharded_param(n)}
+        self.tp_size = parallel.tp_size
         self._hooks = []
         for g in self.groups:
             for n, p in g.named:
@@ -136,11 +160,18 @@ class YvGradientSynchronizer:
     def manages(self, p: torch.nn.Parameter) -> bool:
         return id(p) in self._managed
 
+    def norm_weight(self, p: torch.nn.Parameter) -> float:
+        """Weight of this rank's copy of ``p`` in the global squared gradient norm."""
+        return 1.0 / self.tp_size if id(p) in self._tp_replicated else 1.0
+
     def begin_micro_batch(self, index: int, total: int) -> None:
         self._micro, self._total = index, total
         if index == 0:
             for g in self.groups:
                 g.flat_grad.zero_()
+            if self.groups:
+                dev = self.groups[0].flat_grad.device
+                self.consumed_sq = torch.zeros(1, dtype=torch.float32, device=dev)
 
     def _make_hook(self, g: _FlatGroup, name: str):
         def hook(p: torch.nn.Parameter) -> None:
@@ -155,11 +186,11 @@ class YvGradientSynchronizer:
         """Reduce, update the owned tensors, redistribute.  Called once per optimizer step, after the last
         backward and before ``optimizer.step()``."""
         for g in self.groups:
-            scale = 1.0 / (self.dp_size * self._total)
+            scale = 1.0 / self.dp_size if self.prescaled else 1.0 / (self.dp_size * self._total)
             handled: List[str] = []
             if self.fused and g.symm_grad is not None:
                 from . import fused as fz
-                handled = fz.reduce_scatter_grads(g, scale, self.optimizer)
+                handled = fz.reduce_scatter_grads(g, scale, self.optimizer, sumsq=self.consumed_sq)
             else:
                 shard = g.my_grad_shard()
                 if g.flat_grad.is_cuda:
@@ -173,10 +204,31 @@ class YvGradientSynchronizer:
                     continue
                 grad = g.grad_views[n]
                 if hasattr(self.optimizer, "consume_external_grad"):
+                    if self.consumed_sq is not None:
+                        if grad.is_cuda:
+                            from ..ops import kernels
+                            kernels().sumsq(grad.contiguous(), self.consumed_sq)
+                        else:
+                            self.consumed_sq += grad.float().pow(2).sum()
                     self.optimizer.consume_external_grad(p, grad)
                 else:
                     p.grad = grad
+        if not self.streaming and self.dp_size > 1:
+            for p in self._local_experts:
+                if p.grad is not None:
+                    p.grad.mul_(1.0 / self.dp_size)
         self._pending_gather = True
+
+    @torch.no_grad()
+    def global_sq_norm(self, local_sq: torch.Tensor) -> torch.Tensor:
+        """Squared global gradient norm from each rank's sum over the gradients it alone accounts for: the reduced
+        gradients of the tensors it owns plus the tensors no group manages (unique to the rank: tensor-parallel
+        shards, local experts, its pipeline stage).  Every distinct tensor is owned by exactly one rank, so one
+        all-reduce over all ranks counts each once."""
+        total = local_sq.detach().float().reshape(1).clone()
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(total)
+        return total
 
     @torch.no_grad()
     def after_step(self) -> None:

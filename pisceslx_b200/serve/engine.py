@@ -37,6 +37,7 @@ class YvRequest:
     finish_reason: Optional[str] = None
     on_token: Optional[Callable[[int], None]] = None
     _next_logits: Optional[torch.Tensor] = None
+    preemptions: int = 0
 
     @property
     def ttft(self) -> Optional[float]:
@@ -52,6 +53,7 @@ class YvEngineConfig:
     eos_token_id: Optional[int] = None
     use_cuda_graphs: bool = True          # replay decode steps from CUDA graphs (one graph per batch bucket)
     graph_max_seq_len: int = 8192         # sequences longer than this decode through the eager step
+    status_check_steps: int = 16          # read the kernels' status word every this many decode steps (0 = never)
 
 
 class YvInferenceEngine:
@@ -72,7 +74,8 @@ class YvInferenceEngine:
         self._next_id = 0
         self._lock = threading.Lock()
         self.stats = {"requests": 0, "tokens_generated": 0, "prefill_tokens": 0, "steps": 0, "errors": 0,
-                      "ttft": [], "latency": []}
+                      "preemptions": 0, "ttft": [], "latency": []}
+        self._reserved: Dict[int, int] = {}   # request id -> worst-case number of cache blocks it may ever hold
         self.eos = self.cfg.eos_token_id if self.cfg.eos_token_id is not None else model.cfg.eos_token_id
 
     # ---- request management ---------------------------------------------------------------------------
@@ -94,6 +97,7 @@ class YvInferenceEngine:
     def _finish(self, req: YvRequest, reason: str) -> None:
         req.finished, req.finish_reason, req.finish_time = True, reason, time.perf_counter()
         self.cache.free_sequence(req.request_id)
+        self._reserved.pop(req.request_id, None)
         if req.ttft is not None:
             self.stats["ttft"].append(req.ttft)
         self.stats["latency"].append(req.finish_time - req.arrival)
@@ -110,35 +114,82 @@ class YvInferenceEngine:
         elif len(req.output_ids) >= req.max_new_tokens:
             self._finish(req, "length")
 
+    # ---- admission control ---------------------------------------------------------------------------
+    def _worst_case_blocks(self, req: YvRequest) -> int:
+        remaining = max(req.max_new_tokens - len(req.output_ids), 0)
+        total = len(req.prompt_ids) + len(req.output_ids) + remaining
+        return (total + self.cfg.block_size - 1) // self.cfg.block_size
+
+    def _owed_blocks(self) -> int:
+        """Blocks that running requests may still take: their reservation minus what they already hold.  Running
+        sequences allocate lazily (one block every ``block_size`` tokens), so free blocks alone overstate the room."""
+        owed = 0
+        for rid, need in self._reserved.items():
+            owed += max(need - len(self.cache.tables.get(rid, ())), 0)
+        return owed
+
+    def _preempt_youngest(self) -> bool:
+        """Give the newest running request's blocks back and put it at the head of the queue; its prompt becomes
+        prompt + tokens generated so far, so it resumes by prefill where it stopped."""
+        if len(self.running) <= 1:
+            return False
+        victim = max(self.running, key=lambda r: r.arrival)
+        self.running.remove(victim)
+        self.cache.free_sequence(victim.request_id)
+        self._reserved.pop(victim.request_id, None)
+        victim.preemptions += 1
+        self.stats["preemptions"] += 1
+        self.waiting.appendleft(victim)
+        return True
+
+    def _admit(self, req: YvRequest) -> None:
+        self.cache.add_sequence(req.request_id)
+        self._reserved[req.request_id] = self._worst_case_blocks(req)
+        context = req.prompt_ids + req.output_ids           # non-empty output: resuming after a preemption
+        ids = torch.tensor([context], dtype=torch.long, device=self.device)
+        logits = _prefill(self.model, ids, self.cache, [req.request_id])
+        self.stats["prefill_tokens"] += len(context)
+        tok = int(YvSampler(req.sampling).sample(logits, ids)[0])
+        self.running.append(req)
+        self._emit(req, tok)
+
     # ---- one scheduler iteration ---------------------------------------------------------------------------
     @torch.no_grad()
     def step(self) -> None:
         self.stats["steps"] += 1
-        # admit: prefill waiting requests while there is room
+        # admit: prefill waiting requests while there is room for their WORST case next to what is already promised
         while self.waiting and len(self.running) < self.cfg.max_num_seqs:
             req = self.waiting[0]
-            need = (len(req.prompt_ids) + req.max_new_tokens + self.cfg.block_size - 1) // self.cfg.block_size
-            if need > self.cache.alloc.available():
+            now = (len(req.prompt_ids) + len(req.output_ids) + self.cfg.block_size) // self.cfg.block_size
+            need = max(self._worst_case_blocks(req), now)  # ``now``: prefill plus the first decoded token
+            if need > self.cache.alloc.available() - self._owed_blocks():
                 if not self.running:
                     self.waiting.popleft()
                     req.finished, req.finish_reason = True, "error: prompt does not fit the KV cache"
+                    req.finish_time = time.perf_counter()
                     self.stats["errors"] += 1
                     continue
                 break
             self.waiting.popleft()
-            self.cache.add_sequence(req.request_id)
-            ids = torch.tensor([req.prompt_ids], dtype=torch.long, device=self.device)
-            logits = _prefill(self.model, ids, self.cache, [req.request_id])
-            self.stats["prefill_tokens"] += len(req.prompt_ids)
-            tok = int(YvSampler(req.sampling).sample(logits, ids)[0])
-            self.running.append(req)
-            self._emit(req, tok)
+            self._admit(req)
         self.running = [r for r in self.running if not r.finished]
         if not self.running:
             return
+        # Safety net (reservations make it unreachable unless blocks are shared or taken behind the engine's back):
+        # before ANY slot is appended, make sure every running sequence can take its next token.
+        bs = self.cfg.block_size
+        while True:
+            new_blocks = sum(1 for r in self.running if self.cache.lengths[r.request_id] % bs == 0
+                             and self.cache.lengths[r.request_id] // bs >= len(self.cache.tables[r.request_id]))
+            if new_blocks <= self.cache.alloc.available() or not self._preempt_youngest():
+                break
         # decode: one token for every running sequence in a single batched step
         seq_ids = [r.request_id for r in self.running]
         logits = self.graph.step([r.output_ids[-1] for r in self.running], seq_ids)
+        if self.cfg.status_check_steps and self.device.type == "cuda" \
+                and self.stats["steps"] % self.cfg.status_check_steps == 0:
+            from ..ops import check_status
+            check_status(self.device)      # a bounded wait that ran out or a bad block-table entry raises here
         greedy = all(r.sampling.strategy == "greedy" for r in self.running)
         if greedy:
             toks = logits.argmax(-1).tolist()

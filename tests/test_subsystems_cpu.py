@@ -297,6 +297,43 @@ def test_serving_engine_continuous_batching_matches_single_requests():
     assert len(eng.embeddings("hello")) == m.cfg.hidden_size
 
 
+def test_serving_engine_admission_reserves_worst_case_blocks():
+    """A small cache with concurrent long generations: admission counts the blocks that running requests may still
+    take, so the allocator never runs dry inside a decode step; requests wait and all finish with exact outputs.
+    A request forced in behind the scheduler's back is preempted and resumed, again token for token."""
+    from pisceslx_b200.serve.engine import YvEngineConfig, YvInferenceEngine
+    torch.manual_seed(1)
+    m = build_model(tiny())
+    # 8 blocks of 4 tokens: one request needs ceil((3 + 17) / 4) = 5 blocks in the worst case, so two never fit
+    eng = YvInferenceEngine(m, cfg=YvEngineConfig(max_num_seqs=4, num_blocks=8, block_size=4, eos_token_id=-1,
+                                                  use_cuda_graphs=False))
+    prompts = [[5, 6, 7], [9, 10, 11], [11, 12, 13]]
+    reqs = [eng.add_request(p, max_new_tokens=17) for p in prompts]
+    peak = 0
+    while eng.has_work():
+        eng.step()
+        peak = max(peak, len(eng.running))
+        assert eng.cache.alloc.available() >= 0
+    assert peak == 1                                       # lazily allocated blocks would have let two in
+    for p, r in zip(prompts, reqs):
+        ref, _ = m.generate(torch.tensor([p]), max_new_tokens=17, eos_token_id=-1)
+        assert r.output_ids == ref[0, len(p):].tolist() and r.finish_reason == "length"
+    assert eng.get_stats()["free_blocks"] == 8 and eng.stats["errors"] == 0
+    # preemption path: shrink the reservations by hand so that two requests run and the pool runs out mid-way
+    reqs = [eng.add_request(p, max_new_tokens=17) for p in prompts[:2]]
+    eng._worst_case_blocks = lambda req: 1
+    eng.run_until_done()
+    assert eng.stats["preemptions"] >= 1
+    for p, r in zip(prompts[:2], reqs):
+        ref, _ = m.generate(torch.tensor([p]), max_new_tokens=17, eos_token_id=-1)
+        assert r.output_ids == ref[0, len(p):].tolist()
+    # a request that can never fit is rejected, not queued forever
+    big = eng.add_request(list(range(3, 40)), max_new_tokens=8)
+    del eng._worst_case_blocks
+    eng.run_until_done()
+    assert big.finished and big.finish_reason.startswith("error")
+
+
 def test_openai_server_endpoints():
     from fastapi.testclient import TestClient
     from pisceslx_b200.serve.engine import YvEngineConfig, YvInferenceEngine
