@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--ep", type=int, default=0)
     ap.add_argument("--no-fused-comm", action="store_true", help="NCCL-only collectives (the stated baseline mode)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--state-dtype", default="int8", choices=["int8", "bf16"],
+                    help="Muon momentum storage: int8 block-quantised (stochastic rounding) or bf16")
     ap.add_argument("--ref-limit", type=int, default=1000, help="seconds given to the reference's full-size attempt")
     ap.add_argument("--no-ref-context", action="store_true", help="skip the reduced-layer context run of the reference")
     return ap.parse_args()
@@ -216,7 +218,7 @@ def main() -> None:
     model = build_model(cfg, dev, torch.bfloat16, parallel=par if world > 1 else None, seed=1234)
     tcfg = YvTrainerConfig(micro_batch_size=micro, optimizer="muon", lr=2e-4, weight_decay=0.1, warmup_steps=10,
                            max_steps=10_000, streaming_optimizer=True, clip_grad_norm=0.0, log_steps=1,
-                           track_grad_norm=False, recompute_policy="auto")
+                           track_grad_norm=False, recompute_policy="auto", state_dtype=args.state_dtype)
     trainer = YvTrainer(model, tcfg, parallel=par if world > 1 else None)
 
     # tensor-parallel peers work on the same sequences: batch size and seed follow the data-parallel rank
@@ -313,8 +315,9 @@ def main() -> None:
             "config": {"model": "Yv 7B-class text MoE: 32L h4096 32q/8kv hd128, 64 experts ffn1408 top6 + 2 shared "
                                 "ffn2816, vocab 154856" + ("" if args.layers == 32 else f" [INVALID: {args.layers} layers]"),
                        "global_batch": seqs_rank * par.dp_size, "seq_len": SEQ,
-                       "micro_batch": micro, "parallelism": par_name, "optimizer": "Muon(2-D)+AdamW, bf16 states, "
-                       "gradients consumed inside backward", "activation_recompute": ("per layer, sized from measured memory: " + trainer.recompute_planner.summary())
+                       "micro_batch": micro, "parallelism": par_name, "optimizer": "Muon(2-D)+AdamW, "
+                       + ("int8 block-scaled Muon momentum (128-element blocks, stochastic rounding), bf16 AdamW moments, "
+                          if args.state_dtype == "int8" else "bf16 states, ") + "gradients consumed inside backward", "activation_recompute": ("per layer, sized from measured memory: " + trainer.recompute_planner.summary())
                        if trainer.recompute_planner is not None else "per layer",
                        "l2": "inputs larger than L2 (80 GB of weights and >1 GB of activations per layer)",
                        "fused_comm": bool(cfg.fused_comm) if world > 1 else None},

@@ -46,7 +46,7 @@ class YvTrainerConfig:
     save_steps: int = 0
     output_dir: str = ".pisceslx/ckpt"
     abort_on_non_finite: bool = True
-    state_dtype: Optional[str] = None       # "bf16" | "fp32" | None (= parameter dtype)
+    state_dtype: Optional[str] = None       # "bf16" | "fp32" | "int8" (Muon momentum block-quantised) | None (= parameter dtype)
     recompute_policy: str = "config"        # "config": as the model config says; "auto": sized from measured memory
     optimizer_kwargs: Dict[str, Any] = field(default_factory=dict)
 
@@ -56,7 +56,7 @@ class YvTrainer:
                  optimizer: Optional[torch.optim.Optimizer] = None):
         self.model, self.cfg, self.parallel = model, cfg, parallel
         self.device = next(model.parameters()).device
-        sd = {"bf16": torch.bfloat16, "fp32": torch.float32, None: None}[cfg.state_dtype]
+        sd = {"bf16": torch.bfloat16, "fp32": torch.float32, "int8": torch.int8, None: None}[cfg.state_dtype]
         self.optimizer = optimizer or build_optimizer(model, cfg.optimizer, lr=cfg.lr, weight_decay=cfg.weight_decay,
                                                       state_dtype=sd, **cfg.optimizer_kwargs)
         self.scheduler = YvLRScheduler(self.optimizer, YvLRSchedulerConfig(

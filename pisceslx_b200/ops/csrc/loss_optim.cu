@@ -186,6 +186,80 @@ __global__ void muon_apply_vec_kernel(uint4* __restrict__ p, const uint4* __rest
   }
 }
 
+// ---- block-quantised momentum: int8 values with one fp32 scale per 128 consecutive elements ----------------------
+// 32-bit mix of an element index and a per-call seed (the finaliser of MurmurHash3): the uniform variate of the
+// stochastic rounding.  The same (seed, index) always rounds the same way, so a run is reproducible.
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+  x ^= x >> 16; x *= 0x85ebca6bu; x ^= x >> 13; x *= 0xc2b2ae35u; x ^= x >> 16;
+  return x;
+}
+
+// m <- (first_fold ? mu * m : m) + gscale * g on a quantised m.  Sixteen lanes own one 128-element block (8 elements
+// each: one 8-byte load of q, one 16-byte load of g); the block's new absolute maximum is reduced over the half-warp
+// and the values are re-quantised with stochastic rounding, which keeps the accumulated momentum unbiased over the
+// many folds of a step (round-to-nearest would drop every contribution below half a quantisation step).
+__global__ void momentum_q8_kernel(int8_t* __restrict__ q, float* __restrict__ scale, const __nv_bfloat16* __restrict__ g,
+                                   int64_t nblocks, float mu, float gscale, int first_fold, uint32_t seed) {
+  const int lane16 = threadIdx.x & 15;
+  const int64_t hw = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 4;     // half-warp index
+  const int64_t nhw = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 4;
+  // every lane of a warp runs the same number of iterations (the shuffles below need all 32 lanes)
+  const int64_t iters = (nblocks + nhw - 1) / nhw;
+  for (int64_t it = 0; it < iters; ++it) {
+    const int64_t b = hw + it * nhw;
+    const bool live = b < nblocks;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    const int64_t e0 = b * 128 + lane16 * 8;
+    if (live) {
+      const float sc = scale[b] * (first_fold ? mu : 1.f);
+      const uint2 qraw = *reinterpret_cast<const uint2*>(q + e0);
+      const int8_t* qb = reinterpret_cast<const int8_t*>(&qraw);
+      float gv[8];
+      unpack8(*reinterpret_cast<const uint4*>(g + e0), gv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = static_cast<float>(qb[j]) * sc + gv[j] * gscale;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (live) {
+      const float ns = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+      const float inv = 1.f / ns;
+      uint2 out;
+      int8_t* ob = reinterpret_cast<int8_t*>(&out);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t r = hash_u32(static_cast<uint32_t>(e0 + j) * 0x9e3779b9u ^ static_cast<uint32_t>((e0 + j) >> 32) ^ seed);
+        const float u = static_cast<float>(r >> 8) * (1.f / 16777216.f);          // [0, 1)
+        float t = floorf(v[j] * inv + u);
+        t = fminf(fmaxf(t, -127.f), 127.f);
+        ob[j] = static_cast<int8_t>(t);
+      }
+      *reinterpret_cast<uint2*>(q + e0) = out;
+      if (lane16 == 0) scale[b] = ns;
+    }
+  }
+}
+
+// out (bf16) <- q * scale, eight elements per thread
+__global__ void dequant_q8_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale,
+                                  __nv_bfloat16* __restrict__ out, int64_t nvec) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float sc = scale[i >> 4];
+    const uint2 qraw = *reinterpret_cast<const uint2*>(q + i * 8);
+    const int8_t* qb = reinterpret_cast<const int8_t*>(&qraw);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = static_cast<float>(qb[j]) * sc;
+    reinterpret_cast<uint4*>(out)[i] = pack8(f);
+  }
+}
+
 // m <- (first_fold ? mu * m : m) + gscale * g ;   out <- nesterov ? gscale*g + mu*m : m   (out optional)
 __global__ void momentum_kernel(__nv_bfloat16* __restrict__ m, const __nv_bfloat16* __restrict__ g,
                                 __nv_bfloat16* __restrict__ out, int64_t n, float mu, float gscale, int nesterov,
@@ -442,6 +516,23 @@ int launch_momentum(void* m, const void* g, void* out, int64_t n, float mu, floa
         YV_BFM(m) + done, YV_BF(g) + done, out != nullptr ? YV_BFM(out) + done : nullptr, n - done, mu, gscale,
         nesterov, first_fold);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_momentum_q8(void* q, float* scale, const void* g, int64_t n, float mu, float gscale, int first_fold,
+                       uint32_t seed, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((n & 127) != 0 || !aligned16(g) || (reinterpret_cast<uintptr_t>(q) & 7u) != 0) return -1;
+  const int64_t nblocks = n >> 7;
+  momentum_q8_kernel<<<grid_for(nblocks * 16, 256), 256, 0, stream>>>(
+      static_cast<int8_t*>(q), scale, YV_BF(g), nblocks, mu, gscale, first_fold, seed);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_dequant_q8(const void* q, const float* scale, void* out, int64_t n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((n & 127) != 0 || !aligned16(out) || (reinterpret_cast<uintptr_t>(q) & 7u) != 0) return -1;
+  dequant_q8_kernel<<<grid_for(n >> 3, 256), 256, 0, stream>>>(static_cast<const int8_t*>(q), scale, YV_BFM(out), n >> 3);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -198,6 +198,12 @@ int launch_adamw(const AdamWArgs& a, cudaStream_t stream);
 // m = mu * m + g  (fold a gradient into a momentum buffer);  optionally out = g + mu * m (Nesterov)
 int launch_momentum(void* m, const void* g, void* out, int64_t n, float mu, float gscale, int nesterov,
                     int first_fold, cudaStream_t stream);
+// The same fold on a block-quantised momentum: q int8 [n], scale fp32 [n / 128] (one per 128 consecutive elements),
+// re-quantised with stochastic rounding keyed by (seed, element index).  n must be a multiple of 128.
+int launch_momentum_q8(void* q, float* scale, const void* g, int64_t n, float mu, float gscale, int first_fold,
+                       uint32_t seed, cudaStream_t stream);
+// out (bf16) = q * scale
+int launch_dequant_q8(const void* q, const float* scale, void* out, int64_t n, cudaStream_t stream);
 // p = p * (1 - lr*wd) - lr*scale * u
 int launch_muon_apply(void* p, const void* u, int64_t n, float lr, float wd, float scale, cudaStream_t stream);
 // x *= 1 / max(||x||_F, eps) per matrix of a batch;  norms scratch fp32 [batch]

@@ -30,6 +30,33 @@ import torch
 from ..ops import kernels, reference as ref, status_word
 
 NS_COEFFS = ref.MUON_NS_COEFFS
+Q8_BLOCK = 128            # elements per scale of the int8 momentum (the reference's Ink optimizer keeps block-quantised
+                          # int8 / int4 moments too, opss/optim/ink/optimizer.py:84-638)
+
+
+def dequantize_q8(q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """int8 values + per-128-element scales -> dense tensor of ``q``'s shape."""
+    if q.is_cuda and dtype == torch.bfloat16:
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+        kernels().dequant_q8(q, scale, out)
+        return out
+    return (q.view(-1, Q8_BLOCK).float() * scale.view(-1, 1)).view(q.shape).to(dtype)
+
+
+def fold_q8_reference(q: torch.Tensor, scale: torch.Tensor, grad: torch.Tensor, mu: float, gscale: float, first: bool,
+                      generator: Optional[torch.Generator] = None) -> None:
+    """PyTorch form of the quantised momentum fold (CPU path and oracle of the kernel's arithmetic): de-quantise,
+    ``m = (mu * m if first else m) + gscale * g``, new per-block scale ``max|m| / 127``, stochastic rounding."""
+    m = q.view(-1, Q8_BLOCK).float() * scale.view(-1, 1)
+    if first:
+        m = m * mu
+    m = m + grad.reshape(-1, Q8_BLOCK).float() * gscale
+    amax = m.abs().amax(dim=1)
+    ns = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    u = torch.rand(m.shape, generator=generator, device=m.device)
+    t = torch.floor(m / ns.view(-1, 1) + u).clamp_(-127, 127)
+    q.copy_(t.to(torch.int8).view(q.shape))
+    scale.copy_(ns)
 
 
 def split_spec_for(name: str, p: torch.Tensor, cfg=None) -> Optional[List[Tuple[int, int]]]:
@@ -147,8 +174,14 @@ class YvMuon(torch.optim.Optimizer):
         if not st:
             dt = self.state_dtype or p.dtype
             if group["use_muon"]:
-                st["momentum_buffer"] = torch.zeros_like(p, dtype=dt)
+                if dt == torch.int8 and p.numel() % Q8_BLOCK == 0:
+                    # block-quantised momentum: int8 values + one fp32 scale per 128 consecutive elements
+                    st["momentum_q"] = torch.zeros_like(p, dtype=torch.int8)
+                    st["momentum_scale"] = torch.ones(p.numel() // Q8_BLOCK, dtype=torch.float32, device=p.device)
+                else:
+                    st["momentum_buffer"] = torch.zeros_like(p, dtype=p.dtype if dt == torch.int8 else dt)
             else:
+                dt = p.dtype if dt == torch.int8 else dt      # AdamW moments stay in the parameter dtype
                 st["adam_step"] = 0
                 st["adam_exp_avg"] = torch.zeros_like(p, dtype=dt)
                 st["adam_exp_avg_sq"] = torch.zeros_like(p, dtype=dt)
@@ -165,8 +198,20 @@ class YvMuon(torch.optim.Optimizer):
     def _fold(self, p: torch.Tensor, grad: torch.Tensor, group: Dict[str, Any], first: bool,
               want_update: bool) -> Optional[torch.Tensor]:
         st = self._state_for(p, group)
-        buf = st["momentum_buffer"]
         mu = group["momentum"]
+        if "momentum_q" in st:
+            q, sc = st["momentum_q"], st["momentum_scale"]
+            if p.is_cuda and grad.dtype == torch.bfloat16:
+                self._q8_calls = getattr(self, "_q8_calls", 0) + 1
+                seed = (self._step_count * 1000003 + self._q8_calls * 7919) & 0x7FFFFFFF
+                kernels().momentum_fold_q8(q, sc, grad.contiguous(), mu, self._grad_scale, first, seed)
+            else:
+                fold_q8_reference(q, sc, grad, mu, self._grad_scale, first)
+            if not want_update:
+                return None
+            m = dequantize_q8(q, sc, p.dtype)
+            return (grad.to(p.dtype) * self._grad_scale).add(m, alpha=mu) if group["nesterov"] else m
+        buf = st["momentum_buffer"]
         if p.is_cuda and buf.dtype == torch.bfloat16 and grad.dtype == torch.bfloat16:
             out = torch.empty_like(buf) if want_update else None
             kernels().momentum_fold(buf, grad.contiguous(), out, mu, self._grad_scale, bool(group["nesterov"]), first)
@@ -325,7 +370,10 @@ class YvMuon(torch.optim.Optimizer):
                 if not st:
                     continue
                 if group["use_muon"]:
-                    self._apply_muon(p, st["momentum_buffer"], group)
+                    if "momentum_q" in st:
+                        self._apply_muon(p, dequantize_q8(st["momentum_q"], st["momentum_scale"], p.dtype), group)
+                    else:
+                        self._apply_muon(p, st["momentum_buffer"], group)
                 elif st.get("grad_acc") is not None:
                     self._apply_adamw(p, st.pop("grad_acc"), group)
         self._grad_scale = 1.0

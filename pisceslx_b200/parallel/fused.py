@@ -279,7 +279,9 @@ def reduce_scatter_grads(g: Any, scale: float, optimizer: Any = None, sumsq: Any
         if optimizer is not None and streaming and numel % 2 == 0 and g.flat_grad.dtype == _BF16:
             group = optimizer._group_of(p)
             state = optimizer._state_for(p, group)
-            if group["use_muon"]:
+            if group["use_muon"] and "momentum_buffer" not in state:
+                pass                                        # quantised momentum: reduce here, fold through the optimizer
+            elif group["use_muon"]:
                 K.zero_reduce_fold(ptrs, g.rank, off, numel, scale, 1, None, state["momentum_buffer"].view(-1), None,
                                    group["momentum"], 0.0, 0.0, 0.0, 0.0, 0.0, 1, sumsq)
                 fused_done = True

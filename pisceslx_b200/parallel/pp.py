@@ -9,8 +9,11 @@ and the LM head) and the schedules below move real tensors:
   * ``1f1b``   warm-up forwards, then one forward / one backward alternation, then the cool-down backwards, which
                bounds the number of live micro-batch activations by the pipeline depth.
 
-Receives for the next micro-batch are posted before the current micro-batch computes (``irecv`` on the NCCL stream),
-so stage-to-stage transfers overlap with compute.  Send / recv stays on NCCL by design.
+The activation receive of micro-batch i+1 is posted before micro-batch i computes (``irecv`` runs on the
+communicator's own stream), so the transfer from the previous stage overlaps with this stage's compute; sends are
+asynchronous and are only waited for at the end of the step.  In 1F1B the previous stage always sends micro-batch
+i+1 before it waits for a gradient that depends on this stage having consumed it, so the early receive cannot
+deadlock.  Send / recv stays on NCCL by design.
 """
 from __future__ import annotations
 
@@ -72,10 +75,17 @@ class YvPipelineStage:
         sends: List[Any] = []
         losses: List[torch.Tensor] = []
         fwd_i = bwd_i = 0
+        # activation receive posted one micro-batch ahead of the compute that consumes it
+        pending = None if (self.first or n == 0) else self._irecv(shape, self.par.pp_prev)
+        self.prefetched_receives = 0
 
         def do_forward():
-            nonlocal fwd_i
-            recv = None if self.first else self._irecv(shape, self.par.pp_prev)
+            nonlocal fwd_i, pending
+            recv = pending
+            pending = None
+            if not self.first and fwd_i + 1 < n:
+                pending = self._irecv(shape, self.par.pp_prev)
+                self.prefetched_receives += 1
             hin, out, send = self.forward_micro(micro_batches[fwd_i], recv)
             if send is not None:
                 sends.append(send)

@@ -30,10 +30,26 @@ class PiscesLxSourceFile:
 class PiscesLxRepositoryScanner:
     """Yields the parsed Python files under a root, skipping caches, build output and hidden folders."""
 
-    SKIP = {"__pycache__", ".git", "build", "csrc", "_work", "gpurun_out", "baseline"}
+    SKIP = {"__pycache__", ".git", "build", "csrc"}
 
-    def __init__(self, root: str):
+    def __init__(self, root: str, skip: Optional[Iterable[str]] = None):
+        """``skip``: further folder names to leave out; by default the folders that the root's ``.gitignore`` lists
+        (scratch and vendored trees are not the project's source)."""
         self.root = root
+        extra = set(skip) if skip is not None else self._gitignored_dirs(root)
+        self.SKIP = set(self.SKIP) | extra
+
+    @staticmethod
+    def _gitignored_dirs(root: str) -> set:
+        out = set()
+        try:
+            for line in open(os.path.join(root, ".gitignore"), encoding="utf-8"):
+                line = line.strip()
+                if line and not line.startswith("#") and line.endswith("/") and "*" not in line:
+                    out.add(line.strip("/").split("/")[0])
+        except OSError:
+            pass
+        return out
 
     def files(self) -> Iterator[PiscesLxSourceFile]:
         for d, dirs, names in os.walk(self.root):

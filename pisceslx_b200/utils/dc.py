@@ -30,38 +30,8 @@ from typing import Any, Dict, Iterator, List, Optional
 import torch
 
 
-def _home() -> Path:
-    return Path(os.environ.get("PISCESLX_HOME", ".pisceslx"))
-
-
-class PiscesLxPaths:
-    def __init__(self, home: Optional[Path] = None):
-        self.home = Path(home) if home else _home()
-
-    def logs(self, name: str = "default") -> Path:
-        p = self.home / "logs" / name
-        p.mkdir(parents=True, exist_ok=True)
-        return p
-
-    def ckpt(self) -> Path:
-        return self.home / "ckpt"
-
-    def runs(self) -> Path:
-        return self.home / "runs"
-
-    def cache(self) -> Path:
-        p = self.home / "cache"
-        p.mkdir(parents=True, exist_ok=True)
-        return p
-
-    def describe(self) -> Dict[str, str]:
-        return {"home": str(self.home), "ckpt": str(self.ckpt()), "runs": str(self.runs()), "cache": str(self.cache())}
-
-    def clear_cache(self) -> int:
-        c = self.cache()
-        n = sum(1 for _ in c.rglob("*") if _.is_file())
-        shutil.rmtree(c, ignore_errors=True)
-        return n
+from .paths import PiscesLxPaths, _home  # noqa: F401,E402  (defined in utils/paths.py)
+from .seed import PiscesLxDeterminism  # noqa: F401,E402  (defined in utils/seed.py)
 
 
 class PiscesLxLogger:
@@ -162,22 +132,6 @@ class PiscesLxTracing:
     def export_chrome_trace(self, path: str) -> None:
         with open(path, "w") as f:
             json.dump({"traceEvents": self.events, "displayTimeUnit": "ms"}, f)
-
-
-class PiscesLxDeterminism:
-    @staticmethod
-    def seed_everything(seed: int, deterministic: bool = False) -> None:
-        random.seed(seed)
-        try:
-            import numpy as np
-            np.random.seed(seed % (2 ** 32))
-        except Exception:
-            pass
-        torch.manual_seed(seed)
-        if torch.cuda.is_available():
-            torch.cuda.manual_seed_all(seed)
-        if deterministic:
-            torch.use_deterministic_algorithms(True, warn_only=True)
 
 
 class PiscesLxDeviceResolver:

@@ -410,6 +410,60 @@ def test_muon_streaming_kernels_vector_and_tail(Y, n, offset, nesterov, first):
     assert close(p, p0 * (1 - 1e-2 * 0.1) - 1e-2 * 0.7 * g.float())
 
 
+@pytest.mark.parametrize("first", [True, False])
+def test_momentum_q8_fold_within_one_step_and_unbiased(Y, first):
+    """Block-quantised momentum fold against the exact fp32 fold: each element lands within one quantisation step
+    of its block (stochastic rounding), the block scale is max|m| / 127, and the rounding is unbiased."""
+    torch.manual_seed(31)
+    n = 128 * 4099                                           # odd block count: the grid's ragged last pass
+    m0 = torch.randn(n, device=DEV) * torch.rand(n // 128, device=DEV).repeat_interleave(128)
+    sc = (m0.view(-1, 128).abs().amax(1) / 127).clamp_min(1e-30)
+    q = torch.round(m0.view(-1, 128) / sc.view(-1, 1)).clamp(-127, 127).to(torch.int8).view(-1)
+    m_start = q.view(-1, 128).float() * sc.view(-1, 1)
+    g = (torch.randn(n, device=DEV) * 0.05).bfloat16()
+    mu, gs = 0.95, 0.25
+    exact = (m_start * mu if first else m_start) + g.float().view(-1, 128) * gs
+    q1, sc1 = q.clone(), sc.clone()
+    Y.momentum_fold_q8(q1, sc1, g, mu, gs, first, 12345)
+    new_scale = exact.abs().amax(1) / 127
+    assert torch.allclose(sc1, new_scale, rtol=1e-5, atol=1e-30)
+    got = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    Y.dequant_q8(q1, sc1, got)
+    err = (q1.view(-1, 128).float() * sc1.view(-1, 1) - exact).abs() / sc1.view(-1, 1)
+    assert float(err.max()) <= 1.0 + 1e-3
+    assert torch.allclose(got.float().view(-1, 128), q1.view(-1, 128).float() * sc1.view(-1, 1), rtol=2 ** -7, atol=0)
+    # unbiased: the mean signed error over 500 k elements is far below half a step; another seed rounds differently
+    assert abs(float(((q1.view(-1, 128).float() * sc1.view(-1, 1) - exact) / sc1.view(-1, 1)).mean())) < 5e-3
+    q2, sc2 = q.clone(), sc.clone()
+    Y.momentum_fold_q8(q2, sc2, g, mu, gs, first, 999)
+    assert not torch.equal(q1, q2)
+    q3, sc3 = q.clone(), sc.clone()
+    Y.momentum_fold_q8(q3, sc3, g, mu, gs, first, 12345)
+    assert torch.equal(q1, q3)                               # same seed, same rounding
+
+
+def test_muon_int8_momentum_tracks_bf16_momentum():
+    """Thirty-two folds per step for three steps (the streaming trainer's pattern): the de-quantised int8 momentum
+    stays within 2 % (relative Frobenius error) of the fp32 accumulation."""
+    torch.manual_seed(32)
+    from pisceslx_b200.optim.muon import YvMuon, dequantize_q8
+    p = torch.nn.Parameter(torch.randn(256, 512, device=DEV).bfloat16())
+    opt = YvMuon([("w", p)], state_dtype=torch.int8)
+    group = opt.param_groups[0]
+    exact = torch.zeros(256, 512, device=DEV)
+    for step in range(3):
+        opt._step_count = step
+        for i in range(32):
+            g = (torch.randn(256, 512, device=DEV) * 0.1).bfloat16()
+            opt._grad_scale = 1.0 / 32
+            opt._fold(p, g, group, i == 0, False)
+            exact = (exact * 0.95 if i == 0 else exact) + g.float() / 32
+    st = opt.state[p]
+    assert st["momentum_q"].dtype == torch.int8 and "momentum_buffer" not in st
+    m = dequantize_q8(st["momentum_q"], st["momentum_scale"])
+    assert rel(m, exact) < 2e-2
+
+
 def test_frob_normalize_vector_and_scalar(Y):
     torch.manual_seed(22)
     for shape in ((5, 64, 96), (5, 7, 143)):

@@ -38,6 +38,35 @@ def test_newton_schulz_orthogonalises():
         assert torch.allclose(o, u @ torch.diag(s) @ vh, atol=1e-3)
 
 
+def test_muon_int8_momentum_cpu_path_and_state_dict():
+    """The quantised-momentum option on CPU (PyTorch fold): state is int8 + per-128 scales, survives a state-dict
+    round trip, and a few steps move the weights like the bf16-state optimizer does."""
+    from pisceslx_b200.optim.muon import YvMuon, dequantize_q8
+    torch.manual_seed(0)
+    w0 = torch.randn(128, 256)
+    outs = {}
+    for name, sd in (("q8", torch.int8), ("fp32", None)):
+        p = torch.nn.Parameter(w0.clone())
+        opt = YvMuon([("layer.w", p)], lr=1e-2, state_dtype=sd, nesterov=False)
+        g = torch.Generator().manual_seed(1)
+        for _ in range(3):
+            p.grad = torch.randn(128, 256, generator=g)
+            opt.step()
+        outs[name] = (p.detach().clone(), opt)
+    st = outs["q8"][1].state_dict()["state"][0]
+    assert st["momentum_q"].dtype == torch.int8 and st["momentum_scale"].numel() == 128 * 256 // 128
+    ref_m = outs["fp32"][1].state_dict()["state"][0]["momentum_buffer"]
+    got_m = dequantize_q8(st["momentum_q"], st["momentum_scale"], torch.float32)
+    assert (got_m - ref_m).norm() / ref_m.norm() < 2e-2
+    assert (outs["q8"][0] - outs["fp32"][0]).norm() / (outs["fp32"][0] - w0).norm() < 0.1
+    # tensors whose size is not a multiple of 128 keep a dense momentum
+    p = torch.nn.Parameter(torch.randn(3, 50))
+    opt = YvMuon([("odd.w", p)], state_dtype=torch.int8)
+    p.grad = torch.randn(3, 50)
+    opt.step()
+    assert "momentum_buffer" in opt.state[p]
+
+
 def test_muon_param_split_and_adamw_formula():
     from pisceslx_b200.optim import YvMuon
     from pisceslx_b200.ops.reference import adamw_step

@@ -48,15 +48,22 @@ def test_noalloc_decode_matches_regular_entry_point_twice():
     for seed, lens, hq, hk, d, splits in cases:
         q, kc, vc, bt, sl = _case(seed, lens, hq, hk, d, splits)
         o = torch.zeros_like(q)
+        args = (q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), o.data_ptr(), len(lens), hq, hk,
+                d, kc.shape[1], bt.shape[1], kc.shape[0], splits, 1.0 / math.sqrt(d), stream)
+        # The first launch of a kernel makes the driver load its code (lazy module loading), which moves the driver's
+        # free-memory figure although nobody allocated; the figures are therefore taken around a second call.
+        rc = fn(*args)
+        assert rc == 0, lib.yv_noalloc_strerror(rc)
+        torch.cuda.synchronize()
+        o.zero_()
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
         free_before = torch.cuda.mem_get_info()[0]          # the driver's view: a raw cudaMalloc would move it
-        rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), sl.data_ptr(), o.data_ptr(), len(lens), hq, hk,
-                d, kc.shape[1], bt.shape[1], kc.shape[0], splits, 1.0 / math.sqrt(d), stream)
+        rc = fn(*args)
         assert rc == 0, lib.yv_noalloc_strerror(rc)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before                  # nothing was taken from torch's allocator
-        assert torch.cuda.mem_get_info()[0] >= free_before              # ... nor from the driver
+        assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)  # ... nor from the driver (scratch would be 8 MiB)
         assert lib.yv_noalloc_status(0, stream) == 0                    # no wait ran out, no index was cut
         ref = F_.paged_decode(q, kc, vc, bt, sl, splits=splits)
         # same kernels, same split count, fixed-order merge: the two entry points agree bit for bit (the regular
