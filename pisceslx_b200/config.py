@@ -109,6 +109,9 @@ class YvConfig:
     kv_lora_rank: int = 512
     mla_q_lora_rank: Optional[int] = None
     mla_rope_dim: int = 64
+    use_enhanced_mla: bool = False           # decoupled RoPE: a shared rotary key slice decompressed from the latent
+    attention_output_gate: bool = False      # per-head sigmoid gate on the attention output, computed from the input
+    attention_sink_tokens: int = 0           # learned sink tokens prepended to every sequence while training
     use_flash_attention: bool = True
     use_sliding_window: bool = False
     streaming_window: int = 16384

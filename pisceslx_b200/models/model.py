@@ -55,6 +55,8 @@ class YvModel(nn.Module):
         if self.is_last_stage:
             self.norm = YvRMSNorm(cfg.hidden_size, cfg.layer_norm_eps)
         rot = cfg.partial_rope_dim if cfg.use_partial_rope else cfg.head_dim
+        if getattr(cfg, "use_mla", False) and getattr(cfg, "use_enhanced_mla", False):
+            rot = min(cfg.mla_rope_dim, cfg.head_dim)        # decoupled RoPE: only the shared key slice is rotated
         scaling = "yarn" if cfg.use_dynamic_yarn else ("linear" if cfg.linear_rope_scale != 1.0 else "none")
         factor = cfg.rope_scaling_factor if cfg.use_dynamic_yarn else cfg.linear_rope_scale
         self.rotary = YvRotaryEmbedding(rot, min(cfg.max_position_embeddings, 8192), cfg.rope_theta, scaling, factor,

@@ -231,10 +231,14 @@ __global__ void momentum_q8_kernel(int8_t* __restrict__ q, float* __restrict__ s
       const float inv = 1.f / ns;
       uint2 out;
       int8_t* ob = reinterpret_cast<int8_t*>(&out);
+      // two hashes per thread: each 32-bit value supplies four 8-bit uniform variates (1/256 resolution bounds the
+      // rounding bias at 1/512 of a quantisation step)
+      const uint32_t key = static_cast<uint32_t>(e0 >> 3) * 0x9e3779b9u ^ static_cast<uint32_t>(e0 >> 35) ^ seed;
+      const uint32_t r0 = hash_u32(key), r1 = hash_u32(key ^ 0x68bc21ebu);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint32_t r = hash_u32(static_cast<uint32_t>(e0 + j) * 0x9e3779b9u ^ static_cast<uint32_t>((e0 + j) >> 32) ^ seed);
-        const float u = static_cast<float>(r >> 8) * (1.f / 16777216.f);          // [0, 1)
+        const uint32_t byte = ((j < 4 ? r0 : r1) >> (8 * (j & 3))) & 0xffu;
+        const float u = (static_cast<float>(byte) + 0.5f) * (1.f / 256.f);          // (0, 1), mean 1/2
         float t = floorf(v[j] * inv + u);
         t = fminf(fmaxf(t, -127.f), 127.f);
         ob[j] = static_cast<int8_t>(t);

@@ -200,3 +200,40 @@ def test_recompute_wrapper_matches_plain_backward():
     lin.weight.grad = None
     lin(x).relu().sum().backward()
     assert torch.allclose(gx, x.grad) and torch.allclose(gw, lin.weight.grad)
+
+
+@pytest.mark.parametrize("options", [
+    dict(use_mla=True, kv_lora_rank=32),
+    dict(use_mla=True, kv_lora_rank=32, mla_q_lora_rank=48, use_enhanced_mla=True, mla_rope_dim=16, use_qk_norm=True),
+    dict(attention_output_gate=True, learnable_attention_scale=True),
+])
+def test_main_attention_options_train_roundtrip_and_decode(options):
+    """The main attention's configuration options (latent KV with the sigmoid embedding gate, low-rank queries,
+    decoupled rotary slice, QK-norm, learned scale, per-head output gate): each trains, round-trips through the
+    reference-named state dict, and decodes from the paged cache exactly like a full forward."""
+    import torch
+    from pisceslx_b200 import YvConfig
+    from pisceslx_b200.models import build_model
+    cfg = YvConfig.tiny_text_moe(vocab_size=512)
+    cfg.n_layer = 2
+    for k, v in options.items():
+        setattr(cfg, k, v)
+    m = build_model(cfg, "cpu", torch.float32, seed=3)
+    ids = torch.randint(0, 512, (2, 24), generator=torch.Generator().manual_seed(0))
+    out = m(input_ids=ids, labels=ids)
+    out["loss"].backward()
+    att = m.model.layers[0].attention
+    grads = [p.grad for p in att.parameters()]
+    assert all(g is not None and torch.isfinite(g).all() for g in grads)
+    sd = m.to_reference_state_dict()
+    if options.get("use_mla"):
+        for name in ("kv_compress", "embedding_gate", "k_decompress", "v_decompress"):
+            assert f"layers.0.attention.{name}.weight" in sd           # the reference's parameter names
+        assert att.latent_for_cache.shape == (48, 32)                   # what a latent cache stores per token
+    m2 = build_model(cfg, "cpu", torch.float32, seed=9)
+    m2.load_reference_state_dict(sd, strict=True)
+    assert abs(float(m2(input_ids=ids, labels=ids)["loss"]) - float(out["loss"])) < 1e-5
+    m.eval()
+    gen, _ = m.generate(ids[:1, :6], max_new_tokens=4, eos_token_id=-1)
+    full = m(input_ids=gen[:, :-1])["logits"][0, 5:].argmax(-1)
+    assert torch.equal(full, gen[0, 6:])
