@@ -55,8 +55,55 @@ def build_trainer_config(model_cfg: YvConfig, stage_cfg: Dict[str, Any], args: A
 
 
 class PiscesLxTrainOrchestrator:
+    CONTROL_SYNC_STEPS = 10            # multi-rank runs agree on stop / pause every this many steps
+
     def __init__(self, args: Any):
         self.args = args
+
+    @staticmethod
+    def apply_policy(model_cfg: YvConfig, stage_cfg: Dict[str, Any], tcfg: YvTrainerConfig, args: Any, par: Any,
+                     seq_len: int) -> list:
+        """Run the convergence and memory rule sets (``engine.policy``) over the merged configuration layers and copy
+        their decisions into the trainer configuration; explicit command-line values are left alone."""
+        from .policy import YvTrainingPlan, apply_convergence_policy, apply_memory_policy
+        plan = YvTrainingPlan.from_layers(model_cfg.extra.get("training_config"), stage_cfg, stage=str(args.stage))
+        plan.max_steps = tcfg.max_steps
+        plan.optimizer = tcfg.optimizer
+        notes = apply_convergence_policy(plan, model_cfg, getattr(args, "model_name_or_path", None),
+                                         getattr(args, "resume_ckpt", None))
+        tcfg.scheduler, tcfg.warmup_steps, tcfg.min_lr_ratio = plan.scheduler, plan.warmup_steps, plan.min_lr_ratio
+        if getattr(args, "save_steps", None) is None and stage_cfg.get("save_steps") is None:
+            tcfg.save_steps = plan.save_steps
+        tcfg.log_steps = tcfg.log_steps or plan.log_steps
+        if plan.gradient_checkpointing is False:
+            model_cfg.use_gradient_checkpointing = False
+        if par.device.type == "cuda":
+            plan.streaming_optimizer = tcfg.streaming_optimizer
+            notes += apply_memory_policy(plan, model_cfg, tp=par.tp_size, ep=par.ep_size, dp=par.dp_size, seq_len=seq_len)
+            tcfg.streaming_optimizer = tcfg.streaming_optimizer or plan.streaming_optimizer
+            if tcfg.state_dtype is None:
+                tcfg.state_dtype = plan.state_dtype
+            if tcfg.streaming_optimizer:
+                tcfg.clip_grad_norm = 0.0                    # gradients are folded as produced: nothing left to clip
+            tcfg.recompute_policy = plan.recompute_policy
+            if getattr(args, "micro_batch_size", None) is None and "micro_batch_size" not in stage_cfg:
+                tcfg.micro_batch_size = plan.micro_batch_size
+        return notes
+
+    @staticmethod
+    def _sync_control(reporter: Any, par: Any) -> bool:
+        """Broadcast rank 0's stop / pause state; paused ranks wait here together.  Returns True to stop."""
+        import torch.distributed as dist
+        while True:
+            if reporter is not None:
+                reporter.poll_control()
+            flags = torch.tensor([int(bool(reporter and reporter.stop_requested)), int(bool(reporter and reporter.paused))],
+                                 dtype=torch.int32, device=par.device)
+            dist.broadcast(flags, src=0)
+            stop, paused = bool(flags[0].item()), bool(flags[1].item())
+            if stop or not paused:
+                return stop
+            time.sleep(0.5)
 
     def run(self, args: Any) -> int:
         from ..data.datasets import build_dataloader
@@ -94,13 +141,17 @@ class PiscesLxTrainOrchestrator:
         model = build_model(model_cfg, par.device, dtype, parallel=par if world > 1 else None, seed=args.seed)
         attach_optional_components(model, model_cfg, par)
         tcfg.streaming_optimizer = bool(stage_cfg.get("streaming_optimizer", False))
+        policy_notes = self.apply_policy(model_cfg, stage_cfg, tcfg, args, par, seq_len)
         trainer = YvTrainer(model, tcfg, parallel=par if world > 1 else None)
         store = PiscesLxRunStore(Path(args.run_dir) if args.run_dir else None)
         run_id = args.run_id or PiscesLxRunIdFactory.new("train")
         reporter = None
         if par.rank == 0:
             if not (store.run_dir(run_id) / "state.json").exists():
-                store.init_run(run_id, {"command": "train", "args": {k: v for k, v in vars(args).items()}})
+                store.init_run(run_id, {"command": "train", "args": {k: v for k, v in vars(args).items()},
+                                        "policy": policy_notes})
+            for note in policy_notes:
+                print(f"[policy] {note}", flush=True)
             store.update_state(run_id, status="running", pid=os.getpid())
             reporter = PiscesLxTrainingRunReporter(store, run_id, trainer)
             trainer.callbacks.append(reporter)
@@ -113,9 +164,14 @@ class PiscesLxTrainOrchestrator:
             for batch_t in loader:
                 if trainer.global_step >= tcfg.max_steps or (reporter is not None and reporter.stop_requested):
                     break
-                while reporter is not None and reporter.paused and not reporter.stop_requested:
+                while reporter is not None and reporter.paused and not reporter.stop_requested and world == 1:
                     time.sleep(0.5)
                     reporter.poll_control()
+                if world > 1 and trainer.global_step % self.CONTROL_SYNC_STEPS == 0:
+                    # rank 0 reads the control channel; every rank must leave (or wait) at the same step, or the
+                    # next collective never completes
+                    if self._sync_control(reporter, par):
+                        break
                 res = trainer.train_step(batch_t)
                 if par.rank == 0 and trainer.global_step % max(tcfg.log_steps, 1) == 0:
                     print(f"step {res['global_step']} loss {res['loss']:.4f} lr {res['learning_rate']:.3e} "

@@ -129,7 +129,7 @@ void gemm_grouped_k(const Tensor& a, const Tensor& b, Tensor c, const Tensor& se
 
 // Batched: a [G, M, K] (or [G, K, M] when a_mn), b [G, N, K] (or [G, K, N] when b_mn), c [G, M, N]; contiguous.
 void gemm_batched(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, bool accumulate, int64_t bn,
-                  const c10::optional<Tensor>& status) {
+                  const c10::optional<Tensor>& status, bool symmetric) {
   check_bf16(a, "a"); check_bf16(b, "b"); check_cuda(c, "c");
   TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3 && a.is_contiguous() && b.is_contiguous() &&
               c.is_contiguous(), "gemm_batched: contiguous 3-D operands expected");
@@ -149,13 +149,14 @@ void gemm_batched(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_
   g.accumulate = accumulate ? 1 : 0;
   g.bn = static_cast<int>(bn);
   g.status = statusp(status);
+  g.symmetric = symmetric;
   check_rc(yv::launch_gemm(g, cur_stream()), "gemm_batched");
 }
 
 // c[g] = ec * (a[g] @ b[g]^T) + eb * cin[g] + ea * I   (square [n, n] outputs, n a multiple of 128): the
 // Newton-Schulz polynomial b A + c A^2 + a I formed in the epilogue of the A A product
 void gemm_batched_affine(const Tensor& a, const Tensor& b, const Tensor& cin, Tensor c, double ea, double eb, double ec,
-                         const c10::optional<Tensor>& status) {
+                         const c10::optional<Tensor>& status, bool symmetric) {
   check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(cin, "cin"); check_bf16(c, "c");
   TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3 && a.is_contiguous() && b.is_contiguous() &&
               c.is_contiguous() && cin.is_contiguous(), "gemm_batched_affine: contiguous 3-D operands expected");
@@ -173,6 +174,7 @@ void gemm_batched_affine(const Tensor& a, const Tensor& b, const Tensor& cin, Te
   g.epi_cin = cin.data_ptr();
   g.epi_a = static_cast<float>(ea); g.epi_b = static_cast<float>(eb); g.epi_c = static_cast<float>(ec);
   g.status = statusp(status);
+  g.symmetric = symmetric;
   check_rc(yv::launch_gemm(g, cur_stream()), "gemm_batched_affine");
 }
 
@@ -249,6 +251,20 @@ void swiglu_fwd(const Tensor& in, Tensor out) {
   TORCH_CHECK(in.size(-1) == 2 * F, "swiglu: input must be [rows, 2F]");
   const c10::cuda::CUDAGuard guard(in.device());
   check_rc(yv::launch_swiglu_fwd(in.data_ptr(), out.data_ptr(), out.numel() / F, F, cur_stream()), "swiglu_fwd");
+}
+
+void swiglu_bwd_rows(const Tensor& in, const Tensor& dact, const Tensor& row_w, Tensor din, Tensor actw, Tensor rowdot) {
+  check_bf16(in, "in"); check_bf16(dact, "dact"); check_bf16(din, "din"); check_bf16(actw, "actw");
+  TORCH_CHECK(in.is_contiguous() && dact.is_contiguous() && din.is_contiguous() && actw.is_contiguous() &&
+              row_w.is_contiguous() && rowdot.is_contiguous(), "swiglu_bwd_rows: contiguous expected");
+  TORCH_CHECK(row_w.scalar_type() == at::kFloat && rowdot.scalar_type() == at::kFloat, "swiglu_bwd_rows: fp32 row vectors");
+  const int F = static_cast<int>(dact.size(-1));
+  const int64_t rows = dact.numel() / F;
+  TORCH_CHECK(in.size(-1) == 2 * F && in.numel() == rows * 2 * F && din.numel() == in.numel() && actw.numel() == dact.numel() &&
+              row_w.numel() == rows && rowdot.numel() == rows, "swiglu_bwd_rows: shape mismatch");
+  const c10::cuda::CUDAGuard guard(in.device());
+  check_rc(yv::launch_swiglu_bwd_rows(in.data_ptr(), dact.data_ptr(), row_w.data_ptr<float>(), din.data_ptr(), actw.data_ptr(),
+                                      rowdot.data_ptr<float>(), rows, F, cur_stream()), "swiglu_bwd_rows");
 }
 
 void swiglu_bwd(const Tensor& in, const Tensor& dout, Tensor din) {

@@ -304,6 +304,48 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __
   }
 }
 
+// SwiGLU backward for expert rows when neither the activation nor the expert outputs were kept: one warp per row.
+//   in [rows, 2F] (gate | up pre-activations), dact [rows, F] = UNWEIGHTED gradient of the activation,
+//   row_w [rows] = combine weight of the row (0 on pad rows and dropped assignments)
+//   din  [rows, 2F] = row_w * dSwiGLU(in, dact)          (gradient of the up projection's output)
+//   actw [rows, F]  = row_w * SwiGLU(in)                 (B operand of the down projection's weight gradient)
+//   rowdot [rows]   = sum_f SwiGLU(in)[f] * dact[f]      (gradient of the row's combine weight)
+__global__ void swiglu_bwd_rows_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ dact,
+                                       const float* __restrict__ row_w, __nv_bfloat16* __restrict__ din,
+                                       __nv_bfloat16* __restrict__ actw, float* __restrict__ rowdot, int64_t rows, int F) {
+  const int lane = threadIdx.x & 31;
+  const int fv = F >> 3;
+  const int64_t warp0 = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t r = warp0; r < rows; r += nwarps) {
+    const float w = row_w[r];
+    float dot = 0.f;
+    for (int cv = lane; cv < fv; cv += 32) {
+      const int c = cv * 8;
+      float g[8], u[8], d[8], dg[8], du[8], a[8];
+      load8(in + r * 2 * F + c, g);
+      load8(in + r * 2 * F + F + c, u);
+      load8(dact + r * F + c, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sg = 1.f / (1.f + __expf(-g[j]));
+        const float silu = g[j] * sg;
+        const float act = silu * u[j];
+        dot += act * d[j];
+        a[j] = w * act;
+        du[j] = w * d[j] * silu;
+        dg[j] = w * d[j] * u[j] * (sg + silu * (1.f - sg));
+      }
+      store8(din + r * 2 * F + c, dg);
+      store8(din + r * 2 * F + F + c, du);
+      store8(actw + r * F + c, a);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) rowdot[r] = dot;
+  }
+}
+
 __global__ void film_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
                             const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ y, int64_t rows,
                             int cols, int64_t rows_per_group) {
@@ -439,6 +481,15 @@ int launch_swiglu_fwd(const void* in, void* out, int64_t rows, int F, cudaStream
   if (rows <= 0) return 0;
   if ((F & 7) != 0) return -1;
   swiglu_fwd_kernel<<<grid_for(rows * (F >> 3), 256), 256, 0, stream>>>(YV_BF(in), YV_BFM(out), rows, F);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_swiglu_bwd_rows(const void* in, const void* dact, const float* row_w, void* din, void* actw, float* rowdot,
+                           int64_t rows, int F, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((F & 7) != 0) return -1;
+  swiglu_bwd_rows_kernel<<<grid_for(rows * 32, 256), 256, 0, stream>>>(YV_BF(in), YV_BF(dact), row_w, YV_BFM(din),
+                                                                      YV_BFM(actw), rowdot, rows, F);
   return static_cast<int>(cudaGetLastError());
 }
 

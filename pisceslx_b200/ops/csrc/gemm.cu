@@ -166,6 +166,16 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
                    out_bytes, a.c, static_cast<uint64_t>(a.N), c_outer, ldc, 128 / out_bytes, kBM);
   if (r != 0) return -40 + r;
 
+  p.symmetric = 0; p.sym_tiles = 0; p.sym_c = nullptr;
+  if (a.symmetric) {
+    if (a.mode != kBatched || a.M != a.N || a.out_fp32 || a.accumulate || a.comm != 0 || a.fp8 ||
+        (a.ldc != 0 && a.ldc != a.N))
+      return -81;
+    p.symmetric = 1;
+    p.sym_c = reinterpret_cast<__nv_bfloat16*>(a.c);
+    const int tm = (a.M + kBM - 1) / kBM, tn = (a.N + bn - 1) / bn;
+    for (int j = 0; j < tn; ++j) p.sym_tiles += (tm < (j + 1) * (bn / kBM)) ? tm : (j + 1) * (bn / kBM);
+  }
   p.comm_world = 1; p.comm_rank = 0; p.comm_blocks_per_rank = 0;
   p.comm_local = nullptr; p.comm_flags = nullptr; p.comm_flag_target = 0; p.comm_row_bytes = 0;
   for (int i = 0; i < 8; ++i) p.comm_peer[i] = nullptr;
@@ -190,6 +200,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   const int64_t tiles_m = (p.M + kBM - 1) / kBM;
   const int64_t tiles_n = (a.N + bn - 1) / bn;
   int64_t tiles = tiles_m * tiles_n * ((p.mode == kGroupedK || p.mode == kBatched) ? a.num_groups : 1);
+  if (p.symmetric) tiles = static_cast<int64_t>(p.sym_tiles) * a.num_groups;
   const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
 

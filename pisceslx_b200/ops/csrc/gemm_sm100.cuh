@@ -59,6 +59,11 @@ struct GemmParams {
   // epi_cin laid out like C; the identity is per group in the batched mode ----
   const __nv_bfloat16* epi_cin;
   float epi_a, epi_b, epi_c;
+  // ---- symmetric output (batched mode, M == N, bf16): tiles entirely below the diagonal are skipped and filled by
+  // the mirrored stores of the computed tiles; sym_tiles = computed tiles per group, sym_c = C as a plain pointer ----
+  int symmetric;
+  int sym_tiles;
+  __nv_bfloat16* sym_c;
 };
 
 constexpr int kBM = 128;
@@ -92,7 +97,20 @@ struct TileCoord {
 template <int BN, bool A_MN, bool B_MN, int COMM = 0, bool FP8 = false>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int tiles_m, int tiles_n, TileCoord& t) {
   int m_blk, n_blk, group = 0;
-  if (p.mode == kGroupedK || p.mode == kBatched) {
+  if (p.mode == kBatched && p.symmetric) {
+    // column tile j keeps the row tiles that start above the column tile's last column: i * 128 < (j + 1) * BN
+    group = idx / p.sym_tiles;
+    if (group >= p.num_groups) return false;
+    int r = idx - group * p.sym_tiles;
+    int j = 0;
+    for (;; ++j) {
+      const int kept = min(tiles_m, (j + 1) * (BN / kBM));
+      if (r < kept) break;
+      r -= kept;
+    }
+    n_blk = j;
+    m_blk = r;
+  } else if (p.mode == kGroupedK || p.mode == kBatched) {
     const int per_group = tiles_m * tiles_n;
     group = idx / per_group;
     if (group >= p.num_groups) return false;
@@ -444,6 +462,30 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) packed[i] = 0u;
+          }
+        }
+        if (sizeof(OutT) == 2 && COMM == 0 && !FP8 && p.symmetric) {
+          // mirrored elements C[col][row] = C[row][col] for the positions whose own tile was skipped.  For a fixed
+          // column the 32 lanes of a warp hold 32 consecutive rows: every store instruction writes 64 contiguous bytes.
+          const int grp_rows = p.c_group_stride;
+          const int lrow = t.c_y % grp_rows + row;                       // row inside the matrix
+          __nv_bfloat16* cbase = p.sym_c + static_cast<int64_t>(t.c_y - t.c_y % grp_rows) * p.N;
+          const int row_tile_end = (lrow / BN + 1) * BN;                 // end of the column tile that holds `lrow` as a column
+          const int col0 = t.c_x + c * kColsPerChunk;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // packed[i] (i < 16) holds columns 2i, 2i+1 of the chunk; packed[16 + i] holds columns 32 + 2i, 33 + 2i
+            const int cc = col0 + (i < 16 ? 2 * i : 32 + 2 * (i - 16));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int gcol = cc + h;
+              // the mirror position (gcol, lrow) lies in row tile gcol / 128 and column tile lrow / BN: skipped iff
+              // that column tile ends at or before the row tile starts
+              if (gcol < p.N && row_tile_end <= (gcol / kBM) * kBM && lrow < p.N) {
+                const uint16_t bits = static_cast<uint16_t>(h == 0 ? (packed[i] & 0xffffu) : (packed[i] >> 16));
+                reinterpret_cast<uint16_t*>(cbase)[static_cast<int64_t>(gcol) * p.N + lrow] = bits;
+              }
+            }
           }
         }
         // 128-byte row, eight 16-byte pieces, XOR-swizzled with the row index (TMA SWIZZLE_128B)

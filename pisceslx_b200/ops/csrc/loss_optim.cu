@@ -228,21 +228,22 @@ __global__ void momentum_q8_kernel(int8_t* __restrict__ q, float* __restrict__ s
     for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if (live) {
       const float ns = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
-      const float inv = 1.f / ns;
-      uint2 out;
-      int8_t* ob = reinterpret_cast<int8_t*>(&out);
-      // two hashes per thread: each 32-bit value supplies four 8-bit uniform variates (1/256 resolution bounds the
-      // rounding bias at 1/512 of a quantisation step)
+      const float inv256 = 256.f / ns;
+      // Stochastic rounding in fixed point: t = round(v / ns * 256) carries 8 fractional bits, a uniform byte is
+      // added and the arithmetic shift by 8 is the floor.  Two hashes per thread supply the eight bytes (1/256
+      // resolution bounds the rounding bias at 1/512 of a quantisation step).  |v / ns| <= 127, so the result is
+      // within [-127, 127] without clamping.
       const uint32_t key = static_cast<uint32_t>(e0 >> 3) * 0x9e3779b9u ^ static_cast<uint32_t>(e0 >> 35) ^ seed;
       const uint32_t r0 = hash_u32(key), r1 = hash_u32(key ^ 0x68bc21ebu);
+      uint32_t lo = 0u, hi = 0u;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t byte = ((j < 4 ? r0 : r1) >> (8 * (j & 3))) & 0xffu;
-        const float u = (static_cast<float>(byte) + 0.5f) * (1.f / 256.f);          // (0, 1), mean 1/2
-        float t = floorf(v[j] * inv + u);
-        t = fminf(fmaxf(t, -127.f), 127.f);
-        ob[j] = static_cast<int8_t>(t);
+      for (int j = 0; j < 4; ++j) {
+        const int a = (__float2int_rn(v[j] * inv256) + static_cast<int>((r0 >> (8 * j)) & 0xffu)) >> 8;
+        const int b = (__float2int_rn(v[j + 4] * inv256) + static_cast<int>((r1 >> (8 * j)) & 0xffu)) >> 8;
+        lo |= (static_cast<uint32_t>(a) & 0xffu) << (8 * j);
+        hi |= (static_cast<uint32_t>(b) & 0xffu) << (8 * j);
       }
+      const uint2 out = make_uint2(lo, hi);
       *reinterpret_cast<uint2*>(q + e0) = out;
       if (lane16 == 0) scale[b] = ns;
     }

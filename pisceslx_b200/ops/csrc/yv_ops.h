@@ -47,6 +47,10 @@ struct GemmArgs {
   // affine epilogue: C = epi_c * (A B) + epi_b * epi_cin + epi_a * I (epi_cin bf16, laid out like C; N % 64 == 0)
   const void* epi_cin = nullptr;
   float epi_a = 0.f, epi_b = 0.f, epi_c = 1.f;
+  // Symmetric result (batched mode, M == N, bf16 C, the caller guarantees C = C^T, e.g. X X^T or a polynomial of a
+  // symmetric matrix): only the tiles that touch the diagonal or lie above it are computed; their epilogue also writes
+  // the mirrored elements of the tiles that were skipped.
+  bool symmetric = false;
 };
 // Returns 0 on success, a negative code when an argument is rejected, a positive cudaError_t otherwise.
 int launch_gemm(const GemmArgs& args, cudaStream_t stream);
@@ -76,6 +80,9 @@ int launch_rope3d(void* q, void* k, const int* pos_thw, int64_t tokens, int hq, 
 // SwiGLU: out[r, j] = silu(in[r, j]) * in[r, F + j]   (in is [rows, 2F])
 int launch_swiglu_fwd(const void* in, void* out, int64_t rows, int F, cudaStream_t stream);
 int launch_swiglu_bwd(const void* in, const void* dout, void* din, int64_t rows, int F, cudaStream_t stream);
+// expert rows: din = row_w * dSwiGLU(in, dact), actw = row_w * SwiGLU(in), rowdot = <SwiGLU(in), dact> per row
+int launch_swiglu_bwd_rows(const void* in, const void* dact, const float* row_w, void* din, void* actw, float* rowdot,
+                           int64_t rows, int F, cudaStream_t stream);
 // FiLM: y = x * (1 + scale[g]) + shift[g], g = row / rows_per_group
 int launch_film(const void* x, const void* scale, const void* shift, void* y, int64_t rows, int cols,
                 int64_t rows_per_group, cudaStream_t stream);

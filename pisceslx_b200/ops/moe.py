@@ -115,6 +115,16 @@ def permute_tokens(x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor, num
 
 
 class _MoEExpertsFn(torch.autograd.Function):
+    """Keeps only the token rows ``x`` and the up-projection output ``y1`` for backward (per micro-batch of 8192
+    tokens x top-6 at hidden 4096 / FFN 1408: 0.07 + 0.28 GB instead of 1.3 GB with the permuted rows, the activation
+    and the expert outputs).  Backward rebuilds what it needs:
+      * the permuted rows from ``x`` and the saved row map (one gather);
+      * the activation from ``y1`` inside the SwiGLU-backward kernel;
+      * the combine-weight gradient without the expert outputs: with ``dA' = dout[token] @ W2[e]`` (the UNWEIGHTED
+        activation gradient), ``d weight = <SwiGLU(y1), dA'>`` per row, and the weight is applied afterwards
+        (``dy1 = w * dSwiGLU(y1, dA')``, ``dW2 = dout^T (w * act)``).  That is also exact for assignments whose weight
+        is zero (dropped by the capacity rule)."""
+
     @staticmethod
     def forward(ctx, x, w13, w2, weights, idx, counts, deterministic, training=True):
         K = _k()
@@ -126,14 +136,16 @@ class _MoEExpertsFn(torch.autograd.Function):
         xp, plan = permute_tokens(x, idx, counts, E, deterministic, zero_pad=training)
         y1 = torch.empty(plan.max_rows, twoF, dtype=_BF16, device=x.device)
         K.gemm_grouped_m(xp, w13, y1, plan.tile_expert, plan.num_m_tiles, False, 0, st)
+        del xp
         act = torch.empty(plan.max_rows, F, dtype=_BF16, device=x.device)
         K.swiglu_fwd(y1, act)
         y2 = torch.empty(plan.max_rows, H, dtype=_BF16, device=x.device)
         K.gemm_grouped_m(act, w2, y2, plan.tile_expert, plan.num_m_tiles, False, 0, st)
+        del act
         out = torch.empty(T, H, dtype=_BF16, device=x.device)
         wts = weights.float().contiguous()
         K.moe_combine(y2, plan.row_map, wts, None, out)
-        ctx.save_for_backward(xp, y1, act, y2, w13, w2, wts, plan.row_map, plan.seg_offsets, plan.tile_expert,
+        ctx.save_for_backward(x, y1, w13, w2, wts, idx, plan.row_map, plan.seg_offsets, plan.tile_expert,
                               plan.num_m_tiles, plan.counts)
         ctx.dims = (T, H, E, F, plan.max_rows, idx.shape[1])
         ctx.w_dtype = weights.dtype
@@ -142,31 +154,39 @@ class _MoEExpertsFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         K = _k()
-        xp, y1, act, y2, w13, w2, wts, row_map, seg, tile_expert, num_tiles, counts = ctx.saved_tensors
+        x, y1, w13, w2, wts, idx, row_map, seg, tile_expert, num_tiles, counts = ctx.saved_tensors
         T, H, E, F, max_rows, k = ctx.dims
         st = status_word(dout.device)
         dev = dout.device
         dout = dout.contiguous()
-        # combine backward (dy2 is written over y2's rows in a fresh buffer; pad rows zeroed)
-        dy2 = torch.empty_like(y2)
-        dwts = torch.empty(T, k, dtype=torch.float32, device=dev)
-        K.moe_combine_bwd(dout, y2, row_map, wts, dy2, dwts)
+        # combine weight of every expert row (0 on pad rows)
+        row_w = torch.zeros(max_rows, dtype=torch.float32, device=dev)
+        row_w.index_put_((row_map.flatten().long(),), wts.flatten())
+        # unweighted output gradient in expert-row order
+        dy2 = torch.empty(max_rows, H, dtype=_BF16, device=dev)
+        K.moe_permute(dout, idx, None, row_map, dy2)
         K.moe_zero_pad(dy2, seg, counts)
-        # down projection
+        # down projection (unweighted activation gradient), then the activation with the weights applied
         dact = torch.empty(max_rows, F, dtype=_BF16, device=dev)
         K.gemm_grouped_m(dy2, w2, dact, tile_expert, num_tiles, True, 0, st)          # dy2 [rows,H] x w2[e] [H,F]
-        dw2 = torch.empty_like(w2)
-        K.gemm_grouped_k(dy2, act, dw2, seg, False, 0, st)                            # [H, rows_e] x [rows_e, F]
-        del dy2
-        # activation
         dy1 = torch.empty_like(y1)
-        K.swiglu_bwd(y1, dact, dy1)
+        act_w = torch.empty(max_rows, F, dtype=_BF16, device=dev)
+        rowdot = torch.empty(max_rows, dtype=torch.float32, device=dev)
+        K.swiglu_bwd_rows(y1, dact, row_w, dy1, act_w, rowdot)
         del dact
+        dw2 = torch.empty_like(w2)
+        K.gemm_grouped_k(dy2, act_w, dw2, seg, False, 0, st)                          # [H, rows_e] x [rows_e, F]
+        del dy2, act_w
+        dwts = rowdot[row_map.flatten().long()].view(T, k)
         # up projection
         dxp = torch.empty(max_rows, H, dtype=_BF16, device=dev)
         K.gemm_grouped_m(dy1, w13, dxp, tile_expert, num_tiles, True, 0, st)          # dy1 [rows,2F] x w13[e] [2F,H]
+        xp = torch.empty(max_rows, H, dtype=_BF16, device=dev)
+        K.moe_permute(x, idx, None, row_map, xp)
+        K.moe_zero_pad(xp, seg, counts)
         dw13 = torch.empty_like(w13)
         K.gemm_grouped_k(dy1, xp, dw13, seg, False, 0, st)
+        del xp, dy1
         dx = torch.empty(T, H, dtype=_BF16, device=dev)
         K.moe_unpermute_sum(dxp, row_map, dx, k)
         return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None, None

@@ -104,24 +104,26 @@ def newton_schulz_batched(x: torch.Tensor, coeffs: Sequence[Tuple[float, float, 
     A2 = torch.empty_like(A)
     Y = torch.empty_like(X)
     # X <- (aI + bA + cA^2) X with A = X X^T: the polynomial is formed on the small Gram matrix, so every
-    # iteration is three GEMMs and one pass over [G, n, n]; the big operand is only ever read and written by GEMMs
+    # iteration is three GEMMs and one pass over [G, n, n]; the big operand is only ever read and written by GEMMs.
+    # A and the polynomial are symmetric: those two products compute the tiles on or above the diagonal only and
+    # mirror them (about 0.6 of the tiles at n = 1408 with 128 x 256 tiles)
     fused_poly = short % 128 == 0 and short % 64 == 0
 
     def poly(a: float, b: float, c: float) -> None:
         """A2 <- aI + bA + cA^2; in the epilogue of the A A product when the shape allows, else a separate pass."""
         if fused_poly:
-            K.gemm_batched_affine(A, A, A, A2, a, b, c, st)
+            K.gemm_batched_affine(A, A, A, A2, a, b, c, st, True)        # symmetric: upper tiles + mirrored stores
         else:
-            K.gemm_batched(A, A, A2, False, False, False, 0, st)         # A2 = A A^T = A^2 (A symmetric)
+            K.gemm_batched(A, A, A2, False, False, False, 0, st, True)   # A2 = A A^T = A^2 (A symmetric)
             K.ns_poly(A, A2, A2, a, b, c)
 
     for a, b, c in coeffs:
         if n <= m:
-            K.gemm_batched(X, X, A, False, False, False, 0, st)          # A = X X^T        [n,n]
+            K.gemm_batched(X, X, A, False, False, False, 0, st, True)    # A = X X^T        [n,n], symmetric
             poly(a, b, c)                                                # B = aI + bA + cA^2
             K.gemm_batched(A2, X, Y, False, True, False, 0, st)          # Y = B X          [n,m]
         else:
-            K.gemm_batched(X, X, A, True, True, False, 0, st)            # A = X^T X        [m,m]
+            K.gemm_batched(X, X, A, True, True, False, 0, st, True)      # A = X^T X        [m,m], symmetric
             poly(a, b, c)
             K.gemm_batched(X, A2, Y, False, False, False, 0, st)         # Y = X B^T = X B  [n,m]
         X, Y = Y, X

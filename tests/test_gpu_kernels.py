@@ -119,6 +119,35 @@ def test_gemm_batched_and_newton_schulz(Y, status, shape):
     assert s.max() < 1.35 and s.min() > 0.3
 
 
+@pytest.mark.parametrize("n,k,bn", [(1408, 512, 256), (1408, 512, 128), (640, 192, 256), (128, 64, 128), (1024, 256, 0)])
+def test_gemm_batched_symmetric_matches_full_product(Y, status, n, k, bn):
+    """Symmetric mode computes the tiles on or above the diagonal and mirrors them: the result must equal the full
+    product bit for bit wherever both wrote, be exactly symmetric in the mirrored region, and leave nothing unwritten."""
+    torch.manual_seed(33)
+    G = 3
+    x = torch.randn(G, n, k, device=DEV, dtype=torch.bfloat16)
+    full = torch.empty(G, n, n, device=DEV, dtype=torch.bfloat16)
+    Y.gemm_batched(x, x, full, False, False, False, bn, status, False)
+    sym = torch.full((G, n, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+    Y.gemm_batched(x, x, sym, False, False, False, bn, status, True)
+    assert not torch.isnan(sym.float()).any()
+    assert torch.equal(sym, full)                           # x x^T is bitwise symmetric: products commute, same K order
+    # the polynomial epilogue: aI + bA + cA^2 of a symmetric A
+    a2_full, a2_sym = torch.empty_like(full), torch.full_like(full, float("nan"))
+    A = (full.float() / n).bfloat16()
+    Y.gemm_batched_affine(A, A, A, a2_full, 3.4445, -4.775, 2.0315, status, False)
+    Y.gemm_batched_affine(A, A, A, a2_sym, 3.4445, -4.775, 2.0315, status, True)
+    assert not torch.isnan(a2_sym.float()).any()
+    assert rel(a2_sym, a2_full) < 1e-3                      # A A differs from its transpose only in accumulation order
+    assert torch.equal(a2_sym.triu(), a2_full.triu())
+    # transposed operands (the n > m branch of Newton-Schulz: A = X^T X)
+    xt = torch.randn(G, k, n, device=DEV, dtype=torch.bfloat16)
+    f2, s2 = torch.empty_like(full), torch.full_like(full, float("nan"))
+    Y.gemm_batched(xt, xt, f2, True, True, False, bn, status, False)
+    Y.gemm_batched(xt, xt, s2, True, True, False, bn, status, True)
+    assert torch.equal(s2, f2)
+
+
 # ---------------------------------------------------------------------------------------------- elementwise
 @pytest.mark.parametrize("rows,cols", [(1, 256), (37, 1024), (1000, 4096), (65, 8192)])
 def test_rmsnorm_fwd_bwd(Y, rows, cols):
@@ -239,7 +268,9 @@ def test_moe_experts_matches_dense_loop(deterministic):
     logits = torch.randn(T, E, device=DEV)
     logits[:, 3] = -50.0                                    # an expert that receives no token
     wts, idx, counts, _ = moe_ops.gate_topk(logits, None, k)
-    wts = wts.detach().requires_grad_(True)
+    wts = wts.detach().clone()
+    wts[::7, 0] = 0.0                                       # assignments dropped by a capacity rule keep their row
+    wts = wts.requires_grad_(True)
     out = moe_ops.moe_experts(x, w13, w2, wts, idx, counts, deterministic)
     do = torch.randn_like(out)
     out.backward(do)
