@@ -48,6 +48,7 @@ class YvTrainerConfig:
     abort_on_non_finite: bool = True
     state_dtype: Optional[str] = None       # "bf16" | "fp32" | "int8" (Muon momentum block-quantised) | None (= parameter dtype)
     recompute_policy: str = "config"        # "config": as the model config says; "auto": sized from measured memory
+    sharding: str = "zero1"                 # "zero1": optimizer state by owner; "full_shard": ZeRO-3 units per block
     optimizer_kwargs: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -56,6 +57,22 @@ class YvTrainer:
                  optimizer: Optional[torch.optim.Optimizer] = None):
         self.model, self.cfg, self.parallel = model, cfg, parallel
         self.device = next(model.parameters()).device
+        self.fsdp_units = []
+        if cfg.sharding == "full_shard" and parallel is not None and getattr(parallel, "dp_size", 1) > 1:
+            # parameters, gradients and optimizer state of every block sharded over the data-parallel group
+            # (reference: FSDP FULL_SHARD, tools/train/core.py:950-985); element-wise optimizer on the shards
+            if parallel.tp_size > 1 or parallel.ep_size > 1 or parallel.pp_size > 1:
+                raise ValueError("sharding='full_shard' is a pure data-parallel layout (tp = ep = pp = 1)")
+            if cfg.optimizer == "muon":
+                raise ValueError("sharding='full_shard' shards matrices element-wise: use optimizer='adamw' "
+                                 "(Muon keeps whole matrices per owner under sharding='zero1')")
+            from ..parallel import fsdp
+            if hasattr(model, "cfg"):
+                model.cfg.use_gradient_checkpointing = False      # the units recompute themselves
+            for blk in getattr(getattr(model, "model", model), "layers", []):
+                if hasattr(blk, "use_recompute"):
+                    blk.use_recompute = False
+            self.fsdp_units = fsdp.fully_shard(model, parallel.dp_group)
         sd = {"bf16": torch.bfloat16, "fp32": torch.float32, "int8": torch.int8, None: None}[cfg.state_dtype]
         self.optimizer = optimizer or build_optimizer(model, cfg.optimizer, lr=cfg.lr, weight_decay=cfg.weight_decay,
                                                       state_dtype=sd, **cfg.optimizer_kwargs)

@@ -110,7 +110,7 @@ class YvGradientSynchronizer:
         #   everything else           replicated over dp         (tp-sharded matrices, embeddings, LM head)
         dense, expert, seqpar = [], [], []
         for n, p in model.named_parameters():
-            if not p.requires_grad:
+            if not p.requires_grad or getattr(p, "_yv_sharded", False):     # FULL_SHARD slices reduce themselves
                 continue
             if _is_expert_param(n):
                 expert.append((n, p))

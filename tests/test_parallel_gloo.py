@@ -36,7 +36,8 @@ WORKER = textwrap.dedent("""
     load_full_into(model, full)
     clip, batch = float(os.environ.get("YV_TEST_CLIP", "0")), int(os.environ.get("YV_TEST_BATCH", "4"))
     tr = YvTrainer(model, YvTrainerConfig(micro_batch_size=2, optimizer="adamw", lr=1e-3, max_steps=100,
-                                          clip_grad_norm=clip), parallel=par if par.world_size > 1 else None)
+                                          clip_grad_norm=clip, sharding=os.environ.get("YV_TEST_SHARDING", "zero1")),
+                   parallel=par if par.world_size > 1 else None)
     g = torch.Generator().manual_seed(0)
     data = torch.randint(0, 1024, (steps, batch, 32), generator=g)
     losses, norms = [], []
@@ -206,3 +207,19 @@ def test_data_parallel_resume_is_bit_equal(tmp_path):
         assert res["path"].endswith("_sharded") and os.path.isfile(os.path.join(res["path"], f"shard_rank{r}.pt"))
         assert res["warnings"] == [] and res["step_b"] == 3
         assert res["loss_a"] == res["loss_b"] and res["sum_a"] == res["sum_b"], res
+
+
+@pytest.mark.timeout(900)
+def test_trainer_full_shard_matches_single_process(tmp_path, init_weights):
+    """``sharding='full_shard'`` through the trainer (two data-parallel ranks, clipping on, two micro-batches per
+    rank): same losses and gradient norms as one process."""
+    steps = 3
+    env = {"YV_TEST_CLIP": "1.0", "YV_TEST_BATCH": "8"}
+    single = _run(tmp_path, 1, 1, 1, steps, init_weights, "fs_single", env)
+    n_single = json.load(open(str(tmp_path / "loss_fs_single.json") + ".norms"))
+    multi = _run(tmp_path, 2, 1, 1, steps, init_weights, "fs_multi", dict(env, YV_TEST_SHARDING="full_shard"))
+    n_multi = json.load(open(str(tmp_path / "loss_fs_multi.json") + ".norms"))
+    for a, b in zip(n_single, n_multi):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (n_single, n_multi)
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
