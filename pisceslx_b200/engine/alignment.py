@@ -57,9 +57,11 @@ def orpo_loss(nll_chosen: torch.Tensor, avg_lp_chosen: torch.Tensor, avg_lp_reje
 
 
 def kto_loss(pi_lp: torch.Tensor, ref_lp: torch.Tensor, desirable: torch.Tensor, beta: float = 0.1,
-             lambda_d: float = 1.0, lambda_u: float = 1.0) -> torch.Tensor:
+             lambda_d: float = 1.0, lambda_u: float = 1.0, kl_ref: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``kl_ref``: the reference point (an estimate of KL(policy || reference), detached); by default the batch mean of
+    the implicit reward, clamped at zero."""
     r = pi_lp - ref_lp
-    z = r.detach().mean().clamp_min(0)
+    z = r.detach().mean().clamp_min(0) if kl_ref is None else kl_ref.detach()
     pos = lambda_d * (1 - torch.sigmoid(beta * (r - z)))
     neg = lambda_u * (1 - torch.sigmoid(beta * (z - r)))
     return torch.where(desirable.bool(), pos, neg).mean()
