@@ -22,7 +22,7 @@ import torch
 
 
 class YvRecomputePlanner:
-    def __init__(self, model: torch.nn.Module, device: torch.device, budget: float = 0.90, min_headroom_gb: float = 6.0,
+    def __init__(self, model: torch.nn.Module, device: torch.device, budget: float = 0.95, min_headroom_gb: float = 6.0,
                  group: Any = None):
         self.layers: List[Any] = list(model.model.layers)
         self.device, self.budget, self.min_headroom = device, budget, min_headroom_gb * 2 ** 30
