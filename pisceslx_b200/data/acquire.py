@@ -128,14 +128,14 @@ class PiscesLxLocalMirrorSource(PiscesLxDataSource):
 
     def _candidates(self, item: PiscesLxToolsDatasetItem) -> List[Path]:
         out: List[Path] = []
-        for stem in (item.name, item.save_name):
+        for stem in dict.fromkeys((item.name, item.save_name)):
             base = self.root / stem
             if base.is_dir():
                 out += sorted(p for p in base.rglob("*") if p.suffix in (".jsonl", ".json", ".txt", ".parquet"))
             for ext in (".jsonl", ".json", ".txt", ".parquet"):
                 if (self.root / (stem + ext)).exists():
                     out.append(self.root / (stem + ext))
-        return out
+        return list(dict.fromkeys(out))
 
     def fetch(self, item: PiscesLxToolsDatasetItem, dest: Path) -> int:
         files = self._candidates(item)

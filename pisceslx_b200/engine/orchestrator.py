@@ -222,3 +222,79 @@ class PiscesLxInferOrchestrator:
         print(json.dumps({"text": text, "stats": stats, "seconds": dt,
                           "tokens_per_second": stats.get("generated_tokens", 0) / max(dt, 1e-9)}))
         return 0
+
+
+class PiscesLxPreferenceOrchestrator:
+    """``manage.py train --rlhf`` / ``--train_mode preference`` (reference orchestrator ``_run_preference``): DPO over
+    ``{"prompt", "chosen", "rejected"}`` records of ``--rlhf_dataset`` (jsonl), with a frozen reference copy of the
+    policy.  Without a dataset a small synthetic preference set is used, so that the path can be exercised offline."""
+
+    def __init__(self, args: Any):
+        self.args = args
+
+    def run(self, args: Any) -> int:
+        from ..models import build_model
+        from ..models.tokenizer import YvTokenizer
+        from .alignment import PiscesLxDPOTrainingOperator
+        from .rl import PiscesLxPreferenceDataProcessor
+        model_cfg = resolve_model_config(args.model_size, args.model_config)
+        model_cfg.use_gradient_checkpointing = False
+        device = torch.device(args.device or ("cuda" if torch.cuda.is_available() else "cpu"))
+        model = build_model(model_cfg, device, torch.bfloat16 if device.type == "cuda" else torch.float32, seed=args.seed)
+        if args.ckpt:
+            from .checkpoint import extract_state_dict
+            model.load_reference_state_dict(extract_state_dict(torch.load(args.ckpt, map_location="cpu", weights_only=False)),
+                                            strict=False)
+        tok = YvTokenizer.instance()
+        if args.rlhf_dataset:
+            records = [json.loads(l) for l in open(args.rlhf_dataset, encoding="utf-8") if l.strip()]
+        else:
+            records = [{"prompt": f"question {i}: ", "chosen": "a careful and correct answer", "rejected": "no"} for i in range(16)]
+        if args.rlhf_max_samples:
+            records = records[: args.rlhf_max_samples]
+        proc = PiscesLxPreferenceDataProcessor(tok, max_length=args.rlhf_max_length)
+        opt = torch.optim.AdamW(model.parameters(), lr=args.rlhf_lr, weight_decay=0.0)
+        op = PiscesLxDPOTrainingOperator(model, opt)
+        if args.dry_run:
+            print(json.dumps({"mode": "preference", "records": len(records), "batch": args.rlhf_batch_size, "epochs": args.rlhf_epochs}))
+            return 0
+        step, last = 0, {}
+        for _ in range(args.rlhf_epochs):
+            for s in range(0, len(records), args.rlhf_batch_size):
+                b = proc.pairs(records[s:s + args.rlhf_batch_size])
+                b = {k: v.to(device).clamp_(max=model_cfg.vocab_size - 1) if "labels" not in k else v.to(device) for k, v in b.items()}
+                for k in ("chosen_labels", "rejected_labels"):
+                    b[k] = torch.where(b[k] >= model_cfg.vocab_size, torch.full_like(b[k], -100), b[k])
+                loss, last = op.step(b["chosen"], b["rejected"], b["chosen_labels"], b["rejected_labels"])
+                step += 1
+                if args.max_steps and step >= args.max_steps:
+                    break
+            if args.max_steps and step >= args.max_steps:
+                break
+        print(json.dumps({"steps": step, "loss": loss, **last}))
+        if args.output_dir:
+            from .checkpoint import _atomic_save
+            _atomic_save({"model_state_dict": {k: v.cpu() for k, v in model.to_reference_state_dict().items()},
+                          "global_step": step}, os.path.join(args.output_dir, "preference_final.pt"))
+        return 0
+
+
+def run_quant_export(args: Any) -> int:
+    """``manage.py train --train_mode quant_export --ckpt C --quant METHOD --quant_bits N --save OUT``: post-training
+    quantisation of a checkpoint through the PTQ engine and a reference-layout file of the de-quantised weights plus
+    the quantisation report."""
+    from ..quant.pipeline import PiscesLxQuantizationConfig, PiscesLxQuantizationEngine, PiscesLxQuantizationMethod
+    model = load_model_for_inference(args.model_size, args.ckpt, args.device or "cpu", args.model_config)
+    method = PiscesLxQuantizationMethod((args.quant or "rtn").lower())
+    qcfg = PiscesLxQuantizationConfig(method=method, bits=int(args.quant_bits))
+    if args.dry_run:
+        print(json.dumps({"mode": "quant_export", "method": method.value, "bits": qcfg.bits}))
+        return 0
+    result = PiscesLxQuantizationEngine(qcfg).quantize(model)
+    out = args.save or os.path.join(args.output_dir or ".", "quantized.pt")
+    from .checkpoint import _atomic_save
+    _atomic_save({"model_state_dict": {k: v.cpu() for k, v in model.to_reference_state_dict().items()},
+                  "quantization": {"method": method.value, "bits": qcfg.bits}}, out)
+    print(json.dumps({"saved": out, "method": method.value, "bits": qcfg.bits,
+                      "layers": result.layers, "mean_bits": result.mean_bits, "seconds": result.seconds}, default=str))
+    return 0

@@ -52,10 +52,14 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
   constexpr int kStages = S::kStages;
   constexpr int kDBoxes = D / 64;
   constexpr uint32_t kBoxBytes = 128 * 128;
-  constexpr uint32_t kIdescNT = make_idesc_bf16(128, 128, false, false);   // S, dP
+  // A 128-key block is processed as two 64-key halves: TMEM stage s in {0,1} holds S at [128 s, 128 s + 64) and dP at
+  // [128 s + 64, 128 s + 128) (dS as bf16 over the first 32 columns of S), so the scores of half h + 1 are computed
+  // while the softmax threads work on half h; dQ accumulates at [256, 256 + D).
+  constexpr uint32_t kIdescNT = make_idesc_bf16(128, 64, false, false);    // S, dP: 128 queries x 64 keys
   constexpr uint32_t kIdescDQ = make_idesc_bf16(128, D, false, true);      // dS (TMEM) x K (MN-major)
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256;
+  constexpr uint32_t kColDQ = 256;
+  constexpr uint32_t kHalfRows = 64 * 128;            // byte offset of key rows 64.. inside a 64-column box
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -69,10 +73,10 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
   uint64_t* v_full = bars + 3;          // [2]
   uint64_t* k_empty = bars + 5;         // [2]  released after dQ MMA (last reader of K_j)
   uint64_t* v_empty = bars + 7;         // [2]  released after dP MMA
-  uint64_t* sdp_full = bars + 9;        // [1]  S and dP ready
-  uint64_t* ds_full = bars + 10;        // [1]  128 arrivals: dS written
-  uint64_t* dq_done = bars + 11;        // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* sdp_full = bars + 9;        // [2]  S and dP of a TMEM stage ready
+  uint64_t* ds_full = bars + 11;        // [2]  128 arrivals: dS written
+  uint64_t* dq_done = bars + 13;        // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y;
@@ -97,8 +101,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
       mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1);
       mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
     }
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 128);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 128); }
     mbar_init(dq_done, 1);
     fence_barrier_init();
   }
@@ -138,40 +141,56 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
     if (elect_one() && n_kv > 0) {
       bool ok = mbar_wait(qdo_full, 0, p.status);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
-      for (int j = 0; j < n_kv && ok; ++j) {
+      const int n_half = 2 * n_kv;
+      // S = Q K^T and dP = dO V^T of key half `hf` (block hf / 2, key rows 64 (hf % 2) ..) into TMEM stage hf % 2
+      auto issue_sdp = [&](int hf) -> bool {
+        const int j = hf >> 1, half = hf & 1;
         const int s = j % kStages;
-        const uint32_t ph = (j / kStages) & 1u;
-        ok = mbar_wait(&k_full[s], ph, p.status);
-        if (!ok) break;
-        ok = mbar_wait(&v_full[s], ph, p.status);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t aK = smem_u32(sK + s * S::kTile), aV = smem_u32(sV + s * S::kTile);
-        // S = Q K^T and dP = dO V^T (these overwrite dS_{j-1}: in-order after the dQ MMA issued before)
+        if (half == 0) {
+          const uint32_t ph = (j / kStages) & 1u;
+          if (!mbar_wait(&k_full[s], ph, p.status)) return false;
+          if (!mbar_wait(&v_full[s], ph, p.status)) return false;
+          tc_fence_after_sync();
+        }
+        const uint32_t aK = smem_u32(sK + s * S::kTile) + half * kHalfRows;
+        const uint32_t aV = smem_u32(sV + s * S::kTile) + half * kHalfRows;
+        const uint32_t tS = tmem_base + static_cast<uint32_t>((hf & 1) * 128);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-          tc_mma_f16_ss(tmem_base + kColS, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024),
-                        kIdescNT, kk != 0 ? 1u : 0u);
+          tc_mma_f16_ss(tS, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), kIdescNT,
+                        kk != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-          tc_mma_f16_ss(tmem_base + kColDP, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024),
-                        kIdescNT, kk != 0 ? 1u : 0u);
+          tc_mma_f16_ss(tS + 64, make_smem_desc(aDO + off, 16, 1024), make_smem_desc(aV + off, 16, 1024), kIdescNT,
+                        kk != 0 ? 1u : 0u);
         }
-        tc_commit(&v_empty[s]);
-        tc_commit(sdp_full);
-        ok = mbar_wait(ds_full, j & 1u, p.status);
+        if (half == 1) tc_commit(&v_empty[s]);          // V_j is read by the dP products only
+        tc_commit(&sdp_full[hf & 1]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int hf = 0; hf < n_half && ok; ++hf) {
+        if (hf + 1 < n_half) {                           // next half's scores are queued before this half's dQ product
+          ok = issue_sdp(hf + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(&ds_full[hf & 1], (hf >> 1) & 1u, p.status);
         if (!ok) break;
         tc_fence_after_sync();
+        const int j = hf >> 1, half = hf & 1;
+        const int s = j % kStages;
+        const uint32_t aK = smem_u32(sK + s * S::kTile);
+        const uint32_t tS = tmem_base + static_cast<uint32_t>((hf & 1) * 128);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_f16_ts(tmem_base + kColDQ, tmem_base + kColS + kk * 8, make_smem_desc(aK + kk * 2048, kBoxBytes, 1024),
-                        kIdescDQ, (j | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {                 // 64 keys = 4 K-steps of 16
+          tc_mma_f16_ts(tmem_base + kColDQ, tS + kk * 8, make_smem_desc(aK + (half * 4 + kk) * 2048, kBoxBytes, 1024),
+                        kIdescDQ, (hf | kk) != 0 ? 1u : 0u);
         }
-        tc_commit(&k_empty[s]);
-        tc_commit(dq_done);
+        if (half == 1) tc_commit(&k_empty[s]);
+        if (hf == n_half - 1) tc_commit(dq_done);        // one completion, after the last product
       }
     }
   } else {
@@ -185,20 +204,21 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
     const float lse2 = q_valid ? p.lse[stat_idx] * kLog2e : 0.f;
     const float delta = q_valid ? p.delta[stat_idx] : 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      ok = mbar_wait(sdp_full, j & 1u, p.status);
+    const int n_half = 2 * n_kv;
+    for (int hf = 0; hf < n_half && ok; ++hf) {
+      ok = mbar_wait(&sdp_full[hf & 1], (hf >> 1) & 1u, p.status);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t tS = tmem_base + lane_off + kColS, tDP = tmem_base + lane_off + kColDP;
-      const int kbase = j * 128;
-      // the select per element is only needed on tiles that touch the causal diagonal, the end of the keys or a
+      const uint32_t tS = tmem_base + lane_off + static_cast<uint32_t>((hf & 1) * 128), tDP = tS + 64;
+      const int kbase = (hf >> 1) * 128 + (hf & 1) * 64;
+      // the select per element is only needed on halves that touch the causal diagonal, the end of the keys or a
       // query row past the end (uniform over the warp except for q_valid, which is folded in)
-      const bool need_mask = !q_valid || (kbase + 127 > key_limit) || (kbase + 128 > k_len);
+      const bool need_mask = !q_valid || (kbase + 63 > key_limit) || (kbase + 64 > k_len);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-delta, -delta);
-      uint32_t pk[64];
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tDP + c * 32, dv);
@@ -220,18 +240,13 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
           pk[c * 16 + i] = pack_bf16(r.x, r.y);
         }
       }
-      {
-        uint32_t(&h0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
-        uint32_t(&h1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
-        tmem_st32(tS, h0);
-        tmem_st32(tS + 32, h1);
-      }
+      tmem_st32(tS, pk);
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[hf & 1]);
     }
     if (ok && n_kv > 0) {
-      ok = mbar_wait(dq_done, (n_kv - 1) & 1u, p.status);
+      ok = mbar_wait(dq_done, 0u, p.status);
       ok = __all_sync(0xFFFFFFFFu, ok);
     }
     if (ok) {

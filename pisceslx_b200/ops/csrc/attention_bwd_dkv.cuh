@@ -1,5 +1,9 @@
 // dK / dV kernel of the flash attention backward (see attention_bwd.cuh for the scheme).
-// TMEM columns: [0,128) S^T then P^T (bf16), [128,256) dP^T then dS^T (bf16), [256,256+D) dV, [384,384+D) dK.
+// A 128-query block is processed as two 64-query halves so that S^T / dP^T double-buffer inside the 512 TMEM columns:
+// while the softmax threads turn half h into P^T / dS^T, the tensor core already computes S^T / dP^T of half h + 1,
+// and the dV / dK products of half h are queued behind them.
+// TMEM columns: stage s in {0,1}: [128 s, 128 s + 64) S^T then P^T (bf16, 32 columns),
+//               [128 s + 64, 128 s + 128) dP^T then dS^T (bf16, 32 columns); [256,256+D) dV, [384,384+D) dK.
 #pragma once
 
 namespace yv {
@@ -10,10 +14,11 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
   constexpr int kStages = S::kStages;
   constexpr int kDBoxes = D / 64;
   constexpr uint32_t kBoxBytes = 128 * 128;
-  constexpr uint32_t kIdescNT = make_idesc_bf16(128, 128, false, false);
+  constexpr uint32_t kIdescNT = make_idesc_bf16(128, 64, false, false);     // 128 keys x 64 queries
   constexpr uint32_t kIdescAcc = make_idesc_bf16(128, D, false, true);
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
+  constexpr uint32_t kColDV = 256, kColDK = 384;
+  constexpr uint32_t kHalfRows = 64 * 128;            // byte offset of query rows 64.. inside a 64-column box
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -29,10 +34,10 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
   uint64_t* do_full = bars + 3;         // [2]
   uint64_t* q_empty = bars + 5;         // [2]
   uint64_t* do_empty = bars + 7;        // [2]
-  uint64_t* sdp_full = bars + 9;        // [1]
-  uint64_t* pds_full = bars + 10;       // [1] 128 arrivals
-  uint64_t* acc_done = bars + 11;       // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* sdp_full = bars + 9;        // [2] per TMEM stage
+  uint64_t* pds_full = bars + 11;       // [2] 128 arrivals each
+  uint64_t* acc_done = bars + 13;       // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, hkv = blockIdx.y;
@@ -52,6 +57,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
   }
   const int n_i = n_qblk > i_start ? n_qblk - i_start : 0;
   const int n_it = n_i * G;
+  const int n_half = 2 * n_it;                      // 64-query halves
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -59,8 +65,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       mbar_init(&q_full[s], 1); mbar_init(&do_full[s], 1);
       mbar_init(&q_empty[s], 1); mbar_init(&do_empty[s], 1);
     }
-    mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128); }
     mbar_init(acc_done, 1);
     fence_barrier_init();
   }
@@ -102,44 +107,65 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
     if (elect_one() && n_it > 0) {
       bool ok = mbar_wait(kv_full, 0, p.status);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
-      for (int it = 0; it < n_it && ok; ++it) {
+      // S^T and dP^T of half `hf` (block hf / 2, rows 64 (hf % 2) .. of its Q / dO tiles) into TMEM stage hf % 2
+      auto issue_sdp = [&](int hf) -> bool {
+        const int it = hf >> 1, half = hf & 1;
         const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
-        ok = mbar_wait(&q_full[s], ph, p.status);
-        if (!ok) break;
-        ok = mbar_wait(&do_full[s], ph, p.status);
+        if (half == 0) {
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(&q_full[s], ph, p.status)) return false;
+          if (!mbar_wait(&do_full[s], ph, p.status)) return false;
+          tc_fence_after_sync();
+        }
+        const uint32_t aQ = smem_u32(sQ + s * S::kTile) + half * kHalfRows;
+        const uint32_t aDO = smem_u32(sDO + s * S::kTile) + half * kHalfRows;
+        const uint32_t tS = tmem_base + static_cast<uint32_t>((hf & 1) * 128);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          tc_mma_f16_ss(tS, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024), kIdescNT,
+                        kk != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+          tc_mma_f16_ss(tS + 64, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + off, 16, 1024), kIdescNT,
+                        kk != 0 ? 1u : 0u);
+        }
+        tc_commit(&sdp_full[hf & 1]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int hf = 0; hf < n_half && ok; ++hf) {
+        // keep the tensor core busy while the softmax threads work on half hf: queue the next half's scores first
+        if (hf + 1 < n_half) {
+          ok = issue_sdp(hf + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(&pds_full[hf & 1], (hf >> 1) & 1u, p.status);
         if (!ok) break;
         tc_fence_after_sync();
+        const int it = hf >> 1, half = hf & 1;
+        const int s = it % kStages;
         const uint32_t aQ = smem_u32(sQ + s * S::kTile), aDO = smem_u32(sDO + s * S::kTile);
+        const uint32_t tS = tmem_base + static_cast<uint32_t>((hf & 1) * 128);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-          tc_mma_f16_ss(tmem_base + kColST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024),
-                        kIdescNT, kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {                 // 64 queries = 4 K-steps of 16
+          tc_mma_f16_ts(tmem_base + kColDV, tS + kk * 8,
+                        make_smem_desc(aDO + (half * 4 + kk) * 2048, kBoxBytes, 1024), kIdescAcc, (hf | kk) != 0 ? 1u : 0u);
         }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-          tc_mma_f16_ss(tmem_base + kColDPT, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + off, 16, 1024),
-                        kIdescNT, kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {
+          tc_mma_f16_ts(tmem_base + kColDK, tS + 64 + kk * 8,
+                        make_smem_desc(aQ + (half * 4 + kk) * 2048, kBoxBytes, 1024), kIdescAcc, (hf | kk) != 0 ? 1u : 0u);
         }
-        tc_commit(sdp_full);
-        ok = mbar_wait(pds_full, it & 1u, p.status);
-        if (!ok) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_f16_ts(tmem_base + kColDV, tmem_base + kColST + kk * 8,
-                        make_smem_desc(aDO + kk * 2048, kBoxBytes, 1024), kIdescAcc, (it | kk) != 0 ? 1u : 0u);
+        if (half == 1) {
+          tc_commit(&q_empty[s]);
+          tc_commit(&do_empty[s]);
         }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_f16_ts(tmem_base + kColDK, tmem_base + kColDPT + kk * 8,
-                        make_smem_desc(aQ + kk * 2048, kBoxBytes, 1024), kIdescAcc, (it | kk) != 0 ? 1u : 0u);
-        }
-        tc_commit(&q_empty[s]);
-        tc_commit(&do_empty[s]);
-        tc_commit(acc_done);
+        // one completion only, after the very last products: the scores of half hf + 1 are issued ahead of the
+        // accumulator products of half hf, so a barrier that flipped every half could be observed one phase early
+        if (hf == n_half - 1) tc_commit(acc_done);
       }
     }
   } else {
@@ -150,22 +176,23 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
     const int key = k0 + row;
     const bool key_valid = key < k_len;
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
+    for (int hf = 0; hf < n_half && ok; ++hf) {
+      const int it = hf >> 1, half = hf & 1;
       const int g = it / n_i, i = i_start + it % n_i;
       const int h = hkv * G + g;
       const int qb = i * 128;
       float* lse_b = s_lse + (it & 1) * 128;
       float* del_b = s_delta + (it & 1) * 128;
-      {
+      if (half == 0) {
         const int qpos = qb + tix;
         const bool v = qpos < q_len;
         const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
         // stored negated so that the consumers fold them into packed fused multiply-adds
         lse_b[tix] = v ? -p.lse[idx] * kLog2e : -INFINITY;   // -inf -> probability 0 for rows past the end
         del_b[tix] = v ? -p.delta[idx] : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      ok = mbar_wait(sdp_full, it & 1u, p.status);
+      ok = mbar_wait(&sdp_full[hf & 1], (hf >> 1) & 1u, p.status);
       {
         uint32_t all_ok;
         asm volatile(
@@ -182,15 +209,15 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       }
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t tST = tmem_base + lane_off + kColST, tDPT = tmem_base + lane_off + kColDPT;
+      const uint32_t tST = tmem_base + lane_off + static_cast<uint32_t>((hf & 1) * 128), tDPT = tST + 64;
       // a query column c is visible to this key iff key <= (qb + c) + shift
       const int first_vis_c = p.causal ? (key - causal_shift - qb) : 0;
-      // every (key, query) pair of this tile is visible: no per-element selects (uniform over the CTA)
+      // every (key, query) pair of this block is visible: no per-element selects (uniform over the CTA)
       const bool full_vis = (!p.causal || qb >= k0 + 127 - causal_shift) && (k0 + 127 < k_len);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-      uint32_t pp[64], ds[64];
+      uint32_t pp[32], ds[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld32(tST + c * 32, sv);
         tmem_ld32(tDPT + c * 32, dv);
@@ -199,7 +226,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
         // special-function instruction whose result is the packed P operand; dS = P * (dP - delta) in packed fp32.
 #pragma unroll
         for (int i2 = 0; i2 < 16; ++i2) {
-          const int col = c * 32 + 2 * i2;
+          const int col = half * 64 + c * 32 + 2 * i2;           // query column inside the 128-query block
           const float2 nl = *reinterpret_cast<const float2*>(lse_b + col);
           const float2 nd = *reinterpret_cast<const float2*>(del_b + col);
           float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i2]), __uint_as_float(sv[2 * i2 + 1])), sc2, nl);
@@ -216,22 +243,14 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
           ds[c * 16 + i2] = pack_bf16(dsf.x, dsf.y);
         }
       }
-      {
-        uint32_t(&a0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pp[0]);
-        uint32_t(&a1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pp[32]);
-        uint32_t(&b0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ds[0]);
-        uint32_t(&b1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&ds[32]);
-        tmem_st32(tST, a0);
-        tmem_st32(tST + 32, a1);
-        tmem_st32(tDPT, b0);
-        tmem_st32(tDPT + 32, b1);
-      }
+      tmem_st32(tST, pp);
+      tmem_st32(tDPT, ds);
       tc_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(pds_full);
+      mbar_arrive(&pds_full[hf & 1]);
     }
     if (ok && n_it > 0) {
-      ok = mbar_wait(acc_done, (n_it - 1) & 1u, p.status);
+      ok = mbar_wait(acc_done, 0u, p.status);
       ok = __all_sync(0xFFFFFFFFu, ok);
     }
     if (ok) {

@@ -244,6 +244,24 @@ class PiscesLxQuantizationEngine:
             bits_w += bits * w0.numel()
             n_w += w0.numel()
             layers += 1
+        # weight matrices held as bare parameters (fused QKV / gate-up matrices, stacked expert weights [E, out, in])
+        linear_weights = {id(m.weight) for m in model.modules() if isinstance(m, nn.Linear)}
+        for name, p in model.named_parameters():
+            if p.dim() < 2 or id(p) in linear_weights or any(s in name for s in c.skip) or "norm" in name:
+                continue
+            bits = c.per_layer_bits.get(name, c.bits)
+            w0 = p.detach().clone()
+            mats = w0.reshape(-1, w0.shape[-1]).cpu()                     # rows = output channels of every stacked matrix
+            group = min(c.group_size, mats.shape[1])
+            while mats.shape[1] % group:
+                group //= 2
+            wq = op.run({"weight": mats, "activations": None, "bits": bits, "group_size": max(group, 1)})["weight"]
+            with torch.no_grad():
+                p.copy_(wq.reshape(w0.shape).to(p.device, p.dtype))
+            errs[name] = float((wq.float() - mats.float()).norm() / mats.float().norm().clamp_min(1e-12))
+            bits_w += bits * w0.numel()
+            n_w += w0.numel()
+            layers += 1
         return PiscesLxQuantizationResult(layers, PiscesLxQuantizationMethod(c.method).value, bits_w / max(n_w, 1), errs,
                                           time.perf_counter() - t0)
 

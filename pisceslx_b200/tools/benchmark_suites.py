@@ -209,3 +209,63 @@ class PiscesLxVQABenchmark:
 def load_suite_rows(path: str, limit: Optional[int] = None) -> List[Dict[str, Any]]:
     rows = read_jsonl(path)
     return rows[:limit] if limit else rows
+
+
+# --------------------------------------------------------------------------------------------------
+# suite registry used by ``manage.py benchmark --benchmark NAME | --list | --selftest``
+# --------------------------------------------------------------------------------------------------
+_SELFTEST_ROWS = {
+    "mmlu": [{"question": "2 + 2 = ?", "choices": ["3", "4", "5", "6"], "answer": 1, "subject": "arithmetic"},
+             {"question": "The capital of France is", "choices": ["Paris", "Rome", "Oslo", "Bern"], "answer": 0, "subject": "geography"}],
+    "gsm8k": [{"question": "Tom has 3 apples and buys 4 more. How many apples does he have?", "answer": "3 + 4 = 7 #### 7"}],
+    "aime": [{"question": "Find 10 * 12.", "answer": "120"}],
+}
+
+
+def available_suites() -> List[str]:
+    return ["mmlu", "gsm8k", "aime", "humaneval", "needle"]
+
+
+def _generate_fn(model: Any, tokenizer: Any) -> GenerateFn:
+    import torch
+
+    def gen(prompt: str, max_new_tokens: int = 64) -> str:
+        dev = next(model.parameters()).device
+        ids = torch.tensor([tokenizer.encode(prompt)], dtype=torch.long, device=dev).clamp_(0, model.cfg.vocab_size - 1)
+        out, _ = model.generate(ids, max_new_tokens=max_new_tokens)
+        return tokenizer.decode(out[0, ids.shape[1]:].tolist())
+    return gen
+
+
+def run_suite(name: str, model: Any, tokenizer: Any = None, data_path: Optional[str] = None,
+              max_samples: Optional[int] = None) -> Dict[str, Any]:
+    """Evaluate ``model`` on suite ``name``.  Rows come from ``data_path`` (jsonl in the suite's row format) or, without
+    one, from the built-in smoke rows: enough to exercise the harness end to end, not a score to report."""
+    from ..models.tokenizer import YvTokenizer
+    tok = tokenizer or YvTokenizer.instance()
+    name = name.lower()
+    if name not in available_suites():
+        raise ValueError(f"unknown suite {name!r}; available: {', '.join(available_suites())}")
+    rows = load_suite_rows(data_path, max_samples) if data_path else list(_SELFTEST_ROWS.get(name, []))[: max_samples or None]
+    gen = _generate_fn(model, tok)
+    if name == "mmlu":
+        res = PiscesLxMMLUBenchmark(model, tok).evaluate(rows)
+    elif name == "gsm8k":
+        res = PiscesLxGSM8KBenchmark(gen).evaluate(rows, 32)
+    elif name == "aime":
+        res = PiscesLxAIMEBenchmark(gen).evaluate(rows, 32)
+    elif name == "humaneval":
+        res = PiscesLxHumanEvalBenchmark(gen).evaluate(rows) if rows else {"pass@1": 0.0, "n": 0}
+    else:
+        res = PiscesLxLongContextBenchmark(gen, tok).evaluate(lengths=(256,), depths=(0.5,))
+    return {"suite": name, "rows": len(rows), "source": data_path or "built-in smoke rows", "result": res}
+
+
+def selftest() -> Dict[str, Any]:
+    """Exercise the scoring code without a model: answer extraction, pass@k, the patch-format checker."""
+    checks = {
+        "last_number": last_number("so the total is 1,234 apples") in ("1234", "1,234"),
+        "pass_at_k": abs(pass_at_k(10, 3, 1) - 0.3) < 1e-9 and pass_at_k(5, 5, 2) == 1.0,
+        "gsm8k_scoring": PiscesLxGSM8KBenchmark(lambda p, n=0: "the answer is 7").evaluate(_SELFTEST_ROWS["gsm8k"])["exact_match"] == 1.0,
+    }
+    return {"ok": all(checks.values()), "checks": checks}
