@@ -117,11 +117,13 @@ class PiscesLxTrainOrchestrator:
         tp = args.tensor_parallel or int(dist_cfg.get("tensor_parallel", 1))
         ep = args.expert_parallel or int(dist_cfg.get("expert_parallel", 1))
         pp = args.pipeline_parallel or int(dist_cfg.get("pipeline_parallel", 1))
+        cp = getattr(args, "context_parallel", None) or int(dist_cfg.get("context_parallel", 1))
         world = int(os.environ.get("WORLD_SIZE", "1"))
         if world == 1:
-            tp = ep = pp = 1
+            tp = ep = pp = cp = 1
         device = torch.device(args.device) if args.device else None
-        par = init_parallel(tp=tp, ep=ep, pp=pp, device=device)
+        par = init_parallel(tp=tp, ep=ep, pp=pp, cp=cp, device=device)
+        model_cfg.context_parallel = cp
         if args.no_fused_comm:
             from ..parallel import fused
             fused.set_enabled(False)
@@ -135,13 +137,19 @@ class PiscesLxTrainOrchestrator:
         if args.dry_run:
             if par.rank == 0:
                 print(json.dumps({"model": model_cfg.count_parameters(), "trainer": tcfg.__dict__, "seq_len": seq_len,
-                                  "batch": batch, "parallel": {"tp": tp, "ep": ep, "pp": pp, "world": world}},
+                                  "batch": batch, "parallel": {"tp": tp, "ep": ep, "pp": pp, "cp": cp, "world": world}},
                                  default=str))
             return 0
         model = build_model(model_cfg, par.device, dtype, parallel=par if world > 1 else None, seed=args.seed)
         attach_optional_components(model, model_cfg, par)
         tcfg.streaming_optimizer = bool(stage_cfg.get("streaming_optimizer", False))
         policy_notes = self.apply_policy(model_cfg, stage_cfg, tcfg, args, par, seq_len)
+        if getattr(args, "sharding", None):
+            tcfg.sharding = args.sharding
+        if getattr(args, "state_dtype", None):
+            tcfg.state_dtype = args.state_dtype
+        if pp > 1:
+            tcfg.streaming_optimizer = False
         trainer = YvTrainer(model, tcfg, parallel=par if world > 1 else None)
         store = PiscesLxRunStore(Path(args.run_dir) if args.run_dir else None)
         run_id = args.run_id or PiscesLxRunIdFactory.new("train")
@@ -158,7 +166,8 @@ class PiscesLxTrainOrchestrator:
         if args.resume_ckpt:
             from .checkpoint import load_checkpoint
             load_checkpoint(trainer, args.resume_ckpt, reset_lr=args.reset_lr)
-        loader = build_dataloader(args.dataset, model_cfg.vocab_size, seq_len, batch, seed=args.seed + par.dp_rank)
+        # context-parallel peers and the stages of one pipeline read the same sequences
+        loader = build_dataloader(args.dataset, model_cfg.vocab_size, seq_len, batch, seed=args.seed + par.data_rank)
         status = "completed"
         try:
             for batch_t in loader:

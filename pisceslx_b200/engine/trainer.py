@@ -49,6 +49,7 @@ class YvTrainerConfig:
     state_dtype: Optional[str] = None       # "bf16" | "fp32" | "int8" (Muon momentum block-quantised) | None (= parameter dtype)
     recompute_policy: str = "config"        # "config": as the model config says; "auto": sized from measured memory
     sharding: str = "zero1"                 # "zero1": optimizer state by owner; "full_shard": ZeRO-3 units per block
+    pipeline_schedule: str = "1f1b"         # "1f1b" | "gpipe" (used when the parallel state has pipeline stages)
     optimizer_kwargs: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -90,6 +91,15 @@ class YvTrainer:
         if parallel is not None and getattr(parallel, "world_size", 1) > 1:
             from ..parallel.zero import YvGradientSynchronizer
             self.dp = YvGradientSynchronizer(model, parallel, self.optimizer, streaming=self.streaming)
+        self.pipeline = None
+        if parallel is not None and getattr(parallel, "pp_size", 1) > 1:
+            # this rank holds one stage (a contiguous slice of layers); micro-batches travel between stages over
+            # NCCL point-to-point (parallel.pp).  Gradients stay in .grad until the step: no streaming optimizer.
+            from ..parallel.pp import YvPipelineStage
+            if self.streaming:
+                raise ValueError("pipeline parallelism uses the plain optimizer step (streaming_optimizer=False)")
+            mcfg = model.cfg
+            self.pipeline = YvPipelineStage(model, parallel, mcfg.hidden_size, next(model.parameters()).dtype)
         self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -147,7 +157,24 @@ class YvTrainer:
         total_loss = None
         tokens = int(batch["input_ids"].numel())
         n_micro = 1
-        for ci, n_micro, mb in self._micro_batches(batch):
+        if self.pipeline is not None:
+            micros = [mb for _, n_micro, mb in self._micro_batches(batch)]
+            for m in micros:
+                m.setdefault("labels", m["input_ids"])
+            if self.dp is not None:
+                self.dp.begin_micro_batch(0, len(micros))
+            loss = self.pipeline.run(micros, cfg.pipeline_schedule)          # backward included, scaled 1 / n
+            # the last stage knows the loss: share it with the other stages for reporting
+            t = (loss.detach().float() if loss is not None else torch.zeros((), device=self.device)).reshape(1).to(self.device)
+            import torch.distributed as dist
+            last_stage = dist.get_global_rank(self.parallel.pp_group, self.parallel.pp_size - 1) \
+                if self.parallel.pp_group is not None else 0
+            dist.broadcast(t, src=last_stage, group=self.parallel.pp_group)
+            total_loss, n_micro = t[0] * len(micros), len(micros)
+            micro_iter = ()
+        else:
+            micro_iter = self._micro_batches(batch)
+        for ci, n_micro, mb in micro_iter:
             lab = mb.get("labels", mb["input_ids"])
             a = ci * max(1, min(cfg.micro_batch_size, batch["input_ids"].shape[0]))
             lh = labels_host[a:a + lab.shape[0]]

@@ -47,6 +47,8 @@ class AttnContext:
     block_table: Optional[torch.Tensor] = None   # int32 [B, max_blocks]
     seq_lens: Optional[torch.Tensor] = None      # int32 [B] lengths after this step
     decode: bool = False
+    # context parallelism: this rank holds one chunk of every sequence; K/V are gathered over cp_group
+    cp_group: Any = None
     extras: Dict[str, Any] = field(default_factory=dict)
 
 
@@ -168,6 +170,8 @@ class YvAttention(nn.Module):
     def _attend(self, qkv: torch.Tensor, ctx: AttnContext) -> torch.Tensor:
         """Prefill / training attention over the packed projection, writing the paged cache when one is attached."""
         nq, nk = self.hq * self.d, self.hk * self.d
+        if ctx.cp_group is not None:
+            return self._attend_context_parallel(qkv, ctx)
         o = F_.rope_attention(qkv, ctx.cos, ctx.sin, ctx.positions, ctx.cu_seqlens, ctx.max_len, self.hq, self.hk,
                               self.d, self.rot_dim, ctx.causal, self.scale)
         if ctx.cache is not None and ctx.slot_map is not None:
@@ -179,6 +183,26 @@ class YvAttention(nn.Module):
                                        self.rot_dim).reshape(-1, nk)
             F_.kv_cache_write(k_rot.detach(), v_new.detach(), kc, vc, ctx.slot_map)
         return o
+
+    def _attend_context_parallel(self, qkv: torch.Tensor, ctx: AttnContext) -> torch.Tensor:
+        """Training attention when every sequence is split over the ranks of ``ctx.cp_group`` (contiguous chunks):
+        rotate q / k at their GLOBAL positions, all-gather K / V of each sequence (differentiable: the backward is a
+        reduce-scatter) and attend the local queries up to their causal horizon (``parallel.cp``)."""
+        from ..ops import reference as ref
+        from ..parallel import cp
+        T = qkv.shape[0]
+        nq, nk = self.hq * self.d, self.hk * self.d
+        q, k, v = qkv[:, :nq], qkv[:, nq:nq + nk], qkv[:, nq + nk:]
+        if ctx.cos is not None:
+            q = ref.apply_rope(q.reshape(T, self.hq, self.d), ctx.cos, ctx.sin, ctx.positions, self.rot_dim).reshape(T, nq)
+            k = ref.apply_rope(k.reshape(T, self.hk, self.d), ctx.cos, ctx.sin, ctx.positions, self.rot_dim).reshape(T, nk)
+        cu = ctx.cu_seqlens.tolist()
+        outs = []
+        for b in range(len(cu) - 1):
+            sl = slice(cu[b], cu[b + 1])
+            outs.append(cp.allgather_attention(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), ctx.cp_group,
+                                               self.hq, self.hk, self.d, causal=ctx.causal, scale=self.scale))
+        return torch.cat(outs, 0).to(qkv.dtype)
 
     def _decode(self, qkv: torch.Tensor, ctx: AttnContext) -> torch.Tensor:
         B = qkv.shape[0]

@@ -179,6 +179,9 @@ class YvModelForCausalLM(nn.Module):
         cfg = self.cfg
         if prefix_embeds is None and modal and self.model.modal_fusion is not None:
             prefix_embeds = self.model.modal_fusion.encode_modalities(self.model, **modal)
+        par = self.parallel
+        if par is not None and getattr(par, "cp_size", 1) > 1 and self.training and ctx is None and input_ids is not None:
+            return self._forward_context_parallel(input_ids, attention_mask, labels)
         out = self.model(input_ids, attention_mask, inputs_embeds, prefix_embeds, ctx, hidden_in)
         hidden, aux = out["hidden_states"], out["aux_loss"]
         res = YvModelOutput(aux_loss=aux, loss=None, lm_loss=None, mtp_loss=None, logits=None)
@@ -218,6 +221,39 @@ class YvModelForCausalLM(nn.Module):
             if not cfg.moe_aux_loss_free:
                 loss = loss + cfg.moe_aux_loss_weight * aux
             res["loss"] = loss
+        return res
+
+    def _forward_context_parallel(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor],
+                                  labels: Optional[torch.Tensor]) -> YvModelOutput:
+        """Training forward with the sequence dimension split over ``parallel.cp_group``: every rank receives the FULL
+        ``[B, S]`` batch (context-parallel peers read the same data), keeps tokens ``[r L, (r+1) L)`` of every
+        sequence at their global positions, and computes the loss of its own positions against the globally shifted
+        targets, normalised by the global target count, so that the mean over ranks is the full-sequence loss."""
+        par, cfg = self.parallel, self.cfg
+        W, r = par.cp_size, par.cp_rank
+        B, S = input_ids.shape
+        assert S % W == 0, f"sequence length {S} must be divisible by the context-parallel size {W}"
+        L = S // W
+        ids = input_ids[:, r * L:(r + 1) * L]
+        am = attention_mask[:, r * L:(r + 1) * L] if attention_mask is not None else None
+        ctx = self.model.build_context(B, L, ids.device)
+        ctx.positions = ctx.positions + r * L
+        if self.model.rotary is not None:
+            ctx.cos, ctx.sin = self.model.rotary.tables(S, ids.device)
+        ctx.cp_group = par.cp_group
+        out = self.model(ids, am, None, None, ctx, None)
+        hidden, aux = out["hidden_states"], out["aux_loss"]
+        res = YvModelOutput(aux_loss=aux, loss=None, lm_loss=None, mtp_loss=None, logits=None)
+        if labels is not None:
+            tgt_full = torch.cat([labels[:, 1:], labels.new_full((B, 1), -100)], dim=1)       # target of position t is label t+1
+            tgt = tgt_full[:, r * L:(r + 1) * L].reshape(-1)
+            n_global = int((tgt_full != -100).sum().item()) if tgt_full.device.type == "cpu" else \
+                int((tgt_full != -100).sum().item())
+            lm = linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.head_weight, tgt, -100, 1)
+            lm = lm * (float(W) / max(n_global, 1))            # sum over local targets / (global count / ranks)
+            res["lm_loss"] = res["loss"] = lm
+            if not cfg.moe_aux_loss_free:
+                res["loss"] = lm + cfg.moe_aux_loss_weight * aux
         return res
 
     # ------------------------------------------------------------------------------------------------

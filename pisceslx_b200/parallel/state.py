@@ -43,6 +43,8 @@ class YvParallelState:
     model_parallel_group: Any = None   # tp x pp (norm reductions for clipping)
     expert_grad_group: Any = None      # tp x edp: ranks that hold replicas of the same routed experts
     stage_group: Any = None            # tp x dp: all ranks of one pipeline stage
+    cp_group: Any = None               # context parallel: cp consecutive data-parallel ranks share their sequences
+    cp_rank: int = 0
     world_group: Any = None
     backend: str = "none"
     device: torch.device = field(default_factory=lambda: torch.device("cpu"))
@@ -52,6 +54,15 @@ class YvParallelState:
     @property
     def is_distributed(self) -> bool:
         return self.world_size > 1
+
+    @property
+    def data_rank(self) -> int:
+        """Index of the distinct data shard this rank reads: context-parallel peers read the same sequences."""
+        return self.dp_rank // max(self.cp_size, 1)
+
+    @property
+    def data_size(self) -> int:
+        return self.dp_size // max(self.cp_size, 1)
 
 
 _STATE: Optional[YvParallelState] = None
@@ -74,7 +85,7 @@ def default_nccl_env() -> None:
 
 
 def init_parallel(tp: int = 1, ep: int = 1, pp: int = 1, backend: Optional[str] = None,
-                  timeout_s: float = 600.0, device: Optional[torch.device] = None) -> YvParallelState:
+                  timeout_s: float = 600.0, device: Optional[torch.device] = None, cp: int = 1) -> YvParallelState:
     """Create (or reuse) the default process group from the torchrun environment and build the mesh."""
     global _STATE
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -131,6 +142,13 @@ def init_parallel(tp: int = 1, ep: int = 1, pp: int = 1, backend: Optional[str] 
     st.expert_grad_group = make([[r(p, e0 * ep + e, t) for e0 in range(dp // ep) for t in range(tp)]
                                  for p in range(pp) for e in range(ep)])
     st.stage_group = make([[r(p, d, t) for d in range(dp) for t in range(tp)] for p in range(pp)])
+    # Context parallelism is carved out of the data-parallel dimension: cp consecutive dp ranks hold consecutive
+    # chunks of the SAME sequences.  Gradients are still reduced over the whole dp group (different tokens).
+    assert dp % cp == 0, f"dp {dp} not divisible by cp {cp}"
+    st.cp_size, st.cp_rank = cp, st.dp_rank % cp
+    if cp > 1:
+        st.cp_group = make([[r(p, c0 * cp + c, t) for c in range(cp)] for p in range(pp) for t in range(tp)
+                            for c0 in range(dp // cp)])
     if pp > 1:
         st.pp_prev = r(st.pp_rank - 1, st.dp_rank, st.tp_rank) if st.pp_rank > 0 else None
         st.pp_next = r(st.pp_rank + 1, st.dp_rank, st.tp_rank) if st.pp_rank < pp - 1 else None

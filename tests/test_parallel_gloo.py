@@ -25,9 +25,11 @@ WORKER = textwrap.dedent("""
     from pisceslx_b200.engine.trainer import YvTrainer, YvTrainerConfig
     tp, ep, steps, out = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
     torch.manual_seed(0)
-    par = init_parallel(tp=tp, ep=ep, backend="gloo", device=torch.device("cpu"), timeout_s=120)
+    cp, pp = int(os.environ.get("YV_TEST_CP", "1")), int(os.environ.get("YV_TEST_PP", "1"))
+    par = init_parallel(tp=tp, ep=ep, cp=cp, pp=pp, backend="gloo", device=torch.device("cpu"), timeout_s=120)
     cfg = YvConfig.tiny_text_moe(vocab_size=1024)
     cfg.n_layer = 2
+    cfg.context_parallel = cp
     cfg.use_gradient_checkpointing = False
     cfg.extra["moe_deterministic"] = True
     model = build_model(cfg, "cpu", torch.float32, parallel=par if par.world_size > 1 else None, seed=7)
@@ -43,9 +45,9 @@ WORKER = textwrap.dedent("""
     losses, norms = [], []
     for s in range(steps):
         b = data[s]
-        if par.dp_size > 1:
-            per = b.shape[0] // par.dp_size
-            b = b[par.dp_rank * per:(par.dp_rank + 1) * per]
+        if par.data_size > 1:
+            per = b.shape[0] // par.data_size
+            b = b[par.data_rank * per:(par.data_rank + 1) * per]
         res = tr.train_step({{"input_ids": b, "labels": b}})
         losses.append(res["loss"])
         norms.append(res["grad_norm"] or 0.0)
@@ -223,3 +225,36 @@ def test_trainer_full_shard_matches_single_process(tmp_path, init_weights):
         assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (n_single, n_multi)
     for a, b in zip(single, multi):
         assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,cp", [(2, 2), (4, 2)])
+def test_context_parallel_training_matches_single_process(tmp_path, init_weights, world, cp):
+    """Sequences split over context-parallel ranks (K / V all-gathered per layer, loss of local positions against the
+    globally shifted targets): same losses and gradient norm as one process; with 4 ranks two data shards x cp 2."""
+    steps = 3
+    env = {"YV_TEST_CLIP": "1.0", "YV_TEST_BATCH": "4"}
+    single = _run(tmp_path, 1, 1, 1, steps, init_weights, f"cp_single{world}", env)
+    n_single = json.load(open(str(tmp_path / f"loss_cp_single{world}.json") + ".norms"))
+    multi = _run(tmp_path, world, 1, 1, steps, init_weights, f"cp_w{world}", dict(env, YV_TEST_CP=str(cp)))
+    n_multi = json.load(open(str(tmp_path / f"loss_cp_w{world}.json") + ".norms"))
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
+    for a, b in zip(n_single, n_multi):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (n_single, n_multi)
+
+
+@pytest.mark.timeout(900)
+def test_pipeline_parallel_through_the_trainer_matches_single_process(tmp_path, init_weights):
+    """Two pipeline stages driven by ``YvTrainer.train_step`` (1F1B over two micro-batches, clipping with the norm summed
+    over stages, AdamW per stage): same losses and gradient norms as one process."""
+    steps = 3
+    env = {"YV_TEST_CLIP": "1.0", "YV_TEST_BATCH": "4"}
+    single = _run(tmp_path, 1, 1, 1, steps, init_weights, "pp_single", env)
+    n_single = json.load(open(str(tmp_path / "loss_pp_single.json") + ".norms"))
+    multi = _run(tmp_path, 2, 1, 1, steps, init_weights, "pp_w2", dict(env, YV_TEST_PP="2"))
+    n_multi = json.load(open(str(tmp_path / "loss_pp_w2.json") + ".norms"))
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
+    for a, b in zip(n_single, n_multi):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (n_single, n_multi)
