@@ -106,8 +106,8 @@ int launch_attn_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
       r = set_smem(attn_bwd_dkv_kernel<128>, AttnBwdSmem<128>::kTotal); if (r) return r;
       cfg.cur() = 1;
     }
-    attn_bwd_dkv_kernel<128><<<grid_k, 192, AttnBwdSmem<128>::kTotal, stream>>>(p);
-    attn_bwd_dq_kernel<128><<<grid_q, 192, AttnBwdSmem<128>::kTotal, stream>>>(p);
+    attn_bwd_dkv_kernel<128><<<grid_k, kAttnBwdThreads, AttnBwdSmem<128>::kTotal, stream>>>(p);
+    attn_bwd_dq_kernel<128><<<grid_q, kAttnBwdThreads, AttnBwdSmem<128>::kTotal, stream>>>(p);
   } else {
     static PerDeviceInt cfg;
     if (!cfg.cur()) {
@@ -115,8 +115,8 @@ int launch_attn_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
       r = set_smem(attn_bwd_dkv_kernel<64>, AttnBwdSmem<64>::kTotal); if (r) return r;
       cfg.cur() = 1;
     }
-    attn_bwd_dkv_kernel<64><<<grid_k, 192, AttnBwdSmem<64>::kTotal, stream>>>(p);
-    attn_bwd_dq_kernel<64><<<grid_q, 192, AttnBwdSmem<64>::kTotal, stream>>>(p);
+    attn_bwd_dkv_kernel<64><<<grid_k, kAttnBwdThreads, AttnBwdSmem<64>::kTotal, stream>>>(p);
+    attn_bwd_dq_kernel<64><<<grid_q, kAttnBwdThreads, AttnBwdSmem<64>::kTotal, stream>>>(p);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -35,6 +35,10 @@ struct AttnBwdParams {
 };
 
 constexpr float kLog2e = 1.4426950408889634f;
+// Backward CTAs: TMA warp, MMA warp and eight softmax warps (two per TMEM lane quarter, each converting half of the
+// columns of a 64-wide half-block).
+constexpr int kAttnBwdSoftmaxThreads = 256;
+constexpr int kAttnBwdThreads = 64 + kAttnBwdSoftmaxThreads;
 
 template <int D>
 struct AttnBwdSmem {
@@ -47,7 +51,7 @@ struct AttnBwdSmem {
 // dQ kernel
 // --------------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnBwdParams p) {
+__global__ void __launch_bounds__(kAttnBwdThreads, 1) attn_bwd_dq_kernel(const __grid_constant__ AttnBwdParams p) {
   using S = AttnBwdSmem<D>;
   constexpr int kStages = S::kStages;
   constexpr int kDBoxes = D / 64;
@@ -101,7 +105,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
       mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1);
       mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 128); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], kAttnBwdSoftmaxThreads); }
     mbar_init(dq_done, 1);
     fence_barrier_init();
   }
@@ -195,6 +199,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
     }
   } else {
     const int quarter = warp & 3;
+    const int colhalf = (warp - 2) >> 2;                 // two warps per TMEM lane quarter split the columns
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const int q_pos = q0 + row;
@@ -216,9 +221,9 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
       const bool need_mask = !q_valid || (kbase + 63 > key_limit) || (kbase + 64 > k_len);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nl2 = make_float2(-lse2, -lse2), nd2 = make_float2(-delta, -delta);
-      uint32_t pk[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t pk[16];
+      {
+        const int c = colhalf;
         uint32_t sv[32], dv[32];
         tmem_ld32(tS + c * 32, sv);
         tmem_ld32(tDP + c * 32, dv);
@@ -237,10 +242,10 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
           const float2 pf = make_float2(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
           const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), nd2);
           const float2 r = __fmul2_rn(pf, dd);
-          pk[c * 16 + i] = pack_bf16(r.x, r.y);
+          pk[i] = pack_bf16(r.x, r.y);
         }
       }
-      tmem_st32(tS, pk);
+      tmem_st16(tS + colhalf * 16, pk);
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&ds_full[hf & 1]);
@@ -253,7 +258,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dq_kernel(const __grid_consta
       tc_fence_after_sync();
       __nv_bfloat16* orow = p.dq + static_cast<int64_t>(q_begin + q_pos) * p.dq_stride + static_cast<int64_t>(h) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = colhalf * (D / 64); c < (colhalf + 1) * (D / 64); ++c) {      // each warp of a quarter writes half of D
         uint32_t ov[32];
         if (n_kv > 0) {
           tmem_ld32(tmem_base + lane_off + kColDQ + c * 32, ov);

@@ -9,7 +9,7 @@
 namespace yv {
 
 template <int D>
-__global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnBwdParams p) {
+__global__ void __launch_bounds__(kAttnBwdThreads, 1) attn_bwd_dkv_kernel(const __grid_constant__ AttnBwdParams p) {
   using S = AttnBwdSmem<D>;
   constexpr int kStages = S::kStages;
   constexpr int kDBoxes = D / 64;
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       mbar_init(&q_full[s], 1); mbar_init(&do_full[s], 1);
       mbar_init(&q_empty[s], 1); mbar_init(&do_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], kAttnBwdSoftmaxThreads); }
     mbar_init(acc_done, 1);
     fence_barrier_init();
   }
@@ -169,9 +169,12 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       }
     }
   } else {
+    // Eight softmax warps: two warps share each TMEM lane quarter (a warp may only touch lanes 32 (warp % 4) ..) and
+    // split the 64 query columns of a half between them, 32 each.
     const int quarter = warp & 3;
+    const int colhalf = (warp - 2) >> 2;                 // which 32 of the 64 columns of a half this warp converts
     const int row = quarter * 32 + lane;                 // key row of the tile
-    const int tix = threadIdx.x - 64;                    // 0..127 among the softmax threads
+    const int tix = threadIdx.x - 64;                    // 0..255 among the softmax threads
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const int key = k0 + row;
     const bool key_valid = key < k_len;
@@ -184,13 +187,15 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       float* lse_b = s_lse + (it & 1) * 128;
       float* del_b = s_delta + (it & 1) * 128;
       if (half == 0) {
-        const int qpos = qb + tix;
-        const bool v = qpos < q_len;
-        const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
-        // stored negated so that the consumers fold them into packed fused multiply-adds
-        lse_b[tix] = v ? -p.lse[idx] * kLog2e : -INFINITY;   // -inf -> probability 0 for rows past the end
-        del_b[tix] = v ? -p.delta[idx] : 0.f;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tix < 128) {
+          const int qpos = qb + tix;
+          const bool v = qpos < q_len;
+          const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
+          // stored negated so that the consumers fold them into packed fused multiply-adds
+          lse_b[tix] = v ? -p.lse[idx] * kLog2e : -INFINITY;   // -inf -> probability 0 for rows past the end
+          del_b[tix] = v ? -p.delta[idx] : 0.f;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
       ok = mbar_wait(&sdp_full[hf & 1], (hf >> 1) & 1u, p.status);
       {
@@ -199,7 +204,7 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
             "{\n"
             ".reg .pred pin, pout;\n"
             "setp.ne.u32 pin, %1, 0;\n"
-            "bar.red.and.pred pout, 1, 128, pin;\n"
+            "bar.red.and.pred pout, 1, 256, pin;\n"
             "selp.u32 %0, 1, 0, pout;\n"
             "}\n"
             : "=r"(all_ok)
@@ -215,9 +220,9 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       // every (key, query) pair of this block is visible: no per-element selects (uniform over the CTA)
       const bool full_vis = (!p.causal || qb >= k0 + 127 - causal_shift) && (k0 + 127 < k_len);
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-      uint32_t pp[32], ds[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t pp[16], ds[16];
+      {
+        const int c = colhalf;
         uint32_t sv[32], dv[32];
         tmem_ld32(tST + c * 32, sv);
         tmem_ld32(tDPT + c * 32, dv);
@@ -236,15 +241,16 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
           }
           const __nv_bfloat162 e = h2exp2(__float22bfloat162_rn(x));
           const uint32_t bits = *reinterpret_cast<const uint32_t*>(&e);
-          pp[c * 16 + i2] = bits;
+          pp[i2] = bits;
           const float2 pf = make_float2(__uint_as_float(bits << 16), __uint_as_float(bits & 0xFFFF0000u));
           const float2 dd = __fadd2_rn(make_float2(__uint_as_float(dv[2 * i2]), __uint_as_float(dv[2 * i2 + 1])), nd);
           const float2 dsf = __fmul2_rn(pf, dd);
-          ds[c * 16 + i2] = pack_bf16(dsf.x, dsf.y);
+          ds[i2] = pack_bf16(dsf.x, dsf.y);
         }
       }
-      tmem_st32(tST, pp);
-      tmem_st32(tDPT, ds);
+      // 32 queries as bf16 = 16 packed columns, behind the 16 columns of the other warp of this lane quarter
+      tmem_st16(tST + colhalf * 16, pp);
+      tmem_st16(tDPT + colhalf * 16, ds);
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&pds_full[hf & 1]);
@@ -258,8 +264,8 @@ __global__ void __launch_bounds__(192, 1) attn_bwd_dkv_kernel(const __grid_const
       const int64_t tok = k_begin + key;
       __nv_bfloat16* dkrow = p.dk + tok * p.dk_stride + static_cast<int64_t>(hkv) * D;
       __nv_bfloat16* dvrow = p.dv + tok * p.dv_stride + static_cast<int64_t>(hkv) * D;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = colhalf;                         // one warp of the quarter writes dV, the other dK
         const uint32_t col = which == 0 ? kColDV : kColDK;
         const float sc = which == 0 ? 1.f : p.scale;
         __nv_bfloat16* orow = which == 0 ? dvrow : dkrow;

@@ -6,7 +6,8 @@ single-kernel path, one process per GPU.
 
 Times are CUDA-event times on the launching stream after warm-up, maximum over ranks; the L2 is flushed between
 iterations.  The roofline of a pair is the slower of FLOPs / measured bf16 peak and the bytes that must cross
-NVLink / 770 GB/s (measured peer-copy bandwidth per direction)."""
+NVLink / the peer-copy bandwidth per direction, which this program measures first on the same GPUs
+(``parallel.bench_nvlink.measure``; ``--nvlink-gbs`` overrides it)."""
 from __future__ import annotations
 
 import argparse
@@ -16,8 +17,6 @@ import os
 import torch
 import torch.distributed as dist
 
-NVLINK_GBS = 770.0
-
 
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -25,6 +24,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--out", type=int, default=6144, help="output features of the column-parallel layer (all ranks)")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--nvlink-gbs", type=float, default=0.0, help="link bandwidth for the roofline (0 = measure it now)")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
@@ -36,6 +36,11 @@ def main() -> None:
     from pisceslx_b200.parallel import tp as tpm
     K = kernels()
     group = dist.group.WORLD
+    probe = {}
+    if a.nvlink_gbs <= 0:
+        from pisceslx_b200.parallel.bench_nvlink import measure
+        probe = measure(group, 256, 5)
+    NVLINK_GBS = a.nvlink_gbs if a.nvlink_gbs > 0 else probe["peer_copy_gbs"]
     T, H, N = a.tokens, a.hidden, a.out
     rows, n_loc, k_loc = T // world, N // world, H // world
     torch.manual_seed(rank)
@@ -95,7 +100,8 @@ def main() -> None:
                           "rs_fused_frac_of_roofline": rs_roof / res["rs_fused_ms"],
                           "ag_speedup_vs_nccl": res["ag_nccl_ms"] / res["ag_fused_ms"],
                           "rs_speedup_vs_nccl": res["rs_nccl_ms"] / res["rs_fused_ms"],
-                          "max_abs_err_ag": err_ag, "rel_err_rs": err_rs, "peaks": pk["kind"]}))
+                          "max_abs_err_ag": err_ag, "rel_err_rs": err_rs, "peaks": pk["kind"],
+                          "nvlink_gbs_used": NVLINK_GBS, "nvlink_probe": probe}))
     dist.destroy_process_group()
 
 

@@ -58,9 +58,70 @@ def run(par, full_sd, fused: bool, steps: int, streaming: bool):
     return t.tolist()
 
 
+def determinism(par, iters: int = 100) -> dict:
+    """The flag / epoch protocols of the fused kernels, repeated: with the deterministic row order every repetition
+    must reproduce the first one bit for bit and leave the status word clear (a race between a peer's stores and the
+    consumer's loads, or a flag observed one epoch early, shows up as a differing or corrupted tile)."""
+    from pisceslx_b200.ops import moe as moe_ops
+    from pisceslx_b200.parallel import fused_tp as ft
+    dev = par.device
+    fz.set_enabled(True)
+    res = {}
+    torch.manual_seed(100 + par.rank)
+    if par.ep_size > 1:
+        T, H, E, F, k = 512, 512, 8, 256, 2
+        e_loc = E // par.ep_size
+        x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+        w13 = (torch.randn(e_loc, 2 * F, H, device=dev) * 0.05).bfloat16()
+        w2 = (torch.randn(e_loc, H, F, device=dev) * 0.05).bfloat16()
+        wts, idx, _, _ = moe_ops.gate_topk(torch.randn(T, E, device=dev), None, k)
+        first, mism = None, 0
+        for _ in range(iters):
+            y = fz.moe_experts_ep_fused(x, w13, w2, wts, idx, E, par.ep_group, deterministic=True)
+            if first is None:
+                first = y.clone()
+            elif not torch.equal(y, first):
+                mism += 1
+        res["ep_mismatches"] = mism
+        res["ep_finite"] = bool(torch.isfinite(first.float()).all())
+    if par.tp_size > 1:
+        rows, H, N = 256, 512, 1024
+        xs = torch.randn(rows, H, device=dev).bfloat16()
+        wc = (torch.randn(N // par.tp_size, H, device=dev) * 0.05).bfloat16()
+        xf = torch.randn(rows * par.tp_size, H // par.tp_size, device=dev).bfloat16()
+        wr = (torch.randn(H, H // par.tp_size, device=dev) * 0.05).bfloat16()
+        f_ag = f_rs = None
+        m_ag = m_rs = 0
+        for _ in range(iters):
+            a = ft.allgather_gemm(xs, wc, par.tp_group)[1]
+            b = ft.gemm_reduce_scatter(xf, wr, par.tp_group)
+            if f_ag is None:
+                f_ag, f_rs = a.clone(), b.clone()
+            else:
+                m_ag += int(not torch.equal(a, f_ag))
+                m_rs += int(not torch.equal(b, f_rs))
+        res["ag_mismatches"], res["rs_mismatches"] = m_ag, m_rs
+    torch.cuda.synchronize()
+    check_status()
+    res["iters"] = iters
+    t = torch.tensor([float(v) for k, v in sorted(res.items()) if k.endswith("mismatches")], device=dev)
+    if t.numel():
+        dist.all_reduce(t)                                   # any rank's mismatch counts
+        for (k, _), v in zip([(k, v) for k, v in sorted(res.items()) if k.endswith("mismatches")], t.tolist()):
+            res[k] = int(v)
+    return res
+
+
 def main() -> None:
     tp, ep, out_path = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
     par = init_parallel(tp=tp, ep=ep, timeout_s=120)
+    if os.environ.get("YV_MULTI_MODE") == "determinism":
+        res = determinism(par, int(os.environ.get("YV_MULTI_ITERS", "100")))
+        if par.rank == 0:
+            json.dump(res, open(out_path, "w"))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     torch.manual_seed(0)
     ref_model = build_model(small_cfg(), "cpu", torch.float32, seed=3)
     full_sd = ref_model.to_reference_state_dict()

@@ -21,11 +21,11 @@ def _free_port() -> int:
     return p
 
 
-def _launch(world: int, tp: int, ep: int, out: str) -> dict:
+def _launch(world: int, tp: int, ep: int, out: str, extra_env=None) -> dict:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "multi_gpu_worker.py"), str(tp), str(ep), out]
-    env = dict(os.environ, PYTHONPATH=ROOT)
+    env = dict(os.environ, PYTHONPATH=ROOT, **(extra_env or {}))
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
     return json.load(open(out))
@@ -62,3 +62,32 @@ def test_fused_matches_nccl_and_single(tmp_path, single, tp, ep):
         for a, b in zip(res[f"nccl_{mode}"], res[f"fused_{mode}"]):
             assert abs(a - b) < 1.5e-2 * max(1.0, abs(b))
         assert all(x == x and abs(x) < 1e4 for x in ref)
+
+
+@pytest.mark.parametrize("world,tp,ep", [(4, 1, 4), (4, 2, 2), (8, 2, 4)])
+def test_larger_layouts_fused_nccl_and_single_agree(tmp_path, single, world, tp, ep):
+    """The layouts of a four- and an eight-GPU node, the last one being the benchmark's (tp 2 x ep 4 x dp 4): fused
+    peer-memory collectives, NCCL collectives and the single-GPU run give the same losses."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    res = _launch(world, tp, ep, str(tmp_path / f"w{world}.json"))
+    for mode in ("plain", "stream"):
+        ref = single[mode]
+        for impl in ("nccl", "fused"):
+            for a, b in zip(res[f"{impl}_{mode}"], ref):
+                assert abs(a - b) < 1e-2 * max(1.0, abs(b)), (impl, mode, res[f"{impl}_{mode}"], ref)
+
+
+@pytest.mark.parametrize("tp,ep", [(1, 2), (2, 1)])
+def test_flag_protocols_repeat_bit_exact(tmp_path, tp, ep):
+    """One hundred repetitions of the fused expert-parallel layer (deterministic row order) and of the fused
+    tensor-parallel GEMM + collective pairs: every repetition equals the first bit for bit on every rank, and the
+    status word (bounded waits, bounds checks) stays clear."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = _launch(2, tp, ep, str(tmp_path / "det.json"), {"YV_MULTI_MODE": "determinism", "YV_MULTI_ITERS": "100"})
+    assert res["iters"] == 100
+    for k, v in res.items():
+        if k.endswith("mismatches"):
+            assert v == 0, res
+    assert res.get("ep_finite", True)
