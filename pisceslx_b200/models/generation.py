@@ -137,37 +137,58 @@ class YvSamplerFactory:
 # --------------------------------------------------------------------------------------------------
 # cached generation
 # --------------------------------------------------------------------------------------------------
+def _tp_size(model) -> int:
+    par = getattr(model, "parallel", None)
+    return par.tp_size if par is not None else 1
+
+
 def _prefill(model, ids: torch.Tensor, cache: YvPagedKVCache, seq_ids: List[int]) -> torch.Tensor:
-    """Run the prompt(s) [B, S] through the model, filling the cache; returns last-token logits [B, V]."""
+    """Run the prompt(s) [B, S] through the model, filling the cache; returns last-token logits [B, V].
+
+    Under tensor parallelism the token rows are sharded over the ranks between the layers (sequence parallel), so the
+    row count must divide by the group size: the prompts are padded at the END with tokens that are not cached
+    (slot -1); causal attention keeps them out of every real token's context."""
     B, S = ids.shape
     trunk = model.model
-    ctx = trunk.build_context(B, S, ids.device)
+    pad = (-S) % _tp_size(model)
+    if pad:
+        ids = torch.cat([ids, ids.new_zeros(B, pad)], dim=1)
+    ctx = trunk.build_context(B, S + pad, ids.device)
     slots: List[int] = []
     for s in seq_ids:
-        slots += cache.append_slots(s, S)
+        slots += cache.append_slots(s, S) + [-1] * pad
     ctx.cache = cache
     ctx.slot_map = torch.tensor(slots, dtype=torch.int32).to(ids.device)
     out = model(input_ids=ids, ctx=ctx, return_logits=False, return_hidden=True)
-    return model.logits(out["hidden_states"][:, -1, :])
+    return model.logits(out["hidden_states"][:, S - 1, :])
 
 
 def _decode_step(model, tokens: torch.Tensor, cache: YvPagedKVCache, seq_ids: List[int]) -> torch.Tensor:
-    """One token per sequence: tokens [B] -> logits [B, V]."""
+    """One token per sequence: tokens [B] -> logits [B, V].  Under tensor parallelism the batch is padded to a
+    multiple of the group size with rows that read one (arbitrary) cached token and store nothing."""
     trunk = model.model
     dev = tokens.device
     slots = [cache.append_slots(s, 1)[0] for s in seq_ids]
     lens = cache.seq_lens_tensor(seq_ids)
     B = tokens.shape[0]
+    pad = (-B) % _tp_size(model)
+    table = cache.block_table_tensor(seq_ids)
+    if pad:
+        tokens = torch.cat([tokens, tokens.new_zeros(pad)])
+        slots = slots + [-1] * pad
+        lens = torch.cat([lens, lens.new_ones(pad)])
+        table = torch.cat([table, table.new_zeros(pad, table.shape[1])], dim=0)
+    Bp = B + pad
     pos = (lens - 1).int()
     cos = sin = None
     if trunk.rotary is not None:
         cos, sin = trunk.rotary.tables(max(cache.lengths[s] for s in seq_ids), dev)
-    ctx = AttnContext(positions=pos, cu_seqlens=torch.arange(B + 1, dtype=torch.int32, device=dev), max_len=1,
+    ctx = AttnContext(positions=pos, cu_seqlens=torch.arange(Bp + 1, dtype=torch.int32, device=dev), max_len=1,
                       cos=cos, sin=sin, causal=True, cache=cache,
                       slot_map=torch.tensor(slots, dtype=torch.int32).to(dev),
-                      block_table=cache.block_table_tensor(seq_ids), seq_lens=lens, decode=True)
-    out = model(input_ids=tokens.view(B, 1), ctx=ctx, return_logits=False, return_hidden=True)
-    return model.logits(out["hidden_states"][:, -1, :])
+                      block_table=table, seq_lens=lens, decode=True)
+    out = model(input_ids=tokens.view(Bp, 1), ctx=ctx, return_logits=False, return_hidden=True)
+    return model.logits(out["hidden_states"][:B, -1, :])
 
 
 @torch.no_grad()

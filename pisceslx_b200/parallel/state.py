@@ -85,8 +85,14 @@ def default_nccl_env() -> None:
 
 
 def init_parallel(tp: int = 1, ep: int = 1, pp: int = 1, backend: Optional[str] = None,
-                  timeout_s: float = 600.0, device: Optional[torch.device] = None, cp: int = 1) -> YvParallelState:
-    """Create (or reuse) the default process group from the torchrun environment and build the mesh."""
+                  timeout_s: float = 600.0, device: Optional[torch.device] = None, cp: int = 1,
+                  ep_over_tp: bool = False) -> YvParallelState:
+    """Create (or reuse) the default process group from the torchrun environment and build the mesh.
+
+    ``ep_over_tp`` is the serving layout "tensor-parallel attention with expert-parallel experts on the same GPUs"
+    (TP 8 x EP 8 on one node): the expert-parallel group IS the tensor-parallel group - attention shards heads over it,
+    the sequence-parallel token shards between attention and the MoE layer are what the experts' all-to-all
+    dispatches, and every GPU holds 1 / tp of the routed experts instead of a replica of all of them."""
     global _STATE
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -113,6 +119,8 @@ def init_parallel(tp: int = 1, ep: int = 1, pp: int = 1, backend: Optional[str] 
                                 timeout=datetime.timedelta(seconds=timeout_s), **kw)
     assert world % (tp * pp) == 0, f"world {world} not divisible by tp*pp = {tp * pp}"
     dp = world // (tp * pp)
+    if ep_over_tp:
+        ep = 1                                             # the mesh below is built without a separate ep dimension
     assert dp % ep == 0, f"dp {dp} not divisible by ep {ep}"
     st.tp_size, st.pp_size, st.dp_size, st.ep_size, st.edp_size = tp, pp, dp, ep, dp // ep
     st.tp_rank = rank % tp
@@ -142,6 +150,9 @@ def init_parallel(tp: int = 1, ep: int = 1, pp: int = 1, backend: Optional[str] 
     st.expert_grad_group = make([[r(p, e0 * ep + e, t) for e0 in range(dp // ep) for t in range(tp)]
                                  for p in range(pp) for e in range(ep)])
     st.stage_group = make([[r(p, d, t) for d in range(dp) for t in range(tp)] for p in range(pp)])
+    if ep_over_tp and tp > 1:
+        st.ep_size, st.ep_rank, st.ep_group = tp, st.tp_rank, st.tp_group
+        st.edp_size, st.edp_rank = dp, st.dp_rank
     # Context parallelism is carved out of the data-parallel dimension: cp consecutive dp ranks hold consecutive
     # chunks of the SAME sequences.  Gradients are still reduced over the whole dp group (different tokens).
     assert dp % cp == 0, f"dp {dp} not divisible by cp {cp}"
