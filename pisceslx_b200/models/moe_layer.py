@@ -114,7 +114,8 @@ class YvDeepSeekMoELayer(nn.Module):
         if self.ep_size > 1:
             from ..parallel import ep
             routed = ep.moe_experts_ep(x, self.experts_w13, self.experts_w2, weights, idx, self.num_experts,
-                                       self.ep_group, fused=self.cfg.fused_comm, deterministic=self.deterministic)
+                                       self.ep_group, fused=self.cfg.fused_comm, deterministic=self.deterministic,
+                                       counts=counts)
         else:
             routed = moe_ops.moe_experts(x, self.experts_w13, self.experts_w2, weights, idx, counts,
                                          self.deterministic)

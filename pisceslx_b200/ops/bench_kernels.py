@@ -15,7 +15,7 @@ import argparse
 import json
 import math
 import os
-from typing import Any, Callable, Dict
+from typing import Any, Callable, Dict, List
 
 import torch
 
@@ -221,9 +221,130 @@ def bench_newton_schulz(a: argparse.Namespace) -> Dict[str, Any]:
                             "apply": 2.0 * G * s * s * l / t_apply / 1e9}}
 
 
+def _bw(name: str, shape, ms: float, nbytes: float) -> Dict[str, Any]:
+    gbs = nbytes / ms / 1e6
+    return {"kernel": name, "shape": list(shape), "ms": ms, "gbs": gbs, "frac_of_peak": gbs / peaks()["hbm_gbs"]}
+
+
+def bench_moe(a: argparse.Namespace) -> List[Dict[str, Any]]:
+    """The routed-expert path at the benchmark's layer shape for one micro-batch: gate, plan, permute, grouped GEMMs
+    (up: [rows, H] x [E, 2F, H]; down: [rows, F] x [E, H, F]; weight gradient over expert segments), SwiGLU forward and
+    the row-wise backward, combine and its backward, un-permute."""
+    from . import moe as moe_ops
+    K, st = kernels(), status_word(torch.device("cuda"))
+    T, H, E, F, k = a.m, a.n, 64, 1408, 6
+    dev = "cuda"
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+    logits = torch.randn(T, E, device=dev)
+    w = torch.empty(T, k, device=dev)
+    idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+    probs = torch.empty(T, E, device=dev)
+    counts = torch.zeros(E, dtype=torch.int32, device=dev)
+
+    def gate():
+        counts.zero_()
+        K.gate_topk(logits, None, w, idx, probs, counts, True, 0)
+    out = [_bw("gate_topk", (T, E), timeit(gate, a.iters), T * E * 8 + T * k * 8)]
+    xp, plan = moe_ops.permute_tokens(x, idx, counts, E, False, True)
+    rows = plan.max_rows
+    cursor = torch.empty(E, dtype=torch.int32, device=dev)
+
+    def permute():
+        K.moe_plan(counts, plan.seg_offsets, plan.tile_expert, plan.num_m_tiles, cursor)
+        K.moe_permute(x, idx, cursor, plan.row_map, xp)
+    out.append(_bw("moe_plan + moe_permute", (T, H, k), timeit(permute, a.iters), (T + T * k) * H * 2))
+    w13 = (torch.randn(E, 2 * F, H, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(E, H, F, device=dev) * 0.02).bfloat16()
+    y1 = torch.empty(rows, 2 * F, dtype=torch.bfloat16, device=dev)
+    act = torch.empty(rows, F, dtype=torch.bfloat16, device=dev)
+    y2 = torch.empty(rows, H, dtype=torch.bfloat16, device=dev)
+    real = T * k
+    for name, fn, fl in (
+            ("gemm_grouped_m up [rows,H]x[E,2F,H]", lambda: K.gemm_grouped_m(xp, w13, y1, plan.tile_expert, plan.num_m_tiles, False, 0, st), 2.0 * real * H * 2 * F),
+            ("gemm_grouped_m down [rows,F]x[E,H,F]", lambda: K.gemm_grouped_m(act, w2, y2, plan.tile_expert, plan.num_m_tiles, False, 0, st), 2.0 * real * H * F),
+            ("gemm_grouped_m dX [rows,H]x[E,H,F]^T", lambda: K.gemm_grouped_m(y2, w2, act, plan.tile_expert, plan.num_m_tiles, True, 0, st), 2.0 * real * H * F)):
+        ms = timeit(fn, a.iters)
+        out.append({"kernel": name, "shape": [rows, H, F], "ms": ms, "tflops": fl / ms / 1e9,
+                    "frac_of_peak": fl / ms / 1e9 / peaks()["bf16_tflops"]})
+    dw13 = torch.empty_like(w13)
+    ms = timeit(lambda: K.gemm_grouped_k(y1, xp, dw13, plan.seg_offsets, False, 0, st), a.iters)
+    fl = 2.0 * real * H * 2 * F
+    out.append({"kernel": "gemm_grouped_k dW [2F,rows_e]x[rows_e,H]", "shape": [E, 2 * F, H], "ms": ms,
+                "tflops": fl / ms / 1e9, "frac_of_peak": fl / ms / 1e9 / peaks()["bf16_tflops"]})
+    out.append(_bw("swiglu_fwd", (rows, F), timeit(lambda: K.swiglu_fwd(y1, act), a.iters), rows * F * 6))
+    row_w = torch.rand(rows, device=dev)
+    dy1, actw, rowdot = torch.empty_like(y1), torch.empty_like(act), torch.empty(rows, device=dev)
+    out.append(_bw("swiglu_bwd_rows", (rows, F), timeit(lambda: K.swiglu_bwd_rows(y1, act, row_w, dy1, actw, rowdot), a.iters),
+                   rows * F * 2 * (2 + 1 + 2 + 1)))
+    o = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    out.append(_bw("moe_combine", (T, H, k), timeit(lambda: K.moe_combine(y2, plan.row_map, w, None, o), a.iters),
+                   (T * k + T) * H * 2))
+    dx = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    out.append(_bw("moe_unpermute_sum", (T, H, k), timeit(lambda: K.moe_unpermute_sum(y2, plan.row_map, dx, k), a.iters),
+                   (T * k + T) * H * 2))
+    return out
+
+
+def bench_streaming(a: argparse.Namespace) -> List[Dict[str, Any]]:
+    """Bandwidth-bound kernels at model shapes: quantised momentum fold, AdamW, cross-entropy over a logits chunk, RoPE,
+    RMSNorm backward, patch extraction."""
+    K = kernels()
+    dev = "cuda"
+    out = []
+    n = 64 * 2816 * 4096                                                      # one layer's expert up-projections
+    q = torch.zeros(n, dtype=torch.int8, device=dev)
+    sc = torch.ones(n // 128, device=dev)
+    g = (torch.randn(n, device=dev) * 0.01).bfloat16()
+    out.append(_bw("momentum_q8 (fold into int8 momentum)", (64, 2816, 4096),
+                   timeit(lambda: K.momentum_fold_q8(q, sc, g, 0.95, 1.0 / 32, False, 7), a.iters), n * 4.0 + n / 32))
+    mt = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    out.append(_bw("dequant_q8", (64, 2816, 4096), timeit(lambda: K.dequant_q8(q, sc, mt), a.iters), n * 3.0))
+    na = 154856 * 4096
+    p, ga = torch.randn(na, device=dev).bfloat16(), torch.randn(na, device=dev).bfloat16()
+    m1, v1 = torch.zeros_like(p), torch.zeros_like(p)
+    out.append(_bw("adamw (bf16 p, g, m, v)", (154856, 4096),
+                   timeit(lambda: K.adamw(p, ga, m1, v1, 1e-3, 0.9, 0.95, 1e-8, 0.1, 3, 1.0), a.iters), na * 2.0 * 7))
+    Tc, V = 2048, 154856
+    logits = torch.randn(Tc, V, device=dev)
+    labels = torch.randint(0, V, (Tc,), device=dev)
+    loss = torch.zeros(1, device=dev)
+    dl = torch.empty(Tc, V, dtype=torch.bfloat16, device=dev)
+    out.append(_bw("ce_fwd_bwd (fp32 logits chunk -> loss + bf16 dlogits)", (Tc, V),
+                   timeit(lambda: K.ce_fwd_bwd(logits, labels, loss, dl, -100, 1.0), a.iters), Tc * V * 6.0))
+    T, hq, hk, d = 8192, 32, 8, 128
+    qk = torch.randn(T, (hq + 2 * hk) * d, device=dev).bfloat16()
+    from . import reference as ref
+    cos, sin = ref.rope_tables(4096, d, 1e4, 1.0, device=dev)
+    pos = (torch.arange(T, device=dev) % 4096).int()
+    qv, kv = qk[:, : hq * d], qk[:, hq * d:(hq + hk) * d]
+    out.append(_bw("rope (q and k in place)", (T, hq + hk, d),
+                   timeit(lambda: K.rope(qv, kv, cos, sin, pos, hq, hk, d, d, False), a.iters), T * (hq + hk) * d * 4.0))
+    x = torch.randn(32768, 4096, device=dev).bfloat16()
+    dy, dx = torch.randn_like(x), torch.empty_like(x)
+    w = torch.ones(4096, device=dev).bfloat16()
+    y, rstd = torch.empty_like(x), torch.empty(32768, device=dev)
+    K.rmsnorm_fwd(x, None, w, None, None, 1, y, None, rstd, 1e-6)
+    from .functional import _NORM_BWD_BLOCKS
+    dwp = torch.empty(_NORM_BWD_BLOCKS, 4096, device=dev)
+    dwo = torch.empty(4096, device=dev)
+    try:
+        out.append(_bw("rmsnorm_bwd", (32768, 4096),
+                       timeit(lambda: K.rmsnorm_bwd(dy, x, w, rstd, None, dx, dwp, dwo, False), a.iters), 32768 * 4096 * 6.0))
+    except Exception as e:                                                    # workspace shape differs between builds
+        out.append({"kernel": "rmsnorm_bwd", "skipped": str(e)[:120]})
+    img = torch.randn(4, 3, 1022, 1022, device=dev).bfloat16()
+    patches = torch.empty(4 * 73 * 73, 640, dtype=torch.bfloat16, device=dev)       # 588 padded to a multiple of 64
+    try:
+        out.append(_bw("patchify 14x14", (4, 3, 1022, 1022), timeit(lambda: K.patchify(img, patches, 14, None, None), a.iters),
+                       img.numel() * 4.0))
+    except Exception as e:
+        out.append({"kernel": "patchify", "skipped": str(e)[:120]})
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs", "muon_fold"])
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs", "muon_fold", "moe", "streaming"])
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -258,8 +379,10 @@ def main() -> None:
         fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
               "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz, "gemm_fp8": bench_gemm_fp8,
               "ssm": bench_ssm, "gemm_tp_ag": lambda x: bench_gemm_tp(x, 1),
-              "gemm_tp_rs": lambda x: bench_gemm_tp(x, 2), "muon_fold": bench_muon_fold}[a.kernel]
-        res.append(fn(a))
+              "gemm_tp_rs": lambda x: bench_gemm_tp(x, 2), "muon_fold": bench_muon_fold, "moe": bench_moe,
+              "streaming": bench_streaming}[a.kernel]
+        r = fn(a)
+        res.extend(r if isinstance(r, list) else [r])
     out = {"peaks": peaks(), "results": res}
     print(json.dumps(out, indent=1))
     if a.json:

@@ -90,10 +90,38 @@ __global__ void ep_put_counts_kernel(const int* __restrict__ seg_offsets, PeerPt
 
 // counts_all [world][e_local] (rows sent by each source per local expert; multiples of 128).
 // Source s's rows live at rows [s*cap, s*cap + sum_e counts_all[s][e]).  Emits one flat tile list.
+//   source-major (expert_major = 0): tiles ordered (source, expert); seg_src [world][e_local + 1] = row offsets of the
+//     expert segments inside each source's block.
+//   expert-major (expert_major = 1): tiles ordered (expert, source), so that a COMPACT buffer holding the listed tiles
+//     back to back has every expert's rows contiguous; seg_src [e_local + 1] = offsets of the experts in that buffer.
 __global__ void ep_recv_plan_kernel(const int* __restrict__ counts_all, int world, int e_local, int cap_rows,
                                     int* __restrict__ tile_rows, int* __restrict__ tile_expert,
-                                    int* __restrict__ num_tiles, int* __restrict__ seg_src, int max_tiles) {
+                                    int* __restrict__ num_tiles, int* __restrict__ seg_src, int max_tiles,
+                                    int expert_major) {
   __shared__ int s_base[kMaxRanks + 1];
+  if (expert_major) {
+    // one thread walks the (expert, source) grid: e_local * world <= a few hundred entries
+    if (threadIdx.x == 0) {
+      int t = 0;
+      for (int e = 0; e < e_local; ++e) {
+        seg_src[e] = t * 128;
+        for (int s = 0; s < world; ++s) {
+          int row = 0;                                        // offset of expert e inside source s's block
+          for (int e2 = 0; e2 < e; ++e2) row += counts_all[s * e_local + e2];
+          const int n = counts_all[s * e_local + e] / 128;
+          for (int i = 0; i < n; ++i, ++t) {
+            if (t < max_tiles) {
+              tile_rows[t] = (s * cap_rows + row) / 128 + i;
+              tile_expert[t] = e;
+            }
+          }
+        }
+      }
+      seg_src[e_local] = (t < max_tiles ? t : max_tiles) * 128;
+      *num_tiles = t < max_tiles ? t : max_tiles;
+    }
+    return;
+  }
   if (threadIdx.x == 0) {
     int t = 0;
     for (int s = 0; s < world; ++s) {
@@ -122,6 +150,18 @@ __global__ void ep_recv_plan_kernel(const int* __restrict__ counts_all, int worl
     }
     if (threadIdx.x == 0) seg_src[s * (e_local + 1) + e_local] = row;
   }
+}
+
+// dst tile j = src tile tile_rows[j] (128 rows of `cols` bf16 each); one CTA per tile, 16-byte copies.
+__global__ void tile_gather_kernel(const uint4* __restrict__ src, const int* __restrict__ tile_rows, uint4* __restrict__ dst,
+                                   int vec_per_tile, int src_tiles, uint32_t* status) {
+  const int j = blockIdx.x;
+  const int t = tile_rows[j];
+  const bool ok = t >= 0 && t < src_tiles;
+  if (!ok && status != nullptr && threadIdx.x == 0) atomicOr(status, kStatusIndexOutOfRange);
+  const uint4* s = src + static_cast<int64_t>(ok ? t : 0) * vec_per_tile;
+  uint4* d = dst + static_cast<int64_t>(j) * vec_per_tile;
+  for (int i = threadIdx.x; i < vec_per_tile; i += blockDim.x) d[i] = ok ? s[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // Encoded destination of assignment (t, j): g = dest_rank * region + my_rank * cap + row_in_my_block,

@@ -77,6 +77,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   p.num_groups = a.num_groups;
   p.tile_expert = a.tile_expert;
   p.tile_rows = a.tile_rows;
+  p.tile_rows_c_only = (a.tile_rows != nullptr && a.tile_rows_c_only) ? 1 : 0;
   p.num_m_tiles = a.num_m_tiles;
   p.seg_offsets = a.seg_offsets;
   p.status = a.status;
@@ -100,7 +101,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     p.b_group_stride = a.b_mn ? a.K : a.N;
     b_outer = groups * static_cast<uint64_t>(p.b_group_stride);
     if (a.b_mn && (a.K % kBK) != 0) return -14;   // a K tile must not run into the next expert's rows
-    c_outer = a.rows_total;
+    c_outer = a.c_rows_total > 0 ? static_cast<uint64_t>(a.c_rows_total) : a.rows_total;
   } else if (a.mode == kGroupedK) {
     if (!a.a_mn || !a.b_mn || a.seg_offsets == nullptr) return -15;
     if (a.M % kBM != 0) return -16;               // C tiles must not cross expert boundaries

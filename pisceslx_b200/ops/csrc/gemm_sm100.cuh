@@ -36,6 +36,7 @@ struct GemmParams {
   int a_group_stride;          // kBatched: outer-dim rows of A per batch entry
   const int* tile_expert;      // kGroupedM: expert id of every 128-row tile
   const int* tile_rows;        // kGroupedM (optional): index of the 128-row tile in A / C for every listed tile
+  int tile_rows_c_only;        // 1: the list addresses C only, A is compact (listed tile j = rows 128 j .. of A)
   const int* num_m_tiles;      // kGroupedM: number of valid 128-row tiles (device scalar)
   const int* seg_offsets;      // kGroupedK: [E+1] row offsets of the expert segments (multiples of 128)
   uint32_t* status;            // device status word (0 = ok)
@@ -134,6 +135,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
   // grouped-M problems may list their 128-row tiles explicitly (receive regions of several sources)
   const int row_tile = (p.mode == kGroupedM && p.tile_rows != nullptr) ? p.tile_rows[m_blk] : m_blk;
   const int m0 = row_tile * kBM, n0 = n_blk * BN;
+  const int m0_a = (p.mode == kGroupedM && p.tile_rows_c_only) ? m_blk * kBM : m0;
   int k_begin = 0, k_len = p.K;
   int a_outer_off = 0, b_outer_off = 0, c_row_off = 0;
   if (p.mode == kBatched) {
@@ -150,7 +152,7 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
   }
   constexpr int kBKe = FP8 ? 2 * kBK : kBK;          // elements of K per pipeline stage (128 bytes per row)
   t.k_iters = (k_len + kBKe - 1) / kBKe;
-  if (A_MN) { t.a_x = m0; t.a_y = a_outer_off + k_begin; } else { t.a_x = k_begin; t.a_y = a_outer_off + m0; }
+  if (A_MN) { t.a_x = m0_a; t.a_y = a_outer_off + k_begin; } else { t.a_x = k_begin; t.a_y = a_outer_off + m0_a; }
   if (B_MN) { t.b_x = n0; t.b_y = b_outer_off + k_begin; } else { t.b_x = k_begin; t.b_y = b_outer_off + n0; }
   t.c_x = n0;
   t.c_y = c_row_off + m0;

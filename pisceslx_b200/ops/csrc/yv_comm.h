@@ -21,7 +21,7 @@ int launch_peer_barrier(void* const* flag_ptrs, int my_rank, int world, uint32_t
 int launch_ep_put_counts(const int* seg_offsets, void* const* table_ptrs, void* const* flag_ptrs, int my_rank,
                          int world, int e_local, uint32_t epoch, uint32_t* status, cudaStream_t stream);
 int launch_ep_recv_plan(const int* counts_all, int world, int e_local, int cap_rows, int* tile_rows, int* tile_expert,
-                        int* num_tiles, int* seg_src, int max_tiles, cudaStream_t stream);
+                        int* num_tiles, int* seg_src, int max_tiles, int expert_major, cudaStream_t stream);
 int launch_ep_dispatch(const void* x, const int* idx, int* cursor, const int* seg_offsets, int64_t* row_map,
                        void* const* recv_ptrs, int my_rank, int e_local, int cap_rows, int world, int64_t tokens, int k,
                        int cols, uint32_t* status, cudaStream_t stream);
@@ -50,6 +50,10 @@ struct ZeroFoldArgs {
   float* sumsq = nullptr;       // optional: += squared norm of the reduced, scaled gradient (fp32 scalar)
 };
 int launch_zero_reduce_fold(const ZeroFoldArgs& a, cudaStream_t stream);
+// dst tile j (rows 128 j ..) = src tile tile_rows[j]; tiles whose index is outside [0, src_tiles) are zero-filled and
+// reported through the status word
+int launch_tile_gather(const void* src, const int* tile_rows, int n_tiles, void* dst, int cols, int src_tiles,
+                       uint32_t* status, cudaStream_t stream);
 int launch_peer_copy(void* dst, const void* src, int64_t bytes, cudaStream_t stream);
 // table shards: rank r owns rows [r*rows_per_rank, (r+1)*rows_per_rank) of every codebook: layout [C, rows_per_rank, D]
 int launch_pq_gather_sum_peer(void* const* table_ptrs, const int* idx, void* out, int64_t tokens, int C,

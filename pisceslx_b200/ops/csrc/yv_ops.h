@@ -25,6 +25,8 @@ struct GemmArgs {
   int64_t rows_total = 0;      // grouped modes: rows of the expert-sorted, padded row dimension
   const int* tile_expert = nullptr;
   const int* tile_rows = nullptr;   // grouped-M only: explicit row-tile index per listed tile (optional)
+  bool tile_rows_c_only = false;    // the list addresses C only; A is compact (tile j = rows 128 j ..)
+  int64_t c_rows_total = 0;         // rows of C when they differ from A's (0 = rows_total)
   const int* num_m_tiles = nullptr;
   const int* seg_offsets = nullptr;
   uint32_t* status = nullptr;

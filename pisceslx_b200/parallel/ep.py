@@ -191,7 +191,7 @@ def _moe_experts_ep_reference(x, w13, w2, weights, idx, num_experts, group):
 
 def moe_experts_ep(x: torch.Tensor, w13_local: torch.Tensor, w2_local: torch.Tensor, weights: torch.Tensor,
                    idx: torch.Tensor, num_experts: int, group: Any, fused: bool = True,
-                   deterministic: bool = False) -> torch.Tensor:
+                   deterministic: bool = False, counts: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Routed experts with the experts sharded over ``group``; same result as ``ops.moe.moe_experts`` on the
     unsharded weights.  x [T,H] local tokens; idx holds global expert ids."""
     if not x.is_cuda:
@@ -199,12 +199,15 @@ def moe_experts_ep(x: torch.Tensor, w13_local: torch.Tensor, w2_local: torch.Ten
     if fused:
         from . import fused as fz
         if fz.enabled():
-            return fz.moe_experts_ep_fused(x, w13_local, w2_local, weights, idx, num_experts, group, deterministic)
+            return fz.moe_experts_ep_fused(x, w13_local, w2_local, weights, idx, num_experts, group, deterministic,
+                                           counts)
     ep = dist.get_world_size(group)
     e_local = num_experts // ep
     dev = x.device
     idx = idx.int()
-    counts = torch.bincount(idx.flatten().long(), minlength=num_experts).int()
+    if counts is None:
+        counts = torch.bincount(idx.flatten().long(), minlength=num_experts)
+    counts = counts.int()
     xp, seg, _te, _nt, row_map = _PermuteFn.apply(x.to(_BF16), idx, counts, num_experts, deterministic)
     padded = (seg[1:] - seg[:-1]).contiguous()                          # padded rows per global expert
     recv_counts = _exchange_counts(padded, ep, group)                   # [ep(src), e_local]

@@ -158,8 +158,18 @@ def _ep_context(group: Any, cap_rows: int, hidden: int, e_local: int) -> _EPCont
 
 
 class _MoEExpertsEPFused(torch.autograd.Function):
+    """Expert-parallel routed experts over peer memory.
+
+    Receive regions are sized for the worst case (every token of every source routed to this rank), but only the tiles
+    that really arrived are computed and stored: the receive plan lists them expert-major, the tile count is read once
+    on the host, and everything behind the receive region (up-projection output, activation, gradients) lives in
+    COMPACT buffers of ``n_tiles * 128`` rows in which each local expert's rows are contiguous.  So the stored
+    activations are those of the tokens this rank serves (about T * k rows when routing is balanced) instead of
+    ``world`` times the bound, the element-wise kernels touch real rows only, and each weight gradient is ONE
+    grouped-K GEMM over the compact buffers instead of one accumulating GEMM per source."""
+
     @staticmethod
-    def forward(ctx, x, w13, w2, weights, idx, num_experts, group, deterministic):
+    def forward(ctx, x, w13, w2, weights, idx, num_experts, group, deterministic, counts=None):
         from ..ops import moe as moe_ops
         K = kernels()
         dev = x.device
@@ -174,7 +184,9 @@ class _MoEExpertsEPFused(torch.autograd.Function):
         rank = heap.rank
         x = x.contiguous()
         idx = idx.int().contiguous()
-        counts = torch.bincount(idx.flatten().long(), minlength=num_experts).int()
+        if counts is None:
+            counts = torch.bincount(idx.flatten().long(), minlength=num_experts)
+        counts = counts.int()
         seg = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
         te_unused = torch.empty(moe_ops.padded_rows_bound(T * k, num_experts) // 128, dtype=torch.int32, device=dev)
         nt_unused = torch.empty(1, dtype=torch.int32, device=dev)
@@ -182,20 +194,29 @@ class _MoEExpertsEPFused(torch.autograd.Function):
         K.moe_plan(counts, seg, te_unused, nt_unused, cursor)
         # 1. publish my per-expert padded row counts to the owners (ends with a barrier)
         K.ep_put_counts(seg, c.table.ptrs, heap.flags.ptrs, rank, e_local, heap.next_epoch(), st)
-        K.ep_recv_plan(c.table_t, world, e_local, cap, c.tile_rows, c.tile_expert, c.num_tiles, c.seg_src)
+        K.ep_recv_plan(c.table_t, world, e_local, cap, c.tile_rows, c.tile_expert, c.num_tiles, c.seg_src, True)
         # 2. dispatch: the permutation writes into the owners' receive regions
         row_map = torch.empty(T, k, dtype=torch.int64, device=dev)
         K.ep_dispatch(x, idx, cursor, seg, row_map, c.x_recv.ptrs, rank, e_local, cap, st)
         K.ep_zero_pad(seg, counts, c.x_recv.ptrs, rank, e_local, cap, H)
         heap.barrier()
-        # 3. local experts on everything that arrived
+        # 3. local experts on the tiles that arrived, in compact buffers (one host read of the tile count)
+        n_tiles = int(c.num_tiles.item())
+        rows = n_tiles * 128
         F = w13.shape[1] // 2
-        rows = c.region_rows
+        tile_rows = c.tile_rows[:n_tiles].clone()
+        tile_expert = c.tile_expert[:max(n_tiles, 1)].clone()
+        num_tiles = c.num_tiles.clone()
+        seg_c = c.seg_src[:e_local + 1].clone()
+        xc = torch.empty(rows, H, dtype=_BF16, device=dev)
+        K.tile_gather(c.x_recv_t, tile_rows, n_tiles, xc)
         y1 = torch.empty(rows, 2 * F, dtype=_BF16, device=dev)
-        K.gemm_grouped_m_rows(c.x_recv_t, w13, y1, c.tile_rows, c.tile_expert, c.num_tiles, False, 0, st)
         act = torch.empty(rows, F, dtype=_BF16, device=dev)
-        K.swiglu_fwd(y1, act)
-        K.gemm_grouped_m_rows(act, w2, c.y_out_t, c.tile_rows, c.tile_expert, c.num_tiles, False, 0, st)
+        if n_tiles > 0:
+            K.gemm_grouped_m(xc, w13, y1, tile_expert, num_tiles, False, 0, st)
+            K.swiglu_fwd(y1, act)
+            # down projection: compact activation rows in, receive-region rows out (peers read them there)
+            K.gemm_grouped_m_rows(act, w2, c.y_out_t, tile_rows, tile_expert, num_tiles, False, 0, st, True)
         heap.barrier()
         # 4. combine: load my tokens' results from the owners
         out = torch.empty(T, H, dtype=_BF16, device=dev)
@@ -203,9 +224,8 @@ class _MoEExpertsEPFused(torch.autograd.Function):
         K.ep_combine(c.y_out.ptrs, row_map, wts, out, c.region_rows)
         need_grad = any(ctx.needs_input_grad[:4])
         if need_grad:
-            ctx.save_for_backward(c.x_recv_t.clone(), y1, act, w13, w2, wts, row_map, seg, counts,
-                                  c.tile_rows.clone(), c.tile_expert.clone(), c.num_tiles.clone(), c.seg_src.clone())
-        ctx.c, ctx.dims, ctx.w_dtype = c, (T, H, k, F, world, e_local, cap), weights.dtype
+            ctx.save_for_backward(xc, y1, act, w13, w2, wts, row_map, seg, counts, tile_rows, tile_expert, num_tiles, seg_c)
+        ctx.c, ctx.dims, ctx.w_dtype = c, (T, H, k, F, world, e_local, cap, n_tiles), weights.dtype
         return out
 
     @staticmethod
@@ -213,8 +233,8 @@ class _MoEExpertsEPFused(torch.autograd.Function):
         K = kernels()
         c = ctx.c
         heap = c.heap
-        (xr, y1, act, w13, w2, wts, row_map, seg, counts, tile_rows, tile_expert, num_tiles, seg_src) = ctx.saved_tensors
-        T, H, k, F, world, e_local, cap = ctx.dims
+        (xc, y1, act, w13, w2, wts, row_map, seg, counts, tile_rows, tile_expert, num_tiles, seg_c) = ctx.saved_tensors
+        T, H, k, F, world, e_local, cap, n_tiles = ctx.dims
         dev = dout.device
         st = status_word(dev)
         rank = heap.rank
@@ -224,31 +244,32 @@ class _MoEExpertsEPFused(torch.autograd.Function):
         K.ep_combine_bwd(dout, c.y_out.ptrs, c.dy_recv.ptrs, row_map, wts, dwts, c.region_rows)
         K.ep_zero_pad(seg, counts, c.dy_recv.ptrs, rank, e_local, cap, H)
         heap.barrier()
-        rows = c.region_rows
-        dact = torch.empty(rows, F, dtype=_BF16, device=dev)
-        K.gemm_grouped_m_rows(c.dy_recv_t, w2, dact, tile_rows, tile_expert, num_tiles, True, 0, st)
-        dw2 = torch.zeros_like(w2)
-        dw13 = torch.zeros_like(w13)
-        segs = seg_src.view(world, e_local + 1)
-        for s in range(world):
-            blk = slice(s * cap, (s + 1) * cap)
-            K.gemm_grouped_k(c.dy_recv_t[blk], act[blk], dw2, segs[s], True, 0, st)
-        dy1 = torch.empty_like(y1)
-        K.swiglu_bwd(y1, dact, dy1)
-        del dact
-        # the input gradient rows overwrite dy_recv (already consumed) so that peers can read them
-        K.gemm_grouped_m_rows(dy1, w13, c.dy_recv_t, tile_rows, tile_expert, num_tiles, True, 0, st)
-        for s in range(world):
-            blk = slice(s * cap, (s + 1) * cap)
-            K.gemm_grouped_k(dy1[blk], xr[blk], dw13, segs[s], True, 0, st)
+        rows = n_tiles * 128
+        dw2 = torch.zeros_like(w2) if n_tiles == 0 else torch.empty_like(w2)
+        dw13 = torch.zeros_like(w13) if n_tiles == 0 else torch.empty_like(w13)
+        if n_tiles > 0:
+            dyc = torch.empty(rows, H, dtype=_BF16, device=dev)
+            K.tile_gather(c.dy_recv_t, tile_rows, n_tiles, dyc)
+            dact = torch.empty(rows, F, dtype=_BF16, device=dev)
+            K.gemm_grouped_m(dyc, w2, dact, tile_expert, num_tiles, True, 0, st)
+            K.gemm_grouped_k(dyc, act, dw2, seg_c, False, 0, st)             # every expert's rows are contiguous
+            del dyc
+            dy1 = torch.empty_like(y1)
+            K.swiglu_bwd(y1, dact, dy1)
+            del dact
+            # the input-gradient rows go back into the receive region (already consumed) so that peers can read them
+            K.gemm_grouped_m_rows(dy1, w13, c.dy_recv_t, tile_rows, tile_expert, num_tiles, True, 0, st, True)
+            K.gemm_grouped_k(dy1, xc, dw13, seg_c, False, 0, st)
         heap.barrier()
         dx = torch.empty(T, H, dtype=_BF16, device=dev)
         K.ep_unpermute_sum(c.dy_recv.ptrs, row_map, dx, k, c.region_rows)
-        return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None, None
+        return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None, None, None
 
 
-def moe_experts_ep_fused(x, w13_local, w2_local, weights, idx, num_experts, group, deterministic=False):
-    return _MoEExpertsEPFused.apply(x.to(_BF16), w13_local, w2_local, weights, idx, num_experts, group, deterministic)
+def moe_experts_ep_fused(x, w13_local, w2_local, weights, idx, num_experts, group, deterministic=False, counts=None):
+    """``counts`` [E] int32: the expert histogram the gate kernel produced (recomputed when omitted)."""
+    return _MoEExpertsEPFused.apply(x.to(_BF16), w13_local, w2_local, weights, idx, num_experts, group, deterministic,
+                                    counts)
 
 
 # --------------------------------------------------------------------------------------------------
