@@ -2,26 +2,33 @@
 
 The reference (utils/dc.py:67-89) hard-imports ``dmsc==0.1.8``, which is not installable offline.  This module
 lives OUTSIDE the unmodified copy of the reference and is put on ``sys.path`` by the reference arm of
-``bench.py`` only; it provides the imported names with inert behaviour (loggers that print warnings and errors to
-stderr, metrics that count in memory) so that the reference's own training code runs unchanged.  Nothing of the
+``bench.py`` only; it provides the imported names with inert behaviour (loggers that print warnings, errors and, when
+``YV_STANDIN_INFO=1``, info lines to stderr with the seconds since start; metrics that count in memory) so that the reference's own training code runs unchanged.  Nothing of the
 framework itself imports it.
 """
 from __future__ import annotations
 
+import os
 import sys
+import time
 import types
+
+_T0 = time.time()
+_INFO = os.environ.get("YV_STANDIN_INFO", "0") == "1"
 
 
 class _Logger:
     def _emit(self, level, *a, **k):
-        if level in ("WARN", "ERROR"):
+        if level in ("WARN", "ERROR") or (level == "INFO" and _INFO):
             try:
-                sys.stderr.write(f"[dmsc-standin {level}] " + " ".join(str(x) for x in a) + (f" {k}" if k else "") + "\n")
+                sys.stderr.write(f"[dmsc-standin {level} +{time.time() - _T0:.0f}s] " + " ".join(str(x) for x in a) +
+                                 (f" {k}" if k else "") + "\n")
+                sys.stderr.flush()
             except Exception:
                 pass
 
     def info(self, *a, **k):
-        pass
+        self._emit("INFO", *a, **k)
 
     def debug(self, *a, **k):
         pass

@@ -44,7 +44,7 @@ def parse_args():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--state-dtype", default="int8", choices=["int8", "bf16"],
                     help="Muon momentum storage: int8 block-quantised (stochastic rounding) or bf16")
-    ap.add_argument("--ref-limit", type=int, default=1000, help="seconds given to the reference's full-size attempt")
+    ap.add_argument("--ref-limit", type=int, default=420, help="seconds given to the reference's full-size attempt")
     ap.add_argument("--no-ref-context", action="store_true", help="skip the reduced-layer context run of the reference")
     return ap.parse_args()
 
@@ -57,6 +57,7 @@ def _run_reference_child(extra, out_path, limit_s, port_shift=0):
     if port_shift and env.get("MASTER_PORT"):
         env["MASTER_PORT"] = str(int(env["MASTER_PORT"]) + port_shift)
     env.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    env.setdefault("YV_STANDIN_INFO", "1")                   # the reference's own info log lines go to the child's log
     cmd = [sys.executable, os.path.join(ROOT, "baseline", "run_reference.py"), "--out", out_path] + extra
     log = open(out_path + ".log", "w")
     proc = subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT, env=env, cwd=ROOT)
@@ -65,7 +66,8 @@ def _run_reference_child(extra, out_path, limit_s, port_shift=0):
     except subprocess.TimeoutExpired:
         proc.kill()                                          # the exact child this rank started
         proc.wait()
-        return f"stock reference path did not finish within {limit_s} s (killed)"
+        return (f"stock reference path did not finish within {limit_s} s (killed); its own log says: "
+                + _reference_log_digest(out_path + ".log"))
     finally:
         log.close()
     try:
@@ -78,6 +80,18 @@ def _run_reference_child(extra, out_path, limit_s, port_shift=0):
         except OSError:
             pass
         return f"stock reference path exited with code {proc.returncode} and no result: {tail}"
+
+
+def _reference_log_digest(path: str) -> str:
+    """The reference's parameter-count line and its last log line, from the child's captured output."""
+    try:
+        lines = [l.strip() for l in open(path, errors="replace").read().splitlines() if l.strip()]
+    except OSError:
+        return "(no log)"
+    keep = [l for l in lines if "total parameters" in l][:1]
+    if lines and (not keep or lines[-1] != keep[0]):
+        keep.append(lines[-1])
+    return " | ".join(l[:300] for l in keep) or "(empty log)"
 
 
 def reference_arm(args) -> None:

@@ -230,6 +230,7 @@ class YvConfig:
     sequence_parallel: bool = True
     zero_stage: int = 1
     fused_comm: bool = True                 # peer-memory fused kernels (False = NCCL baseline mode)
+    expert_fp8: Optional[str] = None        # "mx": routed experts' forward products in block-scaled e4m3 (single GPU path)
     # ---- anything else found in a config file -----------------------------------------------------------------
     extra: Dict[str, Any] = field(default_factory=dict)
 

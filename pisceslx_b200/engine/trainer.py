@@ -141,7 +141,7 @@ class YvTrainer:
 
     def train_step(self, batch: Dict[str, torch.Tensor]) -> Dict[str, Any]:
         """One optimizer step over ``batch`` (host or device tensors: input_ids [B,S], labels [B,S], optional
-        attention_mask).  Returns the step result; ``loss`` is read back from the device."""
+        attention_mask; ``images`` [B, n, 3, H, W], ``video`` and ``audio`` reach the model's modality encoders).  Returns the step result; ``loss`` is read back from the device."""
         cfg = self.cfg
         if self.elastic_guard is not None:                # peers' liveness + last step's device status, host only
             self.elastic_guard.before_step()
@@ -183,8 +183,9 @@ class YvTrainer:
                 self.optimizer.begin_micro_batch(ci, n_micro)
             if self.dp is not None:
                 self.dp.begin_micro_batch(ci, n_micro)
+            modal = {k: mb[k] for k in ("images", "video", "audio") if k in mb}      # multimodal batches
             out = self.model(input_ids=mb["input_ids"], labels=lab, attention_mask=mb.get("attention_mask"),
-                             num_valid=num_valid)
+                             num_valid=num_valid, **modal)
             loss = out["loss"]
             (loss if self.streaming else loss / n_micro).backward()
             total_loss = loss.detach() if total_loss is None else total_loss + loss.detach()

@@ -107,9 +107,16 @@ class YvModel(nn.Module):
         aux_total = h.new_zeros((), dtype=torch.float32)
         if film_source is not None:
             film_source.begin(h, batch)
+        fused_film = film_source.apply_fused if h.is_cuda and getattr(film_source, "fused_ok", False) else None
         for blk in self.layers:
-            film = film_source.film_params(blk.layer_idx, h if delta is None else h + delta) \
-                if film_source is not None else None
+            film = None
+            if fused_film is not None:
+                # gather + projection + modulation in one kernel: the block then sees an already modulated stream
+                if film_source.wants(blk.layer_idx):
+                    h = fused_film(h if delta is None else h + delta)
+                    delta = None
+            elif film_source is not None:
+                film = film_source.film_params(blk.layer_idx, h if delta is None else h + delta)
             h, delta, aux = blk(h, delta, ctx, film)
             if torch.is_grad_enabled():          # serving never reads the auxiliary loss: no add kernel per layer
                 aux_total = aux_total + aux.float()

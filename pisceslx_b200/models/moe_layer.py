@@ -118,7 +118,7 @@ class YvDeepSeekMoELayer(nn.Module):
                                        counts=counts)
         else:
             routed = moe_ops.moe_experts(x, self.experts_w13, self.experts_w2, weights, idx, counts,
-                                         self.deterministic)
+                                         self.deterministic, fp8=getattr(self.cfg, "expert_fp8", None))
         out = routed
         if self.num_shared:
             sh = self._shared(x)

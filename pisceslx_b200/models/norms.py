@@ -58,7 +58,9 @@ class YvLayerNorm(nn.LayerNorm):
     """LayerNorm used by the vision / audio encoders (library op: not on the text hot path)."""
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
-        return super().forward(x.float()).to(x.dtype)
+        w = self.weight.float() if self.weight is not None else None
+        b = self.bias.float() if self.bias is not None else None
+        return torch.nn.functional.layer_norm(x.float(), self.normalized_shape, w, b, self.eps).to(x.dtype)
 
 
 class YvRotaryEmbedding(nn.Module):

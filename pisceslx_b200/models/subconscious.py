@@ -117,8 +117,12 @@ class _PQGather(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         (idx,) = ctx.saved_tensors
-        field = ctx.field
-        C, N, D = ctx.table_shape
+        return _PQGather.table_grad(ctx.field, dout, idx, ctx.table_shape), None, None
+
+    @staticmethod
+    def table_grad(field, dout, idx, table_shape):
+        """Gradient of the (local shard of the) table from the gradient of the summed entries."""
+        C, N, D = table_shape
         if field.shard_buf is not None:
             # each rank keeps the gradient rows of its own shard: ids outside the shard are dropped locally and
             # the token gradients of all ranks are exchanged first
@@ -132,7 +136,40 @@ class _PQGather(torch.autograd.Function):
             idx = torch.where((idx >= lo) & (idx < lo + field.rows_per_rank), idx - lo, torch.full_like(idx, -1))
         dt = torch.zeros(C, N, D, dtype=torch.float32, device=dout.device)
         kernels().pq_scatter_grad(dout.contiguous(), idx.contiguous(), dt)
-        return dt.to(torch.bfloat16), None, None
+        return dt.to(torch.bfloat16)
+
+
+class _PQFilmFused(torch.autograd.Function):
+    """``h * (1 + s) + b`` with ``(s | b) = (sum of the tokens' field entries) @ film_proj^T`` as ONE kernel (peer loads of
+    the entries, tensor-core projection, modulation of the h tile in shared memory).  Backward with the saved summed
+    entries ``e`` [T, 128]: the projection is recomputed, the table gradient scatters ``de`` like the plain lookup."""
+
+    @staticmethod
+    def forward(ctx, h, table, w, idx, field):
+        from ..ops import status_word
+        T, H = h.shape
+        out = torch.empty_like(h)
+        e = torch.empty(T, field.D, dtype=torch.bfloat16, device=h.device) if torch.is_grad_enabled() or h.requires_grad \
+            else None
+        kernels().pq_film(field.table_ptrs(), idx, w, h, out, e, field.C, field.rows_per_rank, status_word(h.device))
+        ctx.field, ctx.table_shape = field, table.shape
+        if e is not None:
+            ctx.save_for_backward(h, w, idx, e)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        h, w, idx, e = ctx.saved_tensors
+        field = ctx.field
+        H = h.shape[1]
+        dout = dout.contiguous()
+        s = F_.gemm(e, w[:H])                                               # [T, H] scale, recomputed
+        dh = dout * (1 + s)
+        ds = dout * h
+        de = F_.gemm(ds, w[:H], b_mn=True) + F_.gemm(dout, w[H:], b_mn=True)  # [T, 128]
+        dw = torch.cat([F_.gemm(ds, e, a_mn=True, b_mn=True), F_.gemm(dout, e, a_mn=True, b_mn=True)])
+        dtable = _PQGather.table_grad(field, de, idx, ctx.table_shape)
+        return dh, dtable, dw, None, None
 
 
 class YvPQKnowledgeField(nn.Module):
@@ -186,6 +223,30 @@ class YvPQKnowledgeField(nn.Module):
         stride = self.N // self.nav_cells
         fine = (torch.arange(T, device=hidden.device, dtype=torch.int32) % stride).unsqueeze(1)
         return (cell * stride + fine).int()
+
+    def table_ptrs(self) -> torch.Tensor:
+        """Device pointers of every rank's shard (own rank included), as the kernels take them."""
+        if self.shard_buf is not None:
+            return self.shard_buf.ptrs
+        ptr = self.codebook.data_ptr()
+        if getattr(self, "_ptrs", None) is None or int(self._ptrs[0]) != ptr:
+            self._ptrs = torch.tensor([ptr], dtype=torch.int64)
+        return self._ptrs
+
+    @property
+    def fused_ok(self) -> bool:
+        """The one-kernel path covers the shapes the field is specified with: 128-dim entries, at most 16 codebooks."""
+        return (self.D == 128 and self.C <= 16 and self.cfg.hidden_size % 64 == 0 and self.codebook.is_cuda
+                and self.codebook.dtype == torch.bfloat16 and self.film_proj.dtype == torch.bfloat16)
+
+    def wants(self, layer_idx: int) -> bool:
+        return layer_idx % self.interval == 0
+
+    def apply_fused(self, hidden: torch.Tensor) -> torch.Tensor:
+        """The modulated residual stream [T, H] (CUDA, bf16, entry dimension 128): navigation, then one kernel for
+        gather + sum + projection + ``h * (1 + scale) + shift``."""
+        idx = self.navigate(hidden.detach())
+        return _PQFilmFused.apply(hidden.contiguous(), self.codebook, self.film_proj, idx.contiguous(), self)
 
     def lookup(self, idx: torch.Tensor) -> torch.Tensor:
         if idx.is_cuda:

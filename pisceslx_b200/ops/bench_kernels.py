@@ -149,6 +149,25 @@ def bench_gemm_fp8(a: argparse.Namespace) -> Dict[str, Any]:
             "frac_of_bf16_peak": tf / peaks()["bf16_tflops"]}
 
 
+def bench_gemm_mx(a: argparse.Namespace) -> Dict[str, Any]:
+    """Block-scaled e4m3 GEMM (tcgen05 kind::mxf8f6f4.block_scale, one e8m0 scale per 32 elements of K, applied by the
+    tensor cores); also times the quantise kernel that produces the operands.  The fraction is of the bf16 peak."""
+    from ..quant import fp8 as q8
+    K, st = kernels(), status_word(torch.device("cuda"))
+    M, N, Kd = a.m, a.n, a.k
+    X = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16)
+    W = torch.randn(N, Kd, device="cuda", dtype=torch.bfloat16)
+    xq, xs = q8.quantize_mx(X)
+    wq, ws = q8.quantize_mx(W)
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: K.gemm_mxfp8(xq, xs, wq, ws, C, None, None, a.bn, st), a.iters)
+    ms_q = timeit(lambda: K.mx_quantize(X, xq, xs), a.iters)
+    tf = 2.0 * M * N * Kd / ms / 1e9
+    return {"kernel": "gemm_sm100_mxfp8", "shape": [M, N, Kd], "bn": a.bn, "ms": ms, "tflops": tf,
+            "frac_of_bf16_peak": tf / peaks()["bf16_tflops"], "quantize_ms": ms_q,
+            "quantize_gbs": X.numel() * 3.03 / ms_q / 1e6, "status": int(st[0].item())}
+
+
 def bench_ssm(a: argparse.Namespace) -> Dict[str, Any]:
     """Selective scan forward (batch x seq x d_inner = --batch x --seq x --n, 16 states), bytes = u, delta, y."""
     K = kernels()
@@ -344,7 +363,7 @@ def bench_streaming(a: argparse.Namespace) -> List[Dict[str, Any]]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs", "muon_fold", "moe", "streaming"])
+    ap.add_argument("--kernel", default="gemm", choices=["gemm", "gemm_fp8", "gemm_mx", "attn_fwd", "attn_bwd", "rmsnorm", "decode", "ns", "ssm", "gemm_tp_ag", "gemm_tp_rs", "muon_fold", "moe", "streaming"])
     ap.add_argument("--all", action="store_true")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -378,7 +397,7 @@ def main() -> None:
     else:
         fn = {"gemm": bench_gemm, "attn_fwd": lambda x: bench_attn(x, False), "attn_bwd": lambda x: bench_attn(x, True),
               "rmsnorm": bench_rmsnorm, "decode": bench_decode, "ns": bench_newton_schulz, "gemm_fp8": bench_gemm_fp8,
-              "ssm": bench_ssm, "gemm_tp_ag": lambda x: bench_gemm_tp(x, 1),
+              "gemm_mx": bench_gemm_mx, "ssm": bench_ssm, "gemm_tp_ag": lambda x: bench_gemm_tp(x, 1),
               "gemm_tp_rs": lambda x: bench_gemm_tp(x, 2), "muon_fold": bench_muon_fold, "moe": bench_moe,
               "streaming": bench_streaming}[a.kernel]
         r = fn(a)

@@ -19,7 +19,7 @@ CSRC = HERE / "csrc"
 OBJ = HERE / "build"
 SO = HERE / "_yv_ops.so"
 
-CUDA_SOURCES = ["gemm.cu", "elementwise.cu", "moe.cu", "loss_optim.cu", "attention.cu", "comm.cu", "noalloc.cu", "ssm.cu"]
+CUDA_SOURCES = ["gemm.cu", "elementwise.cu", "moe.cu", "loss_optim.cu", "attention.cu", "comm.cu", "noalloc.cu", "ssm.cu", "pq_film.cu"]
 CPP_SOURCES = ["binding.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-diag-suppress", "550"]

@@ -353,6 +353,59 @@ void gemm_fp8(const Tensor& a, const Tensor& b, Tensor c, const Tensor& out_scal
   check_rc(yv::launch_gemm(g, cur_stream()), "gemm_fp8");
 }
 
+// x [rows, K] bf16 -> q [rows, K] e4m3 + sf uint8 [ceil(rows/128), K/128, 512] (one e8m0 scale per 32 elements)
+void mx_quantize(const Tensor& x, Tensor q, Tensor sf) {
+  check_bf16(x, "x"); check_fp8(q, "q");
+  TORCH_CHECK(sf.is_cuda() && sf.scalar_type() == at::kByte && sf.is_contiguous(), "mx_quantize: sf must be CUDA uint8");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && q.is_contiguous() && q.numel() == x.numel(), "mx_quantize: x [rows,K]");
+  const int64_t rows = x.size(0), K = x.size(1);
+  TORCH_CHECK(K % 128 == 0, "mx_quantize: K must be a multiple of 128");
+  TORCH_CHECK(sf.numel() == (rows + 127) / 128 * (K / 128) * 512, "mx_quantize: sf has the wrong size");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check_rc(yv::launch_mx_quantize(x.data_ptr(), q.data_ptr(), sf.data_ptr(), rows, static_cast<int>(K), cur_stream()),
+           "mx_quantize");
+}
+
+// c (bf16) = A B^T with block-scaled e4m3 operands (scales sfa / sfb in the chunk layout of mx_quantize).
+//   dense:   a [M,K], b [N,K], c [M,N]
+//   grouped: a [rows,K] (128-row tiles, tile i multiplies expert tile_expert[i]), b [E,N,K], c [rows,N]
+void gemm_mxfp8(const Tensor& a, const Tensor& sfa, const Tensor& b, const Tensor& sfb, Tensor c,
+                const c10::optional<Tensor>& tile_expert, const c10::optional<Tensor>& num_m_tiles, int64_t bn,
+                const c10::optional<Tensor>& status) {
+  check_fp8(a, "a"); check_fp8(b, "b"); check_bf16(c, "c");
+  TORCH_CHECK(sfa.is_cuda() && sfa.scalar_type() == at::kByte && sfb.is_cuda() && sfb.scalar_type() == at::kByte &&
+              sfa.is_contiguous() && sfb.is_contiguous(), "gemm_mxfp8: scale tensors must be CUDA uint8");
+  TORCH_CHECK(a.dim() == 2 && a.is_contiguous() && b.is_contiguous() && c.is_contiguous() && c.dim() == 2,
+              "gemm_mxfp8: contiguous operands expected");
+  const bool grouped = tile_expert.has_value();
+  TORCH_CHECK(b.dim() == (grouped ? 3 : 2), "gemm_mxfp8: b is [N,K], or [E,N,K] with tile_expert");
+  const int64_t K = a.size(1), N = grouped ? b.size(1) : b.size(0), brows = grouped ? b.size(0) * b.size(1) : b.size(0);
+  TORCH_CHECK(b.size(-1) == K && K % 128 == 0, "gemm_mxfp8: K mismatch or not a multiple of 128");
+  TORCH_CHECK(c.size(0) == a.size(0) && c.size(1) == N, "gemm_mxfp8: output shape mismatch");
+  TORCH_CHECK(sfa.numel() == (a.size(0) + 127) / 128 * (K / 128) * 512 && sfb.numel() == (brows + 127) / 128 * (K / 128) * 512,
+              "gemm_mxfp8: scale tensor size mismatch");
+  TORCH_CHECK(brows % 128 == 0 && (!grouped || N % 128 == 0), "gemm_mxfp8: rows of b must come in multiples of 128");
+  const c10::cuda::CUDAGuard guard(a.device());
+  yv::GemmArgs g;
+  g.a = a.data_ptr(); g.b = b.data_ptr(); g.c = c.data_ptr();
+  g.sfa = sfa.data_ptr(); g.sfb = sfb.data_ptr();
+  g.M = static_cast<int>(a.size(0)); g.K = static_cast<int>(K); g.N = static_cast<int>(N);
+  g.fp8 = true;
+  if (grouped) {
+    TORCH_CHECK(num_m_tiles.has_value(), "gemm_mxfp8: grouped mode needs num_m_tiles");
+    check_i32(*tile_expert, "tile_expert"); check_i32(*num_m_tiles, "num_m_tiles");
+    TORCH_CHECK(a.size(0) % 128 == 0 && tile_expert->numel() * 128 >= a.size(0), "gemm_mxfp8: grouped rows / tile list");
+    g.mode = 1;
+    g.num_groups = static_cast<int>(b.size(0));
+    g.rows_total = a.size(0);
+    g.tile_expert = tile_expert->data_ptr<int>();
+    g.num_m_tiles = num_m_tiles->data_ptr<int>();
+  }
+  g.bn = static_cast<int>(bn);
+  g.status = statusp(status);
+  check_rc(yv::launch_gemm(g, cur_stream()), "gemm_mxfp8");
+}
+
 void ssm_scan_fwd(const Tensor& u, const Tensor& delta, const Tensor& A, const Tensor& Bm, const Tensor& Cm,
                   const Tensor& Dp, Tensor y, const c10::optional<Tensor>& hs, const c10::optional<Tensor>& h_last) {
   check_f32(u, "u"); check_f32(delta, "delta"); check_f32(A, "A"); check_f32(Bm, "B"); check_f32(Cm, "C");

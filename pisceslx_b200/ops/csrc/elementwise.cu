@@ -579,7 +579,67 @@ __global__ void fp8_quantize_kernel(const uint4* __restrict__ x, const float* __
     if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(mx));   // mx >= 0
   }
 }
+
+// Block-scaled (MX) quantisation: four lanes share one 32-element block (8 elements each).
+__global__ void mx_quantize_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, uint8_t* __restrict__ sf,
+                                   int64_t n8, int K) {
+  const int kchunks = K >> 7;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;           // a multiple of 32
+  const int64_t n8_up = (n8 + 31) & ~static_cast<int64_t>(31);                    // whole warps take the shuffles
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8_up; i += stride) {
+    const bool in = i < n8;
+    const uint4 v = in ? x[i] : make_uint4(0u, 0u, 0u, 0u);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = __bfloat1622float2(h[k]);
+      f[2 * k] = a.x; f[2 * k + 1] = a.y;
+    }
+    float mx = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) mx = fmaxf(mx, fabsf(f[k]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+    // smallest power-of-two scale that brings the block's largest magnitude to at most 448 = 1.75 * 2^8:
+    // amax = m * 2^x with 1 <= m < 2 gives exponent x - 8, one more when m > 1.75.  Stored as a biased exponent byte,
+    // 127 (= 1.0) for an all-zero block.
+    const uint32_t mbits = __float_as_uint(mx);
+    int eb = static_cast<int>((mbits >> 23) & 0xFFu) - 8 + ((mbits & 0x7FFFFFu) > 0x600000u ? 1 : 0);
+    if (!(mx > 0.f)) eb = 127;
+    eb = eb < 0 ? 0 : (eb > 253 ? 253 : eb);
+    const float inv = __uint_as_float(static_cast<uint32_t>(254 - eb) << 23);
+    if (!in) continue;
+    uint32_t out[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      uint16_t lo, hi;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f[4 * k + 1] * inv), "f"(f[4 * k] * inv));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f[4 * k + 3] * inv), "f"(f[4 * k + 2] * inv));
+      out[k] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+    }
+    q[i] = make_uint2(out[0], out[1]);
+    if ((threadIdx.x & 3) == 0) {
+      const int64_t e0 = i << 3;
+      const int64_t row = e0 / K;
+      const int col = static_cast<int>(e0 - row * K);
+      const int r = static_cast<int>(row & 127);
+      sf[((row >> 7) * kchunks + (col >> 7)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + ((col & 127) >> 5)] =
+          static_cast<uint8_t>(eb);
+    }
+  }
+}
 }  // namespace
+
+int launch_mx_quantize(const void* x_bf16, void* q_e4m3, void* sf, int64_t rows, int K, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (K <= 0 || (K & 127) != 0) return -1;
+  const int64_t n8 = rows * K / 8;
+  mx_quantize_kernel<<<grid_for(n8, 256), 256, 0, stream>>>(reinterpret_cast<const uint4*>(x_bf16),
+                                                            reinterpret_cast<uint2*>(q_e4m3),
+                                                            reinterpret_cast<uint8_t*>(sf), n8, K);
+  return static_cast<int>(cudaGetLastError());
+}
 
 int launch_fp8_quantize(const void* x_bf16, const float* scale, void* q_e4m3, float* amax, int64_t n,
                         cudaStream_t stream) {

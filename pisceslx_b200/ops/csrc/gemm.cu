@@ -21,16 +21,16 @@ int sm_count() {
   return g_sm_count;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, bool FP8 = false>
+template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, int FP8 = 0>
 int launch_instance(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, OutT, COMM, FP8>;
   static PerDeviceInt configured;
   if (!configured.cur()) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, FP8 == 2>::kTotal);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured.cur() = 1;
   }
-  kern<<<grid, COMM == 1 ? kGemmThreadsAllGather : kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(p);
+  kern<<<grid, COMM == 1 ? kGemmThreadsAllGather : kGemmThreads, GemmSmem<BN, FP8 == 2>::kTotal, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -147,9 +147,18 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
         (reinterpret_cast<uintptr_t>(a.epi_cin) & 15u) != 0)
       return -80;
   }
-  if (a.fp8) {
+  const bool mx = a.sfa != nullptr || a.sfb != nullptr;
+  p.sfa = static_cast<const uint8_t*>(a.sfa); p.sfb = static_cast<const uint8_t*>(a.sfb);
+  p.sf_kchunks = a.K / 128; p.sf_b_tiles = static_cast<int>(b_outer / kBM);
+  if (mx) {
+    if (a.sfa == nullptr || a.sfb == nullptr || (a.K % 128) != 0 || (b_outer % kBM) != 0) return -71;
+    if (a.mode != kDense && a.mode != kGroupedM) return -72;
+    if (a.mode == kGroupedM && (a.tile_rows != nullptr || (a.N % kBM) != 0)) return -73;
+    if ((reinterpret_cast<uintptr_t>(a.sfa) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a.sfb) & 15u) != 0) return -74;
+  }
+  if (a.fp8 || mx) {
     // e4m3 operands: one byte per element, 128 elements per 128-byte row of a stage
-    if (a.mode != kDense || a.a_mn || a.b_mn || a.out_fp32 || a.accumulate || a.comm != 0) return -70;
+    if ((a.mode != kDense && !mx) || a.a_mn || a.b_mn || a.out_fp32 || a.accumulate || a.comm != 0) return -70;
     r = make_tmap_2d(&p.tma_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.a, a_inner, a_outer, lda, 128, kBM);
     if (r != 0) return -20 + r;
     r = make_tmap_2d(&p.tma_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.b, b_inner, b_outer, ldb, 128,
@@ -205,9 +214,13 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   const int cap = a.max_ctas > 0 ? a.max_ctas : sm_count();
   const int grid = static_cast<int>(tiles < cap ? tiles : cap);
 
+  if (mx) {
+    return bn == 256 ? launch_instance<256, false, false, __nv_bfloat16, 0, 2>(p, grid, stream)
+                     : launch_instance<128, false, false, __nv_bfloat16, 0, 2>(p, grid, stream);
+  }
   if (a.fp8) {
-    return bn == 256 ? launch_instance<256, false, false, __nv_bfloat16, 0, true>(p, grid, stream)
-                     : launch_instance<128, false, false, __nv_bfloat16, 0, true>(p, grid, stream);
+    return bn == 256 ? launch_instance<256, false, false, __nv_bfloat16, 0, 1>(p, grid, stream)
+                     : launch_instance<128, false, false, __nv_bfloat16, 0, 1>(p, grid, stream);
   }
   if (a.comm == 1) {
     cudaError_t e = cudaMemsetAsync(a.comm_flags, 0, sizeof(uint32_t) * static_cast<size_t>(tiles_m), stream);

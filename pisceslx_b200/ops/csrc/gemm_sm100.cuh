@@ -56,6 +56,14 @@ struct GemmParams {
   // ---- fp8 inputs (template parameter FP8): e4m3 operands, K-major, 128 elements per shared-memory row; the
   // epilogue multiplies the fp32 accumulator by *out_scale (= scale_a * scale_b of per-tensor scaling) ----
   const float* out_scale;
+  // ---- block-scaled fp8 (template parameter FP8 == 2, "MX"): one e8m0 scale per 32 elements of K of every row of A
+  // and of B.  Scales are stored in 512-byte chunks, one per (128 rows, 128 elements of K): byte
+  // (r % 32) * 16 + (r / 32) * 4 + j holds row r, 32-element block j; chunk (row tile i, K chunk c) sits at
+  // (i * sf_kchunks + c) * 512.  sf_b_tiles = 128-row tiles of B that have scales ----
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int sf_kchunks;
+  int sf_b_tiles;
   // ---- affine epilogue (bf16 output, no fused collective): C = epi_c * (A B) + epi_b * epi_cin + epi_a * I, with
   // epi_cin laid out like C; the identity is per group in the batched mode ----
   const __nv_bfloat16* epi_cin;
@@ -74,16 +82,17 @@ constexpr int kCopierWarps = 4;              // warps per CTA that pull the peer
 constexpr int kGemmThreadsAllGather = kGemmThreads + 32 * kCopierWarps;
 constexpr int kGroupBand = 16;   // m-tiles per rasterisation band
 
-template <int BN>
+template <int BN, bool MX = false>
 struct GemmSmem {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = ((BN == 256) ? 4 : 6) - (MX ? 1 : 0);
+  static constexpr int kSfBytes = MX ? 512 * (1 + BN / 128) : 0;     // scale factors of one stage: A, then B
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kEpiBytes = kBM * 128;            // 128 rows x 128 B per staging buffer
   static constexpr int kEpiBufs = 2;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kEpiBufs * kEpiBytes + kBarrierBytes + 1024;
+  static constexpr int kTotal = kStages * (kStageBytes + kSfBytes) + kEpiBufs * kEpiBytes + kBarrierBytes + 1024;
 };
 
 struct TileCoord {
@@ -95,7 +104,7 @@ struct TileCoord {
 };
 
 // Decode linear tile index -> coordinates.  Returns false when idx is past the end.
-template <int BN, bool A_MN, bool B_MN, int COMM = 0, bool FP8 = false>
+template <int BN, bool A_MN, bool B_MN, int COMM = 0, int FP8 = 0>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int tiles_m, int tiles_n, TileCoord& t) {
   int m_blk, n_blk, group = 0;
   if (p.mode == kBatched && p.symmetric) {
@@ -160,21 +169,29 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int idx, int ti
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, bool FP8 = false>
+template <int BN, bool A_MN, bool B_MN, typename OutT, int COMM = 0, int FP8 = 0>
 __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using S = GemmSmem<BN>;
+  constexpr bool MX = (FP8 == 2);
+  using S = GemmSmem<BN, MX>;
   constexpr int kStages = S::kStages;
   constexpr int kColsPerChunk = 128 / sizeof(OutT);       // columns covered by one 128-byte staging row
   constexpr int kChunks = BN / kColsPerChunk;
-  constexpr uint32_t kTmemCols = (2 * BN <= 512) ? 2 * BN : 512;
+  // block-scaled mode keeps the scale factors in tensor memory behind the accumulators: 4 columns for A's 128 rows
+  // and 4 per 128 columns of B; with 256-wide tiles that leaves room for one accumulator instead of two
+  constexpr int kAccBufs = (MX && BN == 256) ? 1 : 2;
+  constexpr uint32_t kTmemCols = MX ? 512 : ((2 * BN <= 512) ? 2 * BN : 512);
+  constexpr uint32_t kSfaCol = kAccBufs * BN;
+  constexpr uint32_t kSfbCol = kSfaCol + 4;
   static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
   constexpr int kBKe = FP8 ? 2 * kBK : kBK;
-  constexpr uint32_t kIdesc = FP8 ? make_idesc_e4m3(kBM, BN) : make_idesc_bf16(kBM, BN, A_MN, B_MN);
+  constexpr uint32_t kIdesc = MX ? make_idesc_mxf8(kBM, BN)
+                                 : (FP8 ? make_idesc_e4m3(kBM, BN) : make_idesc_bf16(kBM, BN, A_MN, B_MN));
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_epi = smem + kStages * S::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + S::kEpiBufs * S::kEpiBytes);
+  uint8_t* smem_sf = smem_epi + S::kEpiBufs * S::kEpiBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sf + kStages * S::kSfBytes);
   uint64_t* full_bar = bars;                       // [kStages]
   uint64_t* empty_bar = bars + kStages;            // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;         // [2]
@@ -248,7 +265,19 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
           if (!ok) break;
           uint8_t* sa = smem + s * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
-          mbar_expect_tx(&full_bar[s], S::kStageBytes);
+          if (MX) {
+            // scale factors of this stage: one 512-byte chunk for A's rows and one per 128 columns of B
+            const int b_tile = t.b_y / kBM;
+            const int nb = min(BN / kBM, p.sf_b_tiles - b_tile);
+            mbar_expect_tx(&full_bar[s], S::kStageBytes + 512u * static_cast<uint32_t>(1 + nb));
+            uint8_t* ssf = smem_sf + s * S::kSfBytes;
+            bulk_load_1d(ssf, p.sfa + (static_cast<int64_t>(t.a_y / kBM) * p.sf_kchunks + k) * 512, 512, &full_bar[s]);
+            for (int j = 0; j < nb; ++j)
+              bulk_load_1d(ssf + 512 * (1 + j), p.sfb + (static_cast<int64_t>(b_tile + j) * p.sf_kchunks + k) * 512, 512,
+                           &full_bar[s]);
+          } else {
+            mbar_expect_tx(&full_bar[s], S::kStageBytes);
+          }
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
@@ -274,8 +303,8 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
       for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
         TileCoord t;
         if (!decode_tile<BN, A_MN, B_MN, COMM, FP8>(p, idx, tiles_m, tiles_n, t)) break;
-        const int acc = tile_it & 1;
-        const uint32_t acc_ph = (tile_it >> 1) & 1u;
+        const int acc = tile_it % kAccBufs;
+        const uint32_t acc_ph = (tile_it / kAccBufs) & 1u;
         ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1u, p.status);
         if (!ok) break;
         tc_fence_after_sync();
@@ -288,13 +317,24 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
+          if (MX) {
+            const uint32_t ssf = smem_u32(smem_sf + s * S::kSfBytes);
+            tc_cp_32x128b_warpx4(tmem_base + kSfaCol, make_smem_desc_rows16(ssf));
+#pragma unroll
+            for (int j = 0; j < BN / kBM; ++j)
+              tc_cp_32x128b_warpx4(tmem_base + kSfbCol + 4 * j, make_smem_desc_rows16(ssf + 512 * (1 + j)));
+          }
 #pragma unroll
           for (int kk = 0; kk < kBK / 16; ++kk) {
             const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, kBK * 128, 1024)
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, kBK * 128, 1024)
                                      : make_smem_desc(sb + kk * 32, 16, 1024);
-            if (FP8) {
+            if (MX) {
+              // 32-element block kk of this stage: byte kk of the scale-factor columns
+              tc_mma_mxf8_ss(tmem_d, da, db, kIdesc | (static_cast<uint32_t>(kk) << 29) | (static_cast<uint32_t>(kk) << 4),
+                             tmem_base + kSfaCol, tmem_base + kSfbCol, (k | kk) != 0 ? 1u : 0u);
+            } else if (FP8) {
               tc_mma_f8_ss(tmem_d, da, db, kIdesc, (k | kk) != 0 ? 1u : 0u);
             } else {
               tc_mma_f16_ss(tmem_d, da, db, kIdesc, (k | kk) != 0 ? 1u : 0u);
@@ -378,8 +418,8 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
     for (int idx = blockIdx.x; ok; idx += gridDim.x, ++tile_it) {
       TileCoord t;
       if (!decode_tile<BN, A_MN, B_MN, COMM, FP8>(p, idx, tiles_m, tiles_n, t)) break;
-      const int acc = tile_it & 1;
-      const uint32_t acc_ph = (tile_it >> 1) & 1u;
+      const int acc = tile_it % kAccBufs;
+      const uint32_t acc_ph = (tile_it / kAccBufs) & 1u;
       ok = mbar_wait(&acc_full[acc], acc_ph, p.status);
       // all 128 epilogue threads must take the same branch: barrier with an AND reduction
       {
@@ -428,7 +468,7 @@ __global__ void __launch_bounds__(kGemmThreadsAllGather, 1) gemm_sm100_kernel(co
 #pragma unroll
             for (int i = 0; i < 32; ++i) { v0[i] = 0u; v1[i] = 0u; }
           }
-          const float osc = (FP8 && p.out_scale != nullptr) ? *p.out_scale : 1.f;
+          const float osc = (FP8 == 1 && p.out_scale != nullptr) ? *p.out_scale : 1.f;
           if (!FP8 && COMM == 0 && p.epi_cin != nullptr) {
             // out = epi_c * acc + epi_b * Cin + epi_a * I: the Newton-Schulz polynomial b A + c A^2 (+ a I) formed in
             // the epilogue of the A * A product, Cin = A in the layout of C (N a multiple of 64)

@@ -144,6 +144,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), counted on `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y,
                                             int z) {
   asm volatile(
@@ -239,6 +247,27 @@ __device__ __forceinline__ void tc_mma_f8_ss(uint32_t tmem_d, uint64_t desc_a, u
 }
 
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand (bf16 pairs packed in 32-bit columns) comes from TMEM.
+// Block-scaled 8-bit float product (kind::mxf8f6f4): every 32 elements of K of a row of A and of a column of B
+// carry one e8m0 scale factor, read from tensor memory at `tmem_sfa` / `tmem_sfb`; K = 32 per instruction.
+__device__ __forceinline__ void tc_mma_mxf8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
+// Shared memory -> tensor memory copy of 32 rows x 16 bytes, replicated into all four 32-lane quarters: row r lands
+// in lanes r, r+32, r+64, r+96, its 16 bytes in four consecutive 32-bit columns.  One thread issues; the copy is
+// ordered before later tcgen05.mma of the same thread and is covered by the next tcgen05.commit.
+__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t tmem_dst, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(smem_desc) : "memory");
+}
+
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                               uint32_t accumulate) {
   asm volatile(
@@ -333,6 +362,23 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_m
 // kind::f8f6f4 descriptor with e4m3 (format code 0) for both operands, K-major, fp32 accumulate
 __host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Descriptor of an unswizzled block of 16-byte rows (row r at byte 16 r; groups of 8 rows 128 bytes apart): the
+// source of the scale-factor copy above.
+__device__ __forceinline__ uint64_t make_smem_desc_rows16(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+// kind::mxf8f6f4 block-scaled descriptor: e4m3 operands (format 0), K-major, e8m0 scale factors.
+//   [4,6) byte of the scale-factor column used for B   [7,10) A format   [10,13) B format   [17,23) N >> 3
+//   [23] scale format (1 = e8m0)   [24,29) M >> 4   [29,31) byte of the scale-factor column used for A
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n) {
+  return (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // pack two floats into one bf16x2 register (lo = a, hi = b)

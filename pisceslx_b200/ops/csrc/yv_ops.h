@@ -46,6 +46,11 @@ struct GemmArgs {
   // fp8 (e4m3) operands, both stored K-inner, bf16 output scaled by *out_scale in the epilogue (dense mode only)
   bool fp8 = false;
   const float* out_scale = nullptr;
+  // block-scaled fp8 ("MX": e4m3 elements, one e8m0 scale per 32 elements of K): scale chunks of A and of B in the
+  // 512-byte-per-(128 rows, 128 K) layout written by launch_mx_quantize; dense and grouped-M modes, K % 128 == 0,
+  // rows of B (per expert) a multiple of 128.  Implies fp8.
+  const void* sfa = nullptr;
+  const void* sfb = nullptr;
   // affine epilogue: C = epi_c * (A B) + epi_b * epi_cin + epi_a * I (epi_cin bf16, laid out like C; N % 64 == 0)
   const void* epi_cin = nullptr;
   float epi_a = 0.f, epi_b = 0.f, epi_c = 1.f;
@@ -92,6 +97,19 @@ int launch_add(const void* a, const void* b, void* out, int64_t n, cudaStream_t 
 int launch_l2_flush(void* buf, int64_t bytes, cudaStream_t stream);
 // Per-tensor fp8 (e4m3) quantisation for delayed scaling: q = saturate(x * *scale), and the tensor's own absolute
 // maximum is folded into *amax (atomic max; the caller turns it into the scale of a later step).
+// Knowledge-field FiLM in one kernel: out[t] = h[t] * (1 + s) + b with (s | b) = (sum_c table[c][idx[t][c]]) @ w^T.
+// table_ptrs: per rank of the group the base of its shard [C, rows_per_rank, 128] bf16 (peer pointers for the other
+// ranks); w [2H, 128] bf16 (scale rows, then shift rows); h, out [tokens, H] bf16 (may alias); e_out [tokens, 128]
+// bf16 or null.  D must be 128, H a multiple of 64, C <= 16.
+int launch_pq_film(void* const* table_ptrs, int world, const int* idx, const void* w, const void* h, void* out,
+                   void* e_out, int64_t tokens, int C, int64_t rows_per_rank, int D, int H, uint32_t* status,
+                   cudaStream_t stream);
+
+// Block-scaled quantisation of x [rows, K] (bf16, K % 128 == 0): q [rows, K] e4m3 and the scale chunks
+// [ceil(rows / 128)][K / 128][512] described at GemmArgs::sfa.  Scale of a 32-element block = the smallest power of two that
+// brings the block's largest magnitude to at most 448, stored as a biased exponent byte; rows past `rows` in the last tile get scale 2^0.
+int launch_mx_quantize(const void* x_bf16, void* q_e4m3, void* sf, int64_t rows, int K, cudaStream_t stream);
+
 int launch_fp8_quantize(const void* x_bf16, const float* scale, void* q_e4m3, float* amax, int64_t n,
                         cudaStream_t stream);
 

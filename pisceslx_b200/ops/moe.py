@@ -126,21 +126,37 @@ class _MoEExpertsFn(torch.autograd.Function):
         is zero (dropped by the capacity rule)."""
 
     @staticmethod
-    def forward(ctx, x, w13, w2, weights, idx, counts, deterministic, training=True):
+    def forward(ctx, x, w13, w2, weights, idx, counts, deterministic, training=True, fp8=None):
         K = _k()
         st = status_word(x.device)
         T, H = x.shape
         E, twoF, _ = w13.shape
         F = twoF // 2
         x = x.contiguous()
-        xp, plan = permute_tokens(x, idx, counts, E, deterministic, zero_pad=training)
+        mx = fp8 == "mx" and H % 128 == 0 and twoF % 128 == 0 and F % 128 == 0
+        xp, plan = permute_tokens(x, idx, counts, E, deterministic, zero_pad=training or mx)
         y1 = torch.empty(plan.max_rows, twoF, dtype=_BF16, device=x.device)
-        K.gemm_grouped_m(xp, w13, y1, plan.tile_expert, plan.num_m_tiles, False, 0, st)
-        del xp
         act = torch.empty(plan.max_rows, F, dtype=_BF16, device=x.device)
-        K.swiglu_fwd(y1, act)
         y2 = torch.empty(plan.max_rows, H, dtype=_BF16, device=x.device)
-        K.gemm_grouped_m(act, w2, y2, plan.tile_expert, plan.num_m_tiles, False, 0, st)
+        if mx:
+            # forward products on the block-scaled fp8 tensor cores: rows quantised per 32 elements on the fly, the
+            # expert weights once per optimizer step; backward stays in bf16 from the saved bf16 tensors
+            from ..quant import fp8 as q8
+            xq, xs = q8.quantize_mx(xp)
+            del xp
+            wq, ws = _mx_weight(w13)
+            K.gemm_mxfp8(xq, xs, wq, ws, y1, plan.tile_expert, plan.num_m_tiles, 0, st)
+            del xq, xs
+            K.swiglu_fwd(y1, act)
+            aq, as_ = q8.quantize_mx(act)
+            wq, ws = _mx_weight(w2)
+            K.gemm_mxfp8(aq, as_, wq, ws, y2, plan.tile_expert, plan.num_m_tiles, 0, st)
+            del aq, as_
+        else:
+            K.gemm_grouped_m(xp, w13, y1, plan.tile_expert, plan.num_m_tiles, False, 0, st)
+            del xp
+            K.swiglu_fwd(y1, act)
+            K.gemm_grouped_m(act, w2, y2, plan.tile_expert, plan.num_m_tiles, False, 0, st)
         del act
         out = torch.empty(T, H, dtype=_BF16, device=x.device)
         wts = weights.float().contiguous()
@@ -189,15 +205,33 @@ class _MoEExpertsFn(torch.autograd.Function):
         del xp, dy1
         dx = torch.empty(T, H, dtype=_BF16, device=dev)
         K.moe_unpermute_sum(dxp, row_map, dx, k)
-        return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None, None
+        return dx, dw13, dw2, dwts.to(ctx.w_dtype), None, None, None, None, None
+
+
+_MX_WEIGHTS: dict = {}
+
+
+def _mx_weight(w: torch.Tensor):
+    """Block-scaled copy of a stacked expert weight [E, N, K] (quantised again only after the tensor changed)."""
+    from ..quant import fp8 as q8
+    key = (w.data_ptr(), w._version, tuple(w.shape))
+    hit = _MX_WEIGHTS.get(w.data_ptr())
+    if hit is None or hit[0] != key:
+        E, N, Kd = w.shape
+        q, sf = q8.quantize_mx(w.detach().reshape(E * N, Kd))
+        hit = (key, q.view(E, N, Kd), sf)
+        _MX_WEIGHTS[w.data_ptr()] = hit
+    return hit[1], hit[2]
 
 
 def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: torch.Tensor, idx: torch.Tensor,
-                counts: Optional[torch.Tensor] = None, deterministic: bool = False) -> torch.Tensor:
+                counts: Optional[torch.Tensor] = None, deterministic: bool = False,
+                fp8: Optional[str] = None) -> torch.Tensor:
     """Routed experts: out[t] = sum_j weights[t,j] * SwiGLU_FFN_{idx[t,j]}(x[t]).
 
     x [T,H]; w13 [E, 2F, H] (gate rows then up rows); w2 [E, H, F]; weights/idx [T,k]; counts [E] int32
-    (the histogram the gate kernel produced; recomputed when omitted)."""
+    (the histogram the gate kernel produced; recomputed when omitted).  ``fp8="mx"`` runs the two forward products
+    with e4m3 operands and one power-of-two scale per 32 elements (CUDA; H, F multiples of 128)."""
     if not x.is_cuda:
         return ref.moe_experts(x, w13, w2, weights, idx)
     E = w13.shape[0]
@@ -205,7 +239,7 @@ def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: t
         counts = torch.bincount(idx.flatten().long(), minlength=E).int()
     # without autograd (inference) nothing reads what the pad rows of the expert segments produce: skip zeroing them
     return _MoEExpertsFn.apply(x.to(_BF16), w13, w2, weights, idx.int(), counts.int(), deterministic,
-                               torch.is_grad_enabled())
+                               torch.is_grad_enabled(), fp8)
 
 
 def update_gate_bias(bias: torch.Tensor, counts: torch.Tensor, rate: float, clamp: float = 2.0) -> None:

@@ -111,6 +111,111 @@ class YvFP8DelayedScaling:
         self.steps += 1
 
 
+# ------------------------------------------------------------------------------------------------------------------
+# MX block scaling: e4m3 elements, one power-of-two (e8m0) scale per 32 elements of the reduction dimension.  The
+# tensor cores apply the scales themselves (tcgen05 ``kind::mxf8f6f4.block_scale``), so the GEMM needs no fp32
+# rescaling pass and no amax history.
+# ------------------------------------------------------------------------------------------------------------------
+MX_BLOCK = 32
+
+
+def quantize_mx_reference(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x [R, K] (K % 32 == 0) -> (q e4m3 [R, K], exponent bytes uint8 [R, K / 32]); the block's scale
+    ``2 ** (byte - 127)`` is the smallest power of two that brings the block's largest magnitude to at most 448
+    (byte 127 for an all-zero block), so nothing saturates.  Plain PyTorch on any device: the oracle of the quantise
+    kernel."""
+    R, K = x.shape
+    b = x.float().view(R, K // MX_BLOCK, MX_BLOCK)
+    amax = b.abs().amax(-1)
+    mant, ex = torch.frexp(amax)                            # amax = mant * 2^ex, 0.5 <= mant < 1; 448 = 0.875 * 2^9
+    e = (ex - 9 + (mant > 0.875).to(ex.dtype)).float()
+    e = torch.where(amax > 0, e, torch.zeros_like(e)).clamp(-127, 126)
+    q = (b * torch.exp2(-e)[..., None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.view(R, K), (e + 127).to(torch.uint8)
+
+
+def dequantize_mx(q: torch.Tensor, exp_bytes: torch.Tensor) -> torch.Tensor:
+    """fp32 values of an MX tensor (q [R, K], exponent bytes [R, K / 32])."""
+    R, K = q.shape
+    s = torch.exp2(exp_bytes.float() - 127.0)
+    return (q.float().view(R, K // MX_BLOCK, MX_BLOCK) * s[..., None]).view(R, K)
+
+
+def mx_scales_to_chunks(exp_bytes: torch.Tensor) -> torch.Tensor:
+    """[R, K / 32] exponent bytes -> the layout the GEMM kernel copies into tensor memory:
+    ``[ceil(R / 128), K / 128, 512]``, where byte ``(r % 32) * 16 + (r // 32) * 4 + j`` of a chunk holds row ``r`` of
+    the 128-row tile and 32-element block ``j`` of the 128-element K chunk (missing rows get 127 = 1.0)."""
+    R, KB = exp_bytes.shape
+    assert KB % 4 == 0, "K must be a multiple of 128"
+    tiles = (R + 127) // 128
+    full = torch.full((tiles * 128, KB), 127, dtype=torch.uint8, device=exp_bytes.device)
+    full[:R] = exp_bytes
+    v = full.view(tiles, 4, 32, KB // 4, 4)                 # tile, r // 32, r % 32, chunk, j
+    return v.permute(0, 3, 2, 1, 4).contiguous().view(tiles, KB // 4, 512)
+
+
+def mx_chunks_to_scales(chunks: torch.Tensor, rows: int) -> torch.Tensor:
+    """Inverse of ``mx_scales_to_chunks``."""
+    tiles, kc, _ = chunks.shape
+    v = chunks.view(tiles, kc, 32, 4, 4).permute(0, 3, 2, 1, 4).contiguous().view(tiles * 128, kc * 4)
+    return v[:rows]
+
+
+def quantize_mx(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [R, K] (K % 128 == 0) -> (q e4m3 [R, K], scale chunks uint8 [ceil(R/128), K/128, 512]).  CUDA: one kernel;
+    elsewhere the reference above."""
+    R, K = x.shape
+    if not x.is_cuda:
+        q, e = quantize_mx_reference(x)
+        return q, mx_scales_to_chunks(e)
+    from ..ops import kernels
+    q = torch.empty(R, K, dtype=torch.float8_e4m3fn, device=x.device)
+    tiles = (R + 127) // 128
+    alloc = torch.empty if R % 128 == 0 else (lambda *a, **k: torch.full(*a, 127, **k))
+    sf = alloc((tiles, K // 128, 512), dtype=torch.uint8, device=x.device)
+    kernels().mx_quantize(x.to(torch.bfloat16).contiguous(), q, sf)
+    return q, sf
+
+
+def gemm_mx(a_q: torch.Tensor, a_sf: torch.Tensor, b_q: torch.Tensor, b_sf: torch.Tensor,
+            tile_expert: Optional[torch.Tensor] = None, num_m_tiles: Optional[torch.Tensor] = None,
+            bn: int = 0) -> torch.Tensor:
+    """bf16 ``A @ B.T`` of two MX tensors on the block-scaled tensor-core path.  With ``tile_expert`` the 128-row tile
+    ``i`` of ``a_q`` multiplies ``b_q[tile_expert[i]]`` (``b_q`` [E, N, K]): the routed experts' grouped product."""
+    from ..ops import kernels, status_word
+    N = b_q.shape[-2]
+    c = torch.empty(a_q.shape[0], N, dtype=torch.bfloat16, device=a_q.device)
+    kernels().gemm_mxfp8(a_q, a_sf, b_q, b_sf, c, tile_expert, num_m_tiles, bn, status_word(a_q.device))
+    return c
+
+
+class _MXLinearFn(torch.autograd.Function):
+    """Forward: both operands quantised per 32-element block and multiplied on the block-scaled tensor cores.
+    Backward in bf16 from the saved bf16 operands (reference opss/train/fp8.py:381-399 keeps its backward in the
+    compute dtype as well)."""
+
+    @staticmethod
+    def forward(ctx, x, w, cache):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        xq, xs = quantize_mx(x2)
+        key = (w.data_ptr(), w._version)
+        if cache.get("key") != key:                       # the weight is re-quantised only after it changed
+            cache["key"], cache["q"] = key, quantize_mx(w.detach().contiguous())
+        wq, ws = cache["q"]
+        y = gemm_mx(xq, xs, wq, ws)
+        ctx.save_for_backward(x2, w)
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+        dx = F_.gemm(dy2, w, b_mn=True).view(ctx.shape)
+        dw = F_.gemm(dy2, x2, a_mn=True, b_mn=True)
+        return dx, dw, None
+
+
 def fp8_quantize_delayed(x: torch.Tensor, meta: YvFP8DelayedScaling) -> torch.Tensor:
     """bf16 CUDA tensor -> e4m3 with ``meta.scale``; records the tensor's amax in ``meta.amax_now``."""
     from ..ops import kernels
@@ -150,17 +255,27 @@ class _FP8GemmLinearFn(torch.autograd.Function):
 
 
 class YvFP8GemmLinear(nn.Module):
-    """Linear layer whose forward runs the e4m3 GEMM kernel with delayed per-tensor scaling (CUDA, bf16 parameters;
-    in/out features multiples of 16)."""
+    """Linear layer whose forward runs on the fp8 tensor cores (CUDA, bf16 parameters).
 
-    def __init__(self, in_features: int, out_features: int, device=None, history: int = 16):
+    ``scaling="mx"`` (default when the shapes allow: in_features a multiple of 128, out_features of 128): e4m3 with
+    one power-of-two scale per 32 elements, applied by the tensor cores.  ``scaling="delayed"``: per-tensor scales
+    from an amax history, applied in the GEMM epilogue (in/out features multiples of 16)."""
+
+    def __init__(self, in_features: int, out_features: int, device=None, history: int = 16, scaling: str = "auto"):
         super().__init__()
         device = torch.device(device or "cuda")
+        if scaling == "auto":
+            scaling = "mx" if in_features % 128 == 0 and out_features % 128 == 0 else "delayed"
+        assert scaling in ("mx", "delayed")
+        self.scaling = scaling
+        self._mx_cache: dict = {}
         self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=torch.bfloat16, device=device).normal_(std=0.02))
         self.meta_x = YvFP8DelayedScaling(device, history)
         self.meta_w = YvFP8DelayedScaling(device, history)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.scaling == "mx":
+            return _MXLinearFn.apply(x.to(torch.bfloat16), self.weight, self._mx_cache)
         return _FP8GemmLinearFn.apply(x.to(torch.bfloat16), self.weight, self.meta_x, self.meta_w)
 
 

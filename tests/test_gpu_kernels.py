@@ -523,6 +523,65 @@ def test_pq_gather_and_argmax(Y):
     assert rel(out, ref.pq_gather_sum(table.float(), idx)) < 4e-3
 
 
+@pytest.mark.parametrize("T,H,C,world", [(300, 256, 16, 1), (1000, 512, 7, 4)])
+def test_pq_film_fused_kernel_matches_fp32_reference(Y, T, H, C, world):
+    """Gather + sum + projection + modulation in one kernel against the same arithmetic in fp32.  The "ranks" of the
+    sharded table are separate buffers of this device (the kernel only reads them)."""
+    from pisceslx_b200.ops import check_status, status_word
+    torch.manual_seed(T)
+    rows = 96
+    shards = [(torch.randn(C, rows, 128, device=DEV) * 0.5).bfloat16() for _ in range(world)]
+    ptrs = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64)
+    idx = torch.randint(0, rows * world, (T, C), device=DEV, dtype=torch.int32)
+    w = (torch.randn(2 * H, 128, device=DEV) * 0.05).bfloat16()
+    h = torch.randn(T, H, device=DEV).bfloat16()
+    out = torch.empty_like(h)
+    e = torch.empty(T, 128, device=DEV, dtype=torch.bfloat16)
+    Y.pq_film(ptrs, idx, w, h, out, e, C, rows, status_word(torch.device(DEV, 0)))
+    torch.cuda.synchronize()
+    check_status()
+    full = torch.cat([s.float() for s in shards], 1)                       # [C, rows * world, 128]
+    e_ref = full[torch.arange(C, device=DEV).view(1, C), idx.long()].sum(1)
+    assert rel(e, e_ref) < 4e-3
+    f = e.float() @ w.float().t()                                          # the kernel projects the bf16-rounded sum
+    ref_out = h.float() * (1 + f[:, :H]) + f[:, H:]
+    assert rel(out, ref_out) < 4e-3
+    out2 = h.clone()                                                       # in place, without the side output
+    Y.pq_film(ptrs, idx, w, out2, out2, None, C, rows, None)
+    assert torch.equal(out2, out)
+
+
+def test_pq_field_fused_path_matches_unfused_forward_and_backward():
+    from pisceslx_b200.config import YvConfig
+    from pisceslx_b200.models.subconscious import YvPQKnowledgeField
+    from pisceslx_b200.models.norms import YvFiLMModulation
+    torch.manual_seed(5)
+    cfg = YvConfig(hidden_size=256, n_layer=4, n_head=4, n_kv_head=2, vocab_size=512, use_pq_field=True,
+                   pq_codebook_size=2048, pq_nav_hidden=128)
+    field = YvPQKnowledgeField(cfg).to(device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        field.film_proj.normal_(std=0.05)
+    assert field.fused_ok
+    h = torch.randn(2 * 150, 256, device=DEV).bfloat16()
+    g = torch.randn_like(h)
+    outs, grads = [], []
+    for fused in (True, False):
+        field.zero_grad()
+        hh = h.clone().requires_grad_(True)
+        field.begin(hh, 2)
+        if fused:
+            y = field.apply_fused(hh)
+        else:
+            film = field.film_params(0, hh)
+            y = YvFiLMModulation.apply(hh.view(2, -1, 256), film).view(hh.shape)
+        (y.float() * g.float()).sum().backward()
+        outs.append(y.detach())
+        grads.append((hh.grad.clone(), field.film_proj.grad.clone(), field.codebook.grad.clone()))
+    assert rel(outs[0], outs[1].float()) < 1e-2
+    for a, b in zip(grads[0], grads[1]):
+        assert rel(a, b.float()) < 2e-2
+
+
 def test_patchify(Y):
     from pisceslx_b200.ops import reference as ref
     torch.manual_seed(17)

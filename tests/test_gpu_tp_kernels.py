@@ -112,7 +112,7 @@ def test_fp8_gemm_matches_dequantised_reference(M, N, K):
 def test_fp8_linear_module_delayed_scaling_trains():
     from pisceslx_b200.quant.fp8 import YvFP8GemmLinear
     torch.manual_seed(0)
-    lin = YvFP8GemmLinear(512, 256)
+    lin = YvFP8GemmLinear(512, 256, scaling="delayed")
     x = torch.randn(64, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     for _ in range(3):
         y = lin(x)
@@ -120,6 +120,93 @@ def test_fp8_linear_module_delayed_scaling_trains():
     assert _rel(y, ref) < 6e-2 and lin.meta_x.steps >= 3
     y.float().pow(2).mean().backward()
     assert x.grad is not None and lin.weight.grad is not None and torch.isfinite(lin.weight.grad.float()).all()
+
+
+def test_mx_quantize_kernel_matches_reference_bytes_and_layout():
+    from pisceslx_b200.quant import fp8 as q8
+    torch.manual_seed(3)
+    x = (torch.randn(300, 512, device=DEV) * torch.logspace(-3, 2, 512, device=DEV)).to(torch.bfloat16)
+    x[5, :32] = 0                                               # an all-zero block keeps scale 1
+    x[6, 0] = 448.0                                             # a block whose maximum needs no scaling at all
+    x[6, 1:32] = 0.25
+    q, sf = q8.quantize_mx(x)
+    q_ref, e_ref = q8.quantize_mx_reference(x)
+    e_k = q8.mx_chunks_to_scales(sf, 300)
+    bad = (e_k != e_ref).nonzero()
+    assert bad.numel() == 0, (bad[:4].tolist(), e_k[e_k != e_ref][:4].tolist(), e_ref[e_k != e_ref][:4].tolist(),
+                              x.float().view(300, 16, 32).abs().amax(-1)[e_k != e_ref][:4].tolist())
+    assert torch.equal(sf, q8.mx_scales_to_chunks(e_ref))       # pad rows of the last tile hold 127
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    d = q8.dequantize_mx(q, e_ref)
+    assert _rel(d, x.float()) < 4e-2 and float(d[6, 0]) == 448.0 and int(e_ref[5, 0]) == 127
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(256, 384, 512, 128), (256, 384, 512, 256), (1000, 1408 + 128, 4096, 0),
+                                      (4096, 4096, 1408 - 128, 256), (4096, 4096, 4096, 128)])
+def test_mxfp8_gemm_matches_dequantised_reference(M, N, K, bn):
+    """Block-scaled tensor-core product against the fp32 product of the dequantised operands: the scales are powers
+    of two and the products exact, so only fp32 accumulation order and the bf16 output round."""
+    from pisceslx_b200.ops import check_status
+    from pisceslx_b200.quant import fp8 as q8
+    torch.manual_seed(M + N)
+    # per-column magnitudes spread over five decades: a per-tensor scale would flush most of them to zero
+    x = (torch.randn(M, K, device=DEV) * torch.logspace(-3, 2, K, device=DEV)).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05 * torch.logspace(1, -2, K, device=DEV)).to(torch.bfloat16)
+    xq, xs = q8.quantize_mx(x)
+    wq, ws = q8.quantize_mx(w)
+    y = q8.gemm_mx(xq, xs, wq, ws, bn=bn)
+    torch.cuda.synchronize()
+    check_status()
+    ref = q8.dequantize_mx(xq, q8.mx_chunks_to_scales(xs, M)) @ q8.dequantize_mx(wq, q8.mx_chunks_to_scales(ws, N)).t()
+    assert _rel(y, ref) < 4e-3
+    assert _rel(y, x.float() @ w.float().t()) < 5e-2            # quantisation error of e4m3 with block scales
+
+
+def test_mxfp8_grouped_gemm_and_expert_forward():
+    from pisceslx_b200.ops import check_status, moe as moe_ops
+    from pisceslx_b200.quant import fp8 as q8
+    torch.manual_seed(11)
+    E, H, F, T, k = 8, 512, 384, 1500, 2
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    w13 = (torch.randn(E, 2 * F, H, device=DEV) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, F, device=DEV) * 0.05).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    wts = torch.softmax(torch.randn(T, k, device=DEV), -1)
+    # grouped product alone
+    counts = torch.bincount(idx.flatten().long(), minlength=E).int()
+    xp, plan = moe_ops.permute_tokens(x, idx, counts, E, False, zero_pad=True)
+    xq, xs = q8.quantize_mx(xp)
+    wq, ws = q8.quantize_mx(w13.view(E * 2 * F, H))
+    y = q8.gemm_mx(xq, xs, wq.view(E, 2 * F, H), ws, plan.tile_expert, plan.num_m_tiles)
+    torch.cuda.synchronize()
+    check_status()
+    n_t = int(plan.num_m_tiles)
+    xd = q8.dequantize_mx(xq, q8.mx_chunks_to_scales(xs, xp.shape[0]))
+    wd = q8.dequantize_mx(wq, q8.mx_chunks_to_scales(ws, E * 2 * F)).view(E, 2 * F, H)
+    te = plan.tile_expert[:n_t].long()
+    ref = torch.einsum("trh,tnh->trn", xd[:n_t * 128].view(n_t, 128, H), wd[te]).reshape(n_t * 128, 2 * F)
+    assert _rel(y[:n_t * 128], ref) < 4e-3
+    # whole expert layer: fp8 forward close to the bf16 one, backward runs
+    xg = x.clone().requires_grad_(True)
+    w13g, w2g = w13.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+    out8 = moe_ops.moe_experts(xg, w13g, w2g, wts, idx, fp8="mx")
+    out16 = moe_ops.moe_experts(x, w13, w2, wts, idx)
+    check_status()
+    assert _rel(out8, out16.float()) < 1e-1                      # two chained e4m3 products
+    out8.float().pow(2).mean().backward()
+    assert torch.isfinite(w13g.grad.float()).all() and torch.isfinite(xg.grad.float()).all()
+
+
+def test_fp8_linear_module_mx_forward_backward():
+    from pisceslx_b200.quant.fp8 import YvFP8GemmLinear
+    torch.manual_seed(0)
+    lin = YvFP8GemmLinear(512, 256)
+    assert lin.scaling == "mx"
+    x = torch.randn(3, 70, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = lin(x)
+    assert y.shape == (3, 70, 256) and _rel(y, x.float() @ lin.weight.float().t()) < 5e-2
+    y.float().pow(2).mean().backward()
+    assert torch.isfinite(lin.weight.grad.float()).all() and torch.isfinite(x.grad.float()).all()
 
 
 @pytest.mark.parametrize("G,n", [(3, 256), (2, 1408)])
