@@ -212,11 +212,11 @@ class PiscesLxInferOrchestrator:
 
     def run(self, args: Any) -> int:
         from ..models.tokenizer import YvTokenizer
-        tok = YvTokenizer.instance()
         if args.dry_run:
-            print(json.dumps({"prompt_tokens": len(tok.encode(args.prompt)), "model_size": args.model_size}))
+            print(json.dumps({"prompt_tokens": len(YvTokenizer.instance().encode(args.prompt)), "model_size": args.model_size}))
             return 0
         model = load_model_for_inference(args.model_size, args.ckpt, args.device, args.model_config)
+        tok = YvTokenizer.for_vocab(model.cfg.vocab_size)
         ids = torch.tensor([tok.encode(args.prompt)], dtype=torch.long, device=next(model.parameters()).device)
         ids = ids.clamp_(0, model.cfg.vocab_size - 1)
         t0 = time.perf_counter()
@@ -254,7 +254,7 @@ class PiscesLxPreferenceOrchestrator:
             from .checkpoint import extract_state_dict
             model.load_reference_state_dict(extract_state_dict(torch.load(args.ckpt, map_location="cpu", weights_only=False)),
                                             strict=False)
-        tok = YvTokenizer.instance()
+        tok = YvTokenizer.for_vocab(model_cfg.vocab_size)
         if args.rlhf_dataset:
             records = [json.loads(l) for l in open(args.rlhf_dataset, encoding="utf-8") if l.strip()]
         else:

@@ -6,12 +6,13 @@
 //   s | b   = e[t] @ W^T                                    (W [2H, 128]: rows 0..H-1 scale, H..2H-1 shift)
 //   out[t]  = h[t] * (1 + s) + b
 //
-// A CTA owns 128 tokens.  All of its warps first gather and sum the tokens' entries into shared memory, already in
+// A CTA owns 128 tokens.  Nine of its warps first gather and sum the tokens' entries into shared memory (meanwhile
+// the producer warp already prefetches h tiles), already in
 // the 128-byte-swizzled K-major layout the tensor cores read (the "A" operand, 128 x 128 bf16, written once).  Then
 // the CTA walks the H / 64 column tiles: a producer thread streams the tile's 64 scale rows and 64 shift rows of W
-// (one 128-wide "B" operand, two buffers) and the matching 128 x 64 tile of h (four buffers, so that loads run three
-// tiles ahead of the stores) with TMA, one thread issues eight tcgen05 MMAs into one of two 128-column accumulators
-// in tensor memory, and four epilogue warps read scale and shift from tensor memory, modulate the h tile in shared
+// (one 128-wide "B" operand, three buffers) and the matching 128 x 64 tile of h (five buffers, so that loads run four
+// tiles ahead of the stores: a memory-bound kernel needs about 100 KB in flight per SM) with TMA, one thread issues eight tcgen05 MMAs into one of two 128-column accumulators
+// in tensor memory, and eight epilogue warps read scale and shift from tensor memory, modulate the h tile in shared
 // memory and send it out with a TMA store.  Neither e, nor scale, nor shift touches
 // device memory (e is written out only when the caller asks for it, for the backward pass).
 #include "per_device.h"
@@ -27,8 +28,9 @@ namespace {
 constexpr int kPqD = 128;                 // entry dimension = reduction length of the projection
 constexpr int kPqTile = 128;              // tokens per CTA tile
 constexpr int kPqCols = 64;               // output columns per column tile (the MMA is 2 * kPqCols wide)
-constexpr int kPqHBufs = 4;               // h tile buffers
-constexpr int kPqThreads = 192;           // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kPqHBufs = 5;               // h tile buffers: four tiles of loads in flight per SM
+constexpr int kPqBStages = 3;             // W tile buffers: the W stream (2 MB per CTA out of L2) is as latency-bound as h
+constexpr int kPqThreads = 320;           // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
 constexpr int kPqMaxC = 16;
 
 struct PqFilmParams {
@@ -48,8 +50,9 @@ struct PqSmem {
   static constexpr int kABytes = kPqTile * kPqD * 2;            // 32 KB: two 64-wide K halves of 16 KB
   static constexpr int kBBytes = 2 * kPqCols * kPqD * 2;        // 32 KB per stage: two K halves of 16 KB (128 rows each)
   static constexpr int kHBytes = kPqTile * kPqCols * 2;         // 16 KB: 128 rows of 128 bytes
-  static constexpr int kStages = 2;
-  static constexpr int kTotal = kABytes + kStages * kBBytes + kPqHBufs * kHBytes + 256 + 1024;
+  static constexpr int kStages = kPqBStages;
+  static constexpr int kIdxBytes = kPqTile * kPqMaxC * 4;       // 8 KB: the tile's entry ids
+  static constexpr int kTotal = kABytes + kStages * kBBytes + kPqHBufs * kHBytes + kIdxBytes + 256 + 1024;
 };
 
 // Bounded wait that also records WHICH wait of the pipeline gave up (bits 8..14 of the status word).
@@ -75,15 +78,17 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem_a + PqSmem::kABytes;
   uint8_t* smem_h = smem_b + PqSmem::kStages * PqSmem::kBBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_h + kPqHBufs * PqSmem::kHBytes);
-  uint64_t* b_full = bars;            // [2] W tile landed
-  uint64_t* b_empty = bars + 2;       // [2] MMAs that read the W tile are done
-  uint64_t* acc_full = bars + 4;      // [2]
-  uint64_t* acc_empty = bars + 6;     // [2]
-  uint64_t* h_full = bars + 8;        // [4] h tile landed
-  uint64_t* h_empty = bars + 12;      // [4] the store that read the h buffer is done
-  uint64_t* a_free = bars + 16;       // MMAs of the current token tile are done with the A operand
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  int* s_idx = reinterpret_cast<int*>(smem_h + kPqHBufs * PqSmem::kHBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_h + kPqHBufs * PqSmem::kHBytes + PqSmem::kIdxBytes);
+  uint64_t* acc_full = bars;                      // [2]
+  uint64_t* acc_empty = bars + 2;                 // [2]
+  uint64_t* b_full = bars + 4;                    // [kPqBStages] W tile landed
+  uint64_t* b_empty = b_full + kPqBStages;        // [kPqBStages] MMAs that read the W tile are done
+  uint64_t* h_full = b_empty + kPqBStages;        // [kPqHBufs] h tile landed
+  uint64_t* h_empty = h_full + kPqHBufs;          // [kPqHBufs] the store that read the h buffer is done
+  uint64_t* a_free = h_empty + kPqHBufs;          // MMAs of the current token tile are done with the A operand
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(a_free + 1);
+  static_assert((4 + 2 * kPqBStages + 2 * kPqHBufs + 2) * 8 <= 256, "barrier area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -95,10 +100,12 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
     tma_prefetch_desc(&p.tma_h);
     tma_prefetch_desc(&p.tma_out);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&b_full[s], 1);
-      mbar_init(&b_empty[s], 1);
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 1);
+    }
+    for (int s = 0; s < kPqBStages; ++s) {
+      mbar_init(&b_full[s], 1);
+      mbar_init(&b_empty[s], 1);
     }
     for (int s = 0; s < kPqHBufs; ++s) {
       mbar_init(&h_full[s], 1);
@@ -121,61 +128,91 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
   uint32_t m_it = 0;        // token tiles done by this CTA
   bool ok = true;
   for (int m = blockIdx.x; m < tiles_m; m += gridDim.x, ++m_it) {
-    // ---------------------------- gather + sum: every warp, 16 lanes per token ----------------------------
-    {
-      const int half = lane >> 4;                 // which of the warp's two tokens
-      const int piece = lane & 15;                // 16-byte piece (8 dims) of the 256-byte entry
-      for (int r = warp * 2 + half; r < kPqTile; r += (kPqThreads / 32) * 2) {
-        const long long t = static_cast<long long>(m) * kPqTile + r;
-        float acc[8];
+    // ---------------------------- gather + sum: warps 1-9, 16 lanes per token ----------------------------
+    // Random 256-byte rows of a table far larger than L2 and than the reach of an SM's address-translation cache:
+    // the loop runs over the CODEBOOKS on the outside (two at a time) and over the half-warp's tokens inside, so that
+    // at any moment the whole grid reads from two 32 MB codebooks (a few dozen 2 MB pages) instead of from all of
+    // them.  The tile's ids are staged in shared memory with one coalesced pass first; every lane keeps 16
+    // independent 16-byte loads in flight.
+    if (warp != 0) {
+      constexpr int kGatherThreads = kPqThreads - 32;                   // 288
+      constexpr int kHalfWarps = kGatherThreads / 16;                   // 18
+      constexpr int kRowsPerHw = (kPqTile + kHalfWarps - 1) / kHalfWarps;   // 8
+      const int gt = threadIdx.x - 32;
+      const long long t0 = static_cast<long long>(m) * kPqTile;
+      const long long n_ids = (p.tokens - t0 < kPqTile ? p.tokens - t0 : kPqTile) * p.C;
+      for (int i = gt; i < kPqTile * p.C; i += kGatherThreads) s_idx[i] = i < n_ids ? p.idx[t0 * p.C + i] : -1;
+      asm volatile("bar.sync 2, 288;" ::: "memory");
+      const int hw = gt >> 4;                                           // half-warp 0..17: rows hw, hw + 18, ...
+      const int piece = lane & 15;                                      // 16-byte piece (8 dims) of the 256-byte entry
+      const unsigned rpr = static_cast<unsigned>(p.rows_per_rank);
+      float acc[kRowsPerHw][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        if (t < p.tokens) {
-          uint4 v[kPqMaxC];
+      for (int i = 0; i < kRowsPerHw; ++i)
 #pragma unroll
-          for (int c = 0; c < kPqMaxC; ++c) {
-            v[c] = make_uint4(0u, 0u, 0u, 0u);
-            if (c < p.C) {
-              const long long e = p.idx[t * p.C + c];
-              const long long owner = e / p.rows_per_rank;
-              if (e < 0 || owner >= p.world) {
-                if (p.status != nullptr) atomicOr(p.status, kStatusIndexOutOfRange);
-              } else {
-                const uint4* row = reinterpret_cast<const uint4*>(p.table[owner]) +
-                                   (static_cast<long long>(c) * p.rows_per_rank + (e - owner * p.rows_per_rank)) * (kPqD / 8);
-                v[c] = ld_peer_v4(row + piece);
+        for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
+      for (int c0 = 0; c0 < p.C; c0 += 2) {
+        uint4 v[2][kRowsPerHw];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+          for (int i = 0; i < kRowsPerHw; ++i) {
+            v[u][i] = make_uint4(0u, 0u, 0u, 0u);
+            const int r = hw + kHalfWarps * i, c = c0 + u;
+            if (r < kPqTile && c < p.C) {
+              const int e = s_idx[r * p.C + c];
+              if (e >= 0) {
+                const unsigned owner = static_cast<unsigned>(e) / rpr;
+                if (owner >= static_cast<unsigned>(p.world)) {
+                  if (p.status != nullptr) atomicOr(p.status, kStatusIndexOutOfRange);
+                } else {
+                  const uint4* row = reinterpret_cast<const uint4*>(p.table[owner]) +
+                                     (static_cast<long long>(c) * p.rows_per_rank + (static_cast<unsigned>(e) - owner * rpr)) * (kPqD / 8);
+                  v[u][i] = ld_peer_v4(row + piece);
+                }
+              } else if (t0 + r < p.tokens && p.status != nullptr) {
+                atomicOr(p.status, kStatusIndexOutOfRange);              // a negative id of a real token
               }
             }
           }
+        }
 #pragma unroll
-          for (int c = 0; c < kPqMaxC; ++c) {
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[c]);
+        for (int u = 0; u < 2; ++u) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(h2[i]);
-              acc[2 * i] += f.x;
-              acc[2 * i + 1] += f.y;
+          for (int i = 0; i < kRowsPerHw; ++i) {
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[u][i]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = __bfloat1622float2(h2[k]);
+              acc[i][2 * k] += f.x;
+              acc[i][2 * k + 1] += f.y;
             }
           }
         }
-        uint4 o;
-        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
-        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
-        // K half (piece >> 3), 16-byte slot (piece & 7) XOR-swizzled with the row: the layout TMA SWIZZLE_128B produces
-        *reinterpret_cast<uint4*>(smem_a + (piece >> 3) * (kPqTile * 128) + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = o;
-        if (p.e_out != nullptr && t < p.tokens) reinterpret_cast<uint4*>(p.e_out + t * kPqD)[piece] = o;
       }
+#pragma unroll
+      for (int i = 0; i < kRowsPerHw; ++i) {
+        const int r = hw + kHalfWarps * i;
+        if (r < kPqTile) {
+          uint4 o;
+          o.x = pack_bf16(acc[i][0], acc[i][1]); o.y = pack_bf16(acc[i][2], acc[i][3]);
+          o.z = pack_bf16(acc[i][4], acc[i][5]); o.w = pack_bf16(acc[i][6], acc[i][7]);
+          // K half (piece >> 3), 16-byte slot (piece & 7) XOR-swizzled with the row: the layout TMA SWIZZLE_128B produces
+          *reinterpret_cast<uint4*>(smem_a + (piece >> 3) * (kPqTile * 128) + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = o;
+          if (p.e_out != nullptr && t0 + r < p.tokens) reinterpret_cast<uint4*>(p.e_out + (t0 + r) * kPqD)[piece] = o;
+        }
+      }
+      fence_proxy_async_smem();        // generic-proxy writes of A before the tensor cores read it
+      asm volatile("bar.sync 2, 288;" ::: "memory");      // the gathering warps; the producer does not wait
     }
-    fence_proxy_async_smem();          // generic-proxy writes of A before the tensor cores read it
-    __syncthreads();
 
     if (warp == 0) {
       // ---------------------------- TMA producer ----------------------------
       if (elect_one()) {
         uint32_t j = it;
         for (int n = 0; n < tiles_n && ok; ++n, ++j) {
-          const int s = j & 1;
-          const uint32_t ph = (j >> 1) & 1u;
+          const int s = j % kPqBStages;
+          const uint32_t ph = (j / kPqBStages) & 1u;
           ok = pq_wait(&b_empty[s], ph ^ 1u, p.status, 0);
           if (!ok) break;
           uint8_t* sb = smem_b + s * PqSmem::kBBytes;
@@ -198,14 +235,15 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
         uint32_t j = it;
         const uint32_t sa = smem_u32(smem_a);
         for (int n = 0; n < tiles_n && ok; ++n, ++j) {
-          const int s = j & 1;
+          const int s = j & 1;                                  // accumulator
           const uint32_t ph = (j >> 1) & 1u;
+          const int bs = j % kPqBStages;                        // W buffer
           ok = pq_wait(&acc_empty[s], ph ^ 1u, p.status, 2);
           if (!ok) break;
-          ok = pq_wait(&b_full[s], ph, p.status, 3);
+          ok = pq_wait(&b_full[bs], (j / kPqBStages) & 1u, p.status, 3);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t sb = smem_u32(smem_b + s * PqSmem::kBBytes);
+          const uint32_t sb = smem_u32(smem_b + bs * PqSmem::kBBytes);
           const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(s * 2 * kPqCols);
 #pragma unroll
           for (int kk = 0; kk < kPqD / 16; ++kk) {
@@ -213,7 +251,7 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
             const uint64_t db = make_smem_desc(sb + (kk >> 2) * (2 * kPqCols * 128) + (kk & 3) * 32, 16, 1024);
             tc_mma_f16_ss(tmem_d, da, db, kIdesc, kk != 0 ? 1u : 0u);
           }
-          tc_commit(&b_empty[s]);
+          tc_commit(&b_empty[bs]);
           tc_commit(&acc_full[s]);
         }
         if (ok) {
@@ -222,8 +260,9 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
         }
       }
     } else {
-      // ---------------------------- epilogue: 4 warps, one token row per thread ----------------------------
-      const int quarter = warp & 3;
+      // ---------------------------- epilogue: 8 warps, one token row and 32 of the 64 columns per thread -----------
+      const int quarter = warp & 3;                  // tensor-memory lane quarter this warp may read
+      const int colhalf = (warp - 2) >> 2;           // warps 2-5: columns 0-31, warps 6-9: columns 32-63
       const int row = quarter * 32 + lane;
       const bool issuer = (threadIdx.x == 64);
       uint32_t j = it;
@@ -239,7 +278,7 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
               "{\n"
               ".reg .pred pin, pout;\n"
               "setp.ne.u32 pin, %1, 0;\n"
-              "bar.red.and.pred pout, 1, 128, pin;\n"
+              "bar.red.and.pred pout, 1, 256, pin;\n"
               "selp.u32 %0, 1, 0, pout;\n"
               "}\n"
               : "=r"(all_ok)
@@ -251,8 +290,8 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + static_cast<uint32_t>(s * 2 * kPqCols) + (static_cast<uint32_t>(quarter * 32) << 16);
         uint8_t* sh = smem_h + hb * PqSmem::kHBytes;
-#pragma unroll 1
-        for (int c = 0; c < kPqCols / 32; ++c) {
+        {
+          const int c = colhalf;
           uint32_t sc[32], sf[32];
           tmem_ld32(taddr + c * 32, sc);
           tmem_ld32(taddr + kPqCols + c * 32, sf);
@@ -276,7 +315,7 @@ __global__ void __launch_bounds__(kPqThreads, 1) pq_film_kernel(const __grid_con
         }
         tc_fence_before_sync();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (issuer) {
           mbar_arrive(&acc_empty[s]);
           tma_store_2d(&p.tma_out, sh, n * kPqCols, m * kPqTile);

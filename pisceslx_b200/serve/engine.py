@@ -59,7 +59,10 @@ class YvEngineConfig:
 class YvInferenceEngine:
     def __init__(self, model: torch.nn.Module, tokenizer: Optional[YvTokenizer] = None,
                  cfg: Optional[YvEngineConfig] = None):
-        self.model, self.tokenizer, self.cfg = model.eval(), tokenizer or YvTokenizer.instance(), cfg or YvEngineConfig()
+        vocab = int(getattr(getattr(model, "cfg", None), "vocab_size", 0) or 0)
+        self.vocab_size = vocab
+        self.model, self.cfg = model.eval(), cfg or YvEngineConfig()
+        self.tokenizer = tokenizer or (YvTokenizer.for_vocab(vocab) if vocab else YvTokenizer.instance())
         p = next(model.parameters())
         self.device = p.device
         tp = model.parallel.tp_size if getattr(model, "parallel", None) is not None else 1
@@ -82,6 +85,11 @@ class YvInferenceEngine:
     def add_request(self, prompt_ids: List[int], max_new_tokens: int = 128,
                     sampling: Optional[YvSamplingConfig] = None, stop_token_ids: Optional[List[int]] = None,
                     on_token: Optional[Callable[[int], None]] = None) -> YvRequest:
+        prompt_ids = list(prompt_ids)
+        if not prompt_ids:
+            raise ValueError("empty prompt")
+        if self.vocab_size and (max(prompt_ids) >= self.vocab_size or min(prompt_ids) < 0):
+            raise ValueError(f"prompt holds token ids outside the model's vocabulary of {self.vocab_size}")
         with self._lock:
             rid = self._next_id
             self._next_id += 1

@@ -192,7 +192,8 @@ class PiscesLxNativeInferenceOperator(PiscesLxOperatorInterface):
         self.model = model.eval()
         if tokenizer is None:
             from ..models.tokenizer import YvTokenizer
-            tokenizer = YvTokenizer.instance()
+            vocab = int(getattr(getattr(self.model, "cfg", None), "vocab_size", 0) or 0)
+            tokenizer = YvTokenizer.for_vocab(vocab) if vocab else YvTokenizer.instance()
         self.tok = tokenizer
 
     def validate_inputs(self, inputs: Dict[str, Any]) -> bool:

@@ -242,7 +242,8 @@ def run_suite(name: str, model: Any, tokenizer: Any = None, data_path: Optional[
     """Evaluate ``model`` on suite ``name``.  Rows come from ``data_path`` (jsonl in the suite's row format) or, without
     one, from the built-in smoke rows: enough to exercise the harness end to end, not a score to report."""
     from ..models.tokenizer import YvTokenizer
-    tok = tokenizer or YvTokenizer.instance()
+    vocab = int(getattr(getattr(model, "cfg", None), "vocab_size", 0) or 0)
+    tok = tokenizer or (YvTokenizer.for_vocab(vocab) if vocab else YvTokenizer.instance())
     name = name.lower()
     if name not in available_suites():
         raise ValueError(f"unknown suite {name!r}; available: {', '.join(available_suites())}")
