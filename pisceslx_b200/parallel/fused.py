@@ -144,6 +144,13 @@ class _EPContext:
         self.num_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
         self.seg_src = torch.zeros(w * (e_local + 1), dtype=torch.int32, device=dev)
 
+    def valid(self) -> bool:
+        """The heap grows a named buffer by freeing and re-allocating it (serving sees many token counts: a long
+        prefill after a short one).  A context built before that holds pointers into freed memory."""
+        b = self.heap.buffers
+        return (b.get("ep_x_recv") is self.x_recv and b.get("ep_y_out") is self.y_out
+                and b.get("ep_dy_recv") is self.dy_recv and b.get("ep_counts") is self.table)
+
 
 _EP_CTX: Dict[Tuple[int, int, int, int], _EPContext] = {}
 
@@ -151,6 +158,8 @@ _EP_CTX: Dict[Tuple[int, int, int, int], _EPContext] = {}
 def _ep_context(group: Any, cap_rows: int, hidden: int, e_local: int) -> _EPContext:
     key = (id(group), cap_rows, hidden, e_local)
     ctx = _EP_CTX.get(key)
+    if ctx is not None and not ctx.valid():
+        ctx = None                 # a larger request re-allocated the named buffers since: the cached views are stale
     if ctx is None:
         ctx = _EPContext(heap_for(group), cap_rows, hidden, e_local)
         _EP_CTX[key] = ctx

@@ -112,9 +112,44 @@ def determinism(par, iters: int = 100) -> dict:
     return res
 
 
+def ep_regrow(par) -> dict:
+    """The fused expert-parallel layer at a small, a large and again the small token count (what a serving engine
+    does: short prompt, long prefill, decode).  The large call re-allocates the symmetric buffers; the small call
+    after it must not use views of the freed ones.  Every call is compared with the NCCL path."""
+    from pisceslx_b200.parallel import ep as epm
+    torch.manual_seed(11 + par.rank)
+    dev, E, H, F, k = par.device, 8, 512, 256, 2
+    e_local = E // par.ep_size
+    w13 = (torch.randn(e_local, 2 * F, H, device=dev) * 0.05).bfloat16()
+    w2 = (torch.randn(e_local, H, F, device=dev) * 0.05).bfloat16()
+    errs = []
+    for T in (16, 4096, 16, 9000, 64):
+        x = torch.randn(T, H, device=dev).bfloat16()
+        idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).int()
+        wts = torch.softmax(torch.randn(T, k, device=dev), -1)
+        with torch.no_grad():
+            fz.set_enabled(True)
+            a = epm.moe_experts_ep(x, w13, w2, wts, idx, E, par.ep_group, fused=True)
+            fz.set_enabled(False)
+            b = epm.moe_experts_ep(x, w13, w2, wts, idx, E, par.ep_group, fused=False)
+        torch.cuda.synchronize()
+        errs.append(float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)))
+    check_status()
+    t = torch.tensor(errs, dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"rel_err": t.tolist()}
+
+
 def main() -> None:
     tp, ep, out_path = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
     par = init_parallel(tp=tp, ep=ep, timeout_s=120)
+    if os.environ.get("YV_MULTI_MODE") == "ep_regrow":
+        res = ep_regrow(par)
+        if par.rank == 0:
+            json.dump(res, open(out_path, "w"))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     if os.environ.get("YV_MULTI_MODE") == "determinism":
         res = determinism(par, int(os.environ.get("YV_MULTI_ITERS", "100")))
         if par.rank == 0:

@@ -91,3 +91,12 @@ def test_flag_protocols_repeat_bit_exact(tmp_path, tp, ep):
         if k.endswith("mismatches"):
             assert v == 0, res
     assert res.get("ep_finite", True)
+
+
+def test_fused_expert_parallel_survives_buffer_regrowth(tmp_path):
+    """Token counts small -> large -> small -> larger -> small through the fused expert-parallel layer: the symmetric
+    receive buffers are re-allocated on the way up, and the cached per-shape contexts must follow."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = _launch(2, 1, 2, str(tmp_path / "regrow.json"), {"YV_MULTI_MODE": "ep_regrow"})
+    assert len(res["rel_err"]) == 5 and max(res["rel_err"]) < 2e-2, res
