@@ -195,3 +195,166 @@ class YvSOLAR:
                 self.scale[i] = min(self.bounds[1], max(self.bounds[0], self.scale[i] * (1 + self.meta_lr * agree)))
             self.prev[i] = g.detach().clone()
             p.add_(g, alpha=-self.lr * self.scale[i])
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# VeriCoT on hidden states (reference model/reasoning/vericot.py:42-230).  The text-level checker of arithmetic
+# statements is ``models.reasoning.YvVeriCoTVerifier``; the pair below scores a reasoning step's hidden state
+# against its context and nudges low-scoring steps, and can call the text checker for a symbolic score.
+# ----------------------------------------------------------------------------------------------------------------------
+class YvVeriCoTStepVerifier(nn.Module):
+    """Step / context projections -> validity in (0, 1).  Without a context the score is the neutral 0.5.  When
+    ``step_text`` is given the arithmetic statements in it are checked symbolically and the result is reported (and
+    folded into ``combined_score`` with weight ``symbolic_weight``)."""
+
+    def __init__(self, hidden_size: int, proj_dim: Optional[int] = None, ramp_steps: int = 1000,
+                 symbolic_weight: float = 0.5):
+        super().__init__()
+        p = proj_dim or max(8, hidden_size // 2)
+        self.questioner_proj = nn.Linear(hidden_size, p)
+        self.responder_proj = nn.Linear(hidden_size, p)
+        self.quality_estimator = nn.Sequential(nn.Linear(2 * p, p), nn.GELU(), nn.Linear(p, 1), nn.Sigmoid())
+        self.ramp_steps, self.symbolic_weight = ramp_steps, symbolic_weight
+        self.register_buffer("calls", torch.zeros((), dtype=torch.long))
+
+    @staticmethod
+    def _pool(h: torch.Tensor) -> torch.Tensor:
+        return h if h.dim() == 2 else h.mean(1)
+
+    def forward(self, step_hidden: torch.Tensor, context_hidden: Optional[torch.Tensor] = None, step_text: str = "",
+                return_details: bool = False) -> Dict[str, Any]:
+        q = self.questioner_proj(self._pool(step_hidden).float())
+        if context_hidden is not None:
+            r = self.responder_proj(self._pool(context_hidden).float())
+            quality = self.quality_estimator(torch.cat([q, r.expand_as(q)], -1)).squeeze(-1)
+        else:
+            quality = torch.full((q.shape[0],), 0.5, device=q.device)
+        symbolic = None
+        if step_text:
+            from .reasoning import YvReasoningTrace, YvVeriCoTVerifier
+            symbolic = 1.0 if YvVeriCoTVerifier().verify(YvReasoningTrace(steps=[step_text], answer="")) else 0.0
+        combined = quality if symbolic is None else (1 - self.symbolic_weight) * quality + self.symbolic_weight * symbolic
+        self.calls += 1
+        out = {"validity_score": quality, "consistency_score": quality, "combined_score": combined,
+               "is_valid": combined > 0.5, "symbolic_score": symbolic if symbolic is not None else 0.0}
+        if return_details:
+            out["ramp"] = min(1.0, float(self.calls) / max(self.ramp_steps, 1))
+        return out
+
+    def verify_chain(self, step_hiddens: Sequence[torch.Tensor], step_texts: Optional[Sequence[str]] = None,
+                     context_hidden: Optional[torch.Tensor] = None) -> Dict[str, Any]:
+        """Every step against the running context (the given context, then the mean of the steps seen so far)."""
+        results, ctx = [], context_hidden
+        for i, h in enumerate(step_hiddens):
+            results.append(self.forward(h, ctx, step_texts[i] if step_texts else ""))
+            pooled = self._pool(h).detach()
+            ctx = pooled if ctx is None else 0.5 * (self._pool(ctx) + pooled)
+        valid = [bool(r["is_valid"].all()) for r in results]
+        score = torch.stack([r["combined_score"].mean() for r in results]).mean() if results else torch.tensor(0.0)
+        return {"steps": results, "num_valid": sum(valid), "all_valid": all(valid), "chain_score": score,
+                "first_invalid": valid.index(False) if not all(valid) else None}
+
+    def compute_reflection(self, step_hidden: torch.Tensor, result: Dict[str, Any]) -> torch.Tensor:
+        """Push a step away from itself in proportion to how invalid it scored (reference :174-190)."""
+        q = result["validity_score"].to(step_hidden.dtype)
+        q = q.view(-1, *([1] * (step_hidden.dim() - 1)))
+        return step_hidden + (1.0 - q) * step_hidden * 0.1
+
+
+class YvVeriCoTReflector(nn.Module):
+    """verify -> reflect loop, at most ``max_reflections`` times (reference :192-230)."""
+
+    def __init__(self, verifier: YvVeriCoTStepVerifier, max_reflections: int = 3):
+        super().__init__()
+        self.verifier, self.max_reflections = verifier, max_reflections
+        self.register_buffer("rounds", torch.zeros((), dtype=torch.long))
+
+    def forward(self, step_hidden: torch.Tensor, context_hidden: Optional[torch.Tensor] = None,
+                step_text: str = "") -> Tuple[torch.Tensor, Dict[str, Any]]:
+        cur, n = step_hidden, 0
+        res = self.verifier(cur, context_hidden, step_text, return_details=True)
+        while not bool(res["is_valid"].all()) and n < self.max_reflections:
+            cur = self.verifier.compute_reflection(cur, res)
+            n += 1
+            res = self.verifier(cur, context_hidden, step_text, return_details=True)
+        self.rounds += 1
+        return cur, {"reflections": n, "final_valid": res["is_valid"], "final_validity": res["validity_score"],
+                     "round": int(self.rounds)}
+
+
+class YvAgenticEvolution(nn.Module):
+    """A population of copies of one model under selection and mutation (reference self_evolution.py:151-235):
+    score every agent on a task, keep the top fraction, overwrite the others with noisy copies of the survivors."""
+
+    def __init__(self, base_model: nn.Module, num_agents: int = 4, mutation_rate: float = 0.01,
+                 selection_pressure: float = 0.5):
+        super().__init__()
+        self.num_agents, self.mutation_rate, self.selection_pressure = num_agents, mutation_rate, selection_pressure
+        self.agents = nn.ModuleList([copy.deepcopy(base_model) for _ in range(num_agents)])
+        self.agent_scores = torch.zeros(num_agents)
+        self.generation = 0
+
+    @torch.no_grad()
+    def evaluate_agents(self, task_inputs: torch.Tensor, task_labels: torch.Tensor,
+                        score_fn: Optional[Callable[[torch.Tensor, torch.Tensor], float]] = None) -> torch.Tensor:
+        for i, agent in enumerate(self.agents):
+            out = agent(task_inputs)
+            out = out["logits"] if isinstance(out, dict) else out
+            if score_fn is not None:
+                self.agent_scores[i] = float(score_fn(out, task_labels))
+            elif out.dim() == task_labels.dim() + 1:
+                self.agent_scores[i] = float((out.argmax(-1) == task_labels).float().mean())
+            else:
+                self.agent_scores[i] = -float(F.mse_loss(out.float(), task_labels.float()))
+        return self.agent_scores
+
+    @torch.no_grad()
+    def evolve_population(self, generator: Optional[torch.Generator] = None) -> List[int]:
+        keep = max(1, int(self.num_agents * self.selection_pressure))
+        top = torch.topk(self.agent_scores, keep).indices.tolist()
+        for i in range(self.num_agents):
+            if i in top:
+                continue
+            parent = self.agents[top[i % keep]]
+            for pa, pp in zip(self.agents[i].parameters(), parent.parameters()):
+                noise = torch.randn(pp.shape, generator=generator).to(pp) * self.mutation_rate
+                pa.copy_(pp + noise)
+        self.generation += 1
+        return top
+
+    def best(self) -> nn.Module:
+        return self.agents[int(self.agent_scores.argmax())]
+
+
+class YvVerificationFactory:
+    """Module-level verification operations behind one class (reference verification.py:306-420)."""
+
+    @staticmethod
+    def detect_cot_failure_modes(reasoning_steps: List[str], final_answer: str) -> List[Tuple[str, float]]:
+        fails: List[Tuple[str, float]] = []
+        steps = [s.strip().lower() for s in reasoning_steps]
+        if len(steps) < 3 and len(final_answer.split()) > 5:
+            fails.append(("premature_conclusion", 0.7))
+        if any(a and b and (a in b or b in a) for i, a in enumerate(steps) for b in steps[i + 1:]):
+            fails.append(("circular_reasoning", 0.6))
+        if len(steps) > 5 and len(set(steps)) < 0.7 * len(steps):
+            fails.append(("hallucination", 0.5))
+        from .reasoning import YvReasoningTrace, YvVeriCoTVerifier
+        if steps and not YvVeriCoTVerifier().verify(YvReasoningTrace(steps=list(reasoning_steps), answer=final_answer)):
+            fails.append(("arithmetic_error", 0.9))
+        return fails
+
+    @staticmethod
+    def create(kind: str, hidden_size: int, **kw: Any) -> nn.Module:
+        kind = kind.lower()
+        if kind == "crv":
+            return YvCRV(hidden_size, **kw)
+        if kind == "otv":
+            return YvOTV(hidden_size, **kw)
+        if kind == "ares":
+            return YvARES(hidden_size, **kw)
+        if kind in ("vericot", "vericot_step"):
+            return YvVeriCoTStepVerifier(hidden_size, **kw)
+        if kind == "vericot_reflector":
+            return YvVeriCoTReflector(YvVeriCoTStepVerifier(hidden_size), **kw)
+        raise ValueError(f"unknown verifier kind {kind!r}")

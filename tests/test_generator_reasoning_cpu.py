@@ -1,0 +1,91 @@
+"""Content generator (image / audio / video heads over a Yv trunk) and the hidden-state VeriCoT pair, agentic
+evolution and the verification factory, on CPU."""
+import torch
+import torch.nn as nn
+
+
+def _gen_cfg():
+    from pisceslx_b200.models.multimodal import YvGenerationConfig
+    return YvGenerationConfig(hidden_size=64, num_heads=4, num_layers=1, max_sequence_length=64, image_size=32,
+                              num_inference_steps=4, audio_gen_duration=0.05, audio_gen_num_codebooks=2,
+                              audio_gen_codebook_size=32, video_gen_num_frames=3, latent_dim=16)
+
+
+def test_generator_registry_produces_every_modality_deterministically():
+    from pisceslx_b200.models.multimodal import YvGenerationModality, YvGeneratorFactory
+    g = YvGeneratorFactory.create_generator(_gen_cfg())
+    assert g.get_available_modalities() == ["image", "audio", "video"]
+    a = g.generate_from_text("a red square", "image", seed=1)
+    b = g.generate_from_text("a red square", YvGenerationModality.IMAGE, seed=1)
+    assert a.success and a.data.shape == (1, 3, 32, 32) and torch.equal(a.data, b.data)
+    assert float(a.data.abs().max()) <= 1.0 and a.metadata["backend"] == "yv-text-to-image"
+    assert not torch.equal(a.data, g.generate_from_text("a blue circle", "image", seed=1).data)       # conditioned
+    w = g.generate_from_text("beep", "audio")
+    assert w.success and w.data.shape == (1, 800) and w.metadata["sample_rate"] == 16000
+    v = g.generate_from_text("waves", "video", seed=2)
+    assert v.success and v.data.shape == (1, 3, 3, 32, 32)
+    bad = g.generate_from_text("x", "smell")
+    assert not bad.success and "no backend" in bad.error
+    assert set(g.get_capabilities()["backends"]) == {"image", "audio", "video"}
+
+
+def test_latent_denoiser_learns_a_prompt_conditioned_target():
+    from pisceslx_b200.models.multimodal import YvSelfDevelopedGenerator
+    torch.manual_seed(0)
+    m = YvSelfDevelopedGenerator(_gen_cfg())
+    params = list(m.denoiser.parameters()) + list(m.cond_proj.parameters())
+    opt = torch.optim.Adam(params, lr=3e-3)
+    target = torch.randn(2, 16)
+    first = None
+    for i in range(60):
+        torch.manual_seed(i % 4)                                 # a few fixed (t, noise) draws: the loss must go down
+        loss = m.diffusion_training_loss(["alpha", "beta"], target)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        first = first if first is not None else float(loss)
+    assert float(loss) < 0.7 * first
+
+
+def test_vericot_step_verifier_reflector_and_factory():
+    from pisceslx_b200.models.reasoning_verify import (YvVeriCoTReflector, YvVeriCoTStepVerifier,
+                                                       YvVerificationFactory)
+    torch.manual_seed(0)
+    ver = YvVeriCoTStepVerifier(32)
+    h, ctx = torch.randn(3, 5, 32), torch.randn(3, 7, 32)
+    assert torch.allclose(ver(h)["validity_score"], torch.full((3,), 0.5))          # no context: neutral
+    r = ver(h, ctx, step_text="2 + 2 = 5")
+    assert r["symbolic_score"] == 0.0 and float(r["combined_score"].max()) < 0.51    # the wrong sum pulls it down
+    assert ver(h, ctx, step_text="2 + 2 = 4")["symbolic_score"] == 1.0
+    chain = ver.verify_chain([torch.randn(1, 32) for _ in range(4)], ["1 + 1 = 2", "so", "3 * 3 = 9", "4 - 1 = 2"])
+    assert len(chain["steps"]) == 4 and chain["first_invalid"] is not None and not chain["all_valid"]
+    with torch.no_grad():                                       # force "invalid" so that the reflector has to act
+        ver.quality_estimator[2].bias.fill_(-10.0)
+        ver.quality_estimator[2].weight.zero_()
+    out, info = YvVeriCoTReflector(ver, max_reflections=2)(h, ctx)
+    assert info["reflections"] == 2 and not bool(info["final_valid"].any()) and not torch.equal(out, h)
+    assert torch.allclose(out, h * 1.1 ** 2, atol=1e-3)
+    modes = dict(YvVerificationFactory.detect_cot_failure_modes(["x = 1", "x = 1 again"], "the answer is definitely one hundred"))
+    assert "premature_conclusion" in modes and "circular_reasoning" in modes
+    assert "arithmetic_error" in dict(YvVerificationFactory.detect_cot_failure_modes(["2 * 3 = 7"], "7"))
+    assert isinstance(YvVerificationFactory.create("vericot_reflector", 16), YvVeriCoTReflector)
+
+
+def test_agentic_evolution_selects_and_mutates():
+    from pisceslx_b200.models.reasoning_verify import YvAgenticEvolution
+    torch.manual_seed(0)
+    base = nn.Linear(4, 3)
+    evo = YvAgenticEvolution(base, num_agents=4, mutation_rate=0.5, selection_pressure=0.5)
+    g = torch.Generator().manual_seed(1)
+    for a in list(evo.agents)[1:]:                              # spread the population out
+        for p in a.parameters():
+            p.data.add_(torch.randn(p.shape, generator=g))
+    x = torch.randn(64, 4)
+    y = (x @ torch.randn(4, 3)).argmax(-1)
+    best0 = float(evo.evaluate_agents(x, y).max())
+    for _ in range(15):
+        evo.evaluate_agents(x, y)
+        top = evo.evolve_population(g)
+        assert len(top) == 2
+    assert float(evo.evaluate_agents(x, y).max()) >= best0 and evo.generation == 15
+    assert evo.best() is evo.agents[int(evo.agent_scores.argmax())]
