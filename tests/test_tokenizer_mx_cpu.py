@@ -66,3 +66,29 @@ def test_mx_reference_quantisation_and_chunk_layout():
     assert int(c[1, 0, (127 % 32) * 16 + (127 // 32) * 4]) == 127          # rows past the end hold scale 1
     q2, c2 = q8.quantize_mx(x)                                            # CPU path of the public entry
     assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(c2, c)
+
+
+def test_quartet_linear_stores_four_bits_and_trains_through_stochastic_rounding():
+    import torch.nn as nn
+    from pisceslx_b200.quant.fp4 import PiscesLxQuartetLinear, PiscesLxQuartetTrainer, pack_fp4, unpack_fp4
+    torch.manual_seed(0)
+    q = torch.tensor([0.0, -0.5, 6.0, -3.0, 1.5])
+    assert torch.equal(unpack_fp4(pack_fp4(q), 5), q) and pack_fp4(q).numel() == 3
+    lin = PiscesLxQuartetLinear(32, 16, seed=1)
+    assert lin.storage_bytes() == 32 * 16 // 2 + 32 * 16 // 16 * 4           # half a byte per weight + block scales
+    w = lin.dequantized()
+    lin.apply_update(torch.full_like(w, 1e-4))                              # far below one fp4 step: moves in expectation
+    moved = (lin.dequantized() - w)
+    assert float(moved.abs().max()) > 0 and float((moved != 0).float().mean()) < 0.5
+    net = nn.Sequential(nn.Linear(8, 32), nn.ReLU(), nn.Linear(32, 1))
+    tr = PiscesLxQuartetTrainer(net)
+    assert tr.converted == 2 and tr.get_compression_ratio() > 3.0
+    x = torch.randn(256, 8)
+    y = x[:, :1] * 2 - x[:, 1:2]
+    first = None
+    for _ in range(300):
+        loss = (net(x) - y).pow(2).mean()
+        loss.backward()
+        tr.step(0.05)
+        first = first if first is not None else float(loss.detach())
+    assert float(loss.detach()) < 0.1 * first
