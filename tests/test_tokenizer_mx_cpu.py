@@ -76,10 +76,13 @@ def test_quartet_linear_stores_four_bits_and_trains_through_stochastic_rounding(
     assert torch.equal(unpack_fp4(pack_fp4(q), 5), q) and pack_fp4(q).numel() == 3
     lin = PiscesLxQuartetLinear(32, 16, seed=1)
     assert lin.storage_bytes() == 32 * 16 // 2 + 32 * 16 // 16 * 4           # half a byte per weight + block scales
-    w = lin.dequantized()
-    lin.apply_update(torch.full_like(w, 1e-4))                              # far below one fp4 step: moves in expectation
-    moved = (lin.dequantized() - w)
-    assert float(moved.abs().max()) > 0 and float((moved != 0).float().mean()) < 0.5
+    target = torch.randn(16, 32) * 0.02                                     # stochastic rounding is unbiased:
+    acc = torch.zeros_like(target)                                          # the mean of many stores approaches the target
+    for _ in range(200):
+        lin.store(target)
+        acc += lin.dequantized()
+    one = (lin.dequantized() - target).abs().mean()
+    assert float((acc / 200 - target).abs().mean()) < 0.25 * float(one)
     net = nn.Sequential(nn.Linear(8, 32), nn.ReLU(), nn.Linear(32, 1))
     tr = PiscesLxQuartetTrainer(net)
     assert tr.converted == 2 and tr.get_compression_ratio() > 3.0
