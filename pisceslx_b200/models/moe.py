@@ -26,11 +26,21 @@ from ..ops import moe as moe_ops
 from ..ops import reference as ref
 
 
-def capacity_mask(weights: torch.Tensor, idx: torch.Tensor, probs: torch.Tensor, capacity: int) -> torch.Tensor:
+def capacity_mask(weights: torch.Tensor, idx: torch.Tensor, probs: torch.Tensor, capacity: int,
+                  counts: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Vectorised capacity drop (no host sync): inside every expert keep the ``capacity`` assignments with
     the highest routing probability, zero the rest and renormalise each row."""
     T, k = idx.shape
     E = probs.shape[-1]
+    if weights.is_cuda:
+        # kernel path: exact selection per expert (radix select), then renormalisation through the kept weights so
+        # that the gradient reaches them as in the eager form below
+        if counts is None:
+            counts = torch.bincount(idx.flatten().long(), minlength=E)
+        _, keep = moe_ops.capacity_mask(weights, idx, probs, counts, capacity)
+        w = weights * keep.to(weights.dtype)
+        tot = w.sum(-1, keepdim=True)
+        return torch.where(tot > 0, w / tot.clamp_min(1e-20), torch.zeros_like(w))
     e = idx.flatten().long()
     score = probs.gather(-1, idx.long()).flatten()
     # sort by expert, then by descending score; rank inside the expert = position - segment start
@@ -109,7 +119,7 @@ class YvStableMoEGate(nn.Module):
         weights, idx, counts, probs = moe_ops.gate_topk(logits, bias, self.top_k, self.bias_in_combine,
                                                         self.renorm_mode)
         if self.drop_tokens:
-            weights = capacity_mask(weights, idx, probs, self.capacity(T))
+            weights = capacity_mask(weights, idx, probs, self.capacity(T), counts)
         aux = logits.new_zeros(())
         if not self.aux_loss_free:
             p_mean = torch.softmax(logits.float(), -1).mean(0)
@@ -159,7 +169,7 @@ class YvMoEGate(YvStableMoEGate):
         weights, idx, counts, probs = moe_ops.gate_topk(logits, bias, self.top_k, self.bias_in_combine,
                                                         self.renorm_mode)
         if self.drop_tokens:
-            weights = capacity_mask(weights, idx, probs, self.capacity(T))
+            weights = capacity_mask(weights, idx, probs, self.capacity(T), counts)
         aux = logits.new_zeros(())
         if not self.aux_loss_free:
             p_mean = torch.softmax(logits.float(), -1).mean(0)

@@ -484,6 +484,29 @@ void moe_plan(const Tensor& counts, Tensor seg_offsets, Tensor tile_expert, Tens
            "moe_plan");
 }
 
+void moe_rank(const Tensor& idx, const Tensor& seg_offsets, Tensor row_map) {
+  check_i32(idx, "idx"); check_i32(seg_offsets, "seg_offsets"); check_i32(row_map, "row_map");
+  TORCH_CHECK(idx.is_contiguous() && row_map.is_contiguous() && row_map.numel() == idx.numel(), "moe_rank: idx / row_map [T,k]");
+  const c10::cuda::CUDAGuard guard(idx.device());
+  check_rc(yv::launch_moe_rank(idx.data_ptr<int>(), seg_offsets.data_ptr<int>(), row_map.data_ptr<int>(), idx.numel(),
+                               static_cast<int>(seg_offsets.numel() - 1), cur_stream()), "moe_rank");
+}
+
+void moe_capacity_mask(const Tensor& weights, const Tensor& idx, const Tensor& probs, const Tensor& counts, Tensor keep,
+                       Tensor out, int64_t capacity) {
+  check_f32(weights, "weights"); check_i32(idx, "idx"); check_f32(probs, "probs"); check_i32(counts, "counts");
+  check_f32(out, "out");
+  TORCH_CHECK(keep.is_cuda() && keep.scalar_type() == at::kByte && keep.numel() == idx.numel(), "moe_capacity_mask: keep uint8 [T,k]");
+  TORCH_CHECK(weights.is_contiguous() && idx.is_contiguous() && probs.is_contiguous() && out.is_contiguous() &&
+              weights.sizes() == idx.sizes() && out.sizes() == idx.sizes() && probs.size(0) == idx.size(0) &&
+              probs.size(1) == counts.numel(), "moe_capacity_mask: weights/idx/out [T,k], probs [T,E], counts [E]");
+  const c10::cuda::CUDAGuard guard(idx.device());
+  check_rc(yv::launch_moe_capacity_mask(weights.data_ptr<float>(), idx.data_ptr<int>(), probs.data_ptr<float>(),
+                                        counts.data_ptr<int>(), keep.data_ptr<uint8_t>(), out.data_ptr<float>(), idx.size(0),
+                                        static_cast<int>(idx.size(1)), static_cast<int>(counts.numel()),
+                                        static_cast<int>(capacity), cur_stream()), "moe_capacity_mask");
+}
+
 void moe_permute(const Tensor& x, const Tensor& idx, const c10::optional<Tensor>& cursor, Tensor row_map, Tensor xp) {
   check_bf16(x, "x"); check_i32(idx, "idx"); check_i32(row_map, "row_map"); check_bf16(xp, "xp");
   TORCH_CHECK(x.is_contiguous() && xp.is_contiguous(), "moe_permute: contiguous expected");

@@ -371,6 +371,111 @@ __global__ void gate_bias_update_kernel(float* __restrict__ bias, const int* __r
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// deterministic row map and capacity mask: one CTA per expert walks all assignments in order
+// ---------------------------------------------------------------------------------------------
+// Exclusive prefix of `flag` over the 256 threads of the CTA in thread order, and the CTA's total.
+__device__ __forceinline__ int block_scan_flags(bool flag, int* s_warp, int& total) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const unsigned m = __ballot_sync(0xFFFFFFFFu, flag);
+  if (lane == 0) s_warp[w] = __popc(m);
+  __syncthreads();
+  int before = 0, all = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = s_warp[i];
+    before += i < w ? c : 0;
+    all += c;
+  }
+  __syncthreads();
+  total = all;
+  return before + __popc(m & ((1u << lane) - 1u));
+}
+
+// row_map[a] = seg_offsets[e] + (number of earlier assignments of expert e), a = t * k + j in token order: the
+// stable order a sort by expert would give, without the sort.  grid = E, block = 256.
+__global__ void moe_rank_kernel(const int* __restrict__ idx, const int* __restrict__ seg_offsets,
+                                int* __restrict__ row_map, int64_t n) {
+  __shared__ int s_warp[8];
+  const int e = blockIdx.x;
+  int running = seg_offsets[e];
+  for (int64_t base = 0; base < n; base += 256) {
+    const int64_t a = base + threadIdx.x;
+    const bool mine = a < n && idx[a] == e;
+    int total;
+    const int before = block_scan_flags(mine, s_warp, total);
+    if (mine) row_map[a] = running + before;
+    running += total;
+  }
+}
+
+// keep[a] = 1 when assignment a is among the `capacity` highest routing probabilities of its expert (ties broken
+// by token order), else 0.  An exact radix select over the probabilities' bit patterns (non-negative floats order
+// like their bits) finds the threshold in four passes; a last ordered pass settles the ties.  grid = E, block = 256.
+__global__ void moe_capacity_keep_kernel(const int* __restrict__ idx, const float* __restrict__ probs,
+                                         const int* __restrict__ counts, uint8_t* __restrict__ keep, int64_t n, int k,
+                                         int E, int capacity) {
+  __shared__ int s_warp[8];
+  __shared__ int s_hist[256];
+  __shared__ unsigned s_prefix;
+  __shared__ int s_remaining;
+  const int e = blockIdx.x;
+  const bool all_fit = counts[e] <= capacity;
+  unsigned thr = 0u;
+  int ties_kept = 0;
+  if (!all_fit) {
+    if (threadIdx.x == 0) { s_prefix = 0u; s_remaining = capacity; }
+    __syncthreads();
+    for (int pass = 3; pass >= 0; --pass) {
+      s_hist[threadIdx.x] = 0;
+      __syncthreads();
+      const unsigned prefix = s_prefix;
+      const unsigned hi_mask = pass == 3 ? 0u : (0xFFFFFFFFu << (8 * (pass + 1)));
+      for (int64_t a = threadIdx.x; a < n; a += 256) {
+        if (idx[a] != e) continue;
+        const unsigned key = __float_as_uint(fmaxf(probs[(a / k) * E + e], 0.f));
+        if ((key & hi_mask) == (prefix & hi_mask)) atomicAdd(&s_hist[(key >> (8 * pass)) & 0xFFu], 1);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int rem = s_remaining, b = 255;
+        for (; b > 0; --b) {
+          if (s_hist[b] >= rem) break;
+          rem -= s_hist[b];
+        }
+        s_remaining = rem;                       // how many of the chosen byte's group are still to be kept
+        s_prefix = prefix | (static_cast<unsigned>(b) << (8 * pass));
+      }
+      __syncthreads();
+    }
+    thr = s_prefix;
+    ties_kept = s_remaining;
+  }
+  int tie_running = 0;
+  for (int64_t base = 0; base < n; base += 256) {
+    const int64_t a = base + threadIdx.x;
+    const bool mine = a < n && idx[a] == e;
+    unsigned key = 0u;
+    if (mine && !all_fit) key = __float_as_uint(fmaxf(probs[(a / k) * E + e], 0.f));
+    const bool tie = mine && !all_fit && key == thr;
+    int total;
+    const int before = block_scan_flags(tie, s_warp, total);
+    if (mine) keep[a] = (all_fit || key > thr || (tie && tie_running + before < ties_kept)) ? 1 : 0;
+    tie_running += total;
+  }
+}
+
+// weights[t, :] <- weights * keep, renormalised to sum 1 (all zero when every assignment of the token was dropped)
+__global__ void moe_capacity_renorm_kernel(const float* __restrict__ w, const uint8_t* __restrict__ keep,
+                                           float* __restrict__ out, int64_t tokens, int k) {
+  const int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (t >= tokens) return;
+  float s = 0.f;
+  for (int j = 0; j < k; ++j) s += keep[t * k + j] ? w[t * k + j] : 0.f;
+  const float inv = s > 0.f ? 1.f / fmaxf(s, 1e-20f) : 0.f;
+  for (int j = 0; j < k; ++j) out[t * k + j] = keep[t * k + j] ? w[t * k + j] * inv : 0.f;
+}
+
 }  // namespace
 
 #define YV_BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
@@ -402,6 +507,20 @@ int launch_moe_plan(const int* counts, int* seg_offsets, int* tile_expert, int* 
                     int max_tiles, cudaStream_t stream) {
   if (E > 256) return -1;
   moe_plan_kernel<<<1, 256, 0, stream>>>(counts, seg_offsets, tile_expert, num_m_tiles, cursor, E, max_tiles);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_moe_rank(const int* idx, const int* seg_offsets, int* row_map, int64_t n, int E, cudaStream_t stream) {
+  if (n <= 0 || E <= 0) return 0;
+  moe_rank_kernel<<<E, 256, 0, stream>>>(idx, seg_offsets, row_map, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_moe_capacity_mask(const float* weights, const int* idx, const float* probs, const int* counts, uint8_t* keep,
+                             float* out, int64_t tokens, int k, int E, int capacity, cudaStream_t stream) {
+  if (tokens <= 0 || E <= 0) return 0;
+  moe_capacity_keep_kernel<<<E, 256, 0, stream>>>(idx, probs, counts, keep, tokens * k, k, E, capacity);
+  moe_capacity_renorm_kernel<<<static_cast<unsigned>((tokens + 255) / 256), 256, 0, stream>>>(weights, keep, out, tokens, k);
   return static_cast<int>(cudaGetLastError());
 }
 

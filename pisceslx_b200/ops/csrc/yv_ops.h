@@ -142,6 +142,12 @@ int launch_gate_topk_bwd(const float* dweights, const float* probs, const int* i
 int launch_moe_plan(const int* counts, int* seg_offsets, int* tile_expert, int* num_m_tiles, int* cursor, int E,
                     int max_tiles, cudaStream_t stream);
 // scatter token rows into expert-sorted order; row_map[t*k+j] = destination row; pad rows are zero-filled
+// Deterministic rows: row_map[t*k+j] = seg_offsets[e] + rank of the assignment inside expert e in token order.
+int launch_moe_rank(const int* idx, const int* seg_offsets, int* row_map, int64_t n, int E, cudaStream_t stream);
+// Capacity rule: per expert keep the `capacity` assignments with the highest probability (ties by token order);
+// keep [tokens*k] uint8 scratch, out [tokens,k] = renormalised weights (zeros for fully dropped tokens).
+int launch_moe_capacity_mask(const float* weights, const int* idx, const float* probs, const int* counts, uint8_t* keep,
+                             float* out, int64_t tokens, int k, int E, int capacity, cudaStream_t stream);
 int launch_moe_permute(const void* x, const int* idx, int* cursor, int* row_map, void* xp, int64_t tokens, int k,
                        int cols, cudaStream_t stream);
 int launch_moe_zero_pad(void* xp, const int* seg_offsets, const int* counts, int E, int cols, cudaStream_t stream);

@@ -98,14 +98,9 @@ def permute_tokens(x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor, num
     xp = torch.empty(max_rows, H, dtype=_BF16, device=dev)
     row_map = torch.empty(T, k, dtype=torch.int32, device=dev)
     if deterministic:
-        # stable sort by expert: assignment order inside an expert follows token order
-        flat = idx.flatten().long()
-        order = torch.sort(flat, stable=True).indices
-        rank = torch.empty_like(order)
-        rank[order] = torch.arange(order.numel(), device=dev)
-        starts = torch.cumsum(counts.long(), 0) - counts.long()
-        row = seg[:-1].long()[flat] + (rank - starts[flat])
-        row_map.copy_(row.view(T, k).int())
+        # assignment order inside an expert follows token order (what a stable sort by expert would give): one CTA per
+        # expert counts its assignments in order
+        K.moe_rank(idx.contiguous(), seg, row_map)
         K.moe_permute(x, idx, None, row_map, xp)
     else:
         K.moe_permute(x, idx, cursor, row_map, xp)
@@ -240,6 +235,19 @@ def moe_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: t
     # without autograd (inference) nothing reads what the pad rows of the expert segments produce: skip zeroing them
     return _MoEExpertsFn.apply(x.to(_BF16), w13, w2, weights, idx.int(), counts.int(), deterministic,
                                torch.is_grad_enabled(), fp8)
+
+
+def capacity_mask(weights: torch.Tensor, idx: torch.Tensor, probs: torch.Tensor, counts: torch.Tensor,
+                  capacity: int) -> torch.Tensor:
+    """Capacity rule on the GPU: inside every expert keep the ``capacity`` assignments with the highest routing
+    probability (ties by token order), zero the others and renormalise each token's weights.  No autograd: the
+    result replaces the gate's weights in the forward value, gradients flow through the kept weights' own graph in
+    the caller."""
+    keep = torch.empty(idx.shape, dtype=torch.uint8, device=idx.device)
+    out = torch.empty(idx.shape, dtype=torch.float32, device=idx.device)
+    _k().moe_capacity_mask(weights.detach().float().contiguous(), idx.int().contiguous(), probs.detach().float().contiguous(),
+                           counts.int().contiguous(), keep, out, int(capacity))
+    return out, keep
 
 
 def update_gate_bias(bias: torch.Tensor, counts: torch.Tensor, rate: float, clamp: float = 2.0) -> None:

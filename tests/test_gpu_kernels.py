@@ -591,3 +591,42 @@ def test_patchify(Y):
     out = torch.empty(2 * 4 * 5, 640, device=DEV, dtype=torch.bfloat16)
     Y.patchify(img, out, 14, mean, std)
     assert rel(out, ref.patchify(img, 14, mean, std, 640)) < 4e-3
+
+
+def test_moe_rank_kernel_gives_stable_sort_order(Y):
+    torch.manual_seed(31)
+    T, k, E = 3001, 6, 64
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    counts = torch.bincount(idx.flatten().long(), minlength=E).int()
+    seg = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    te = torch.empty((T * k + E * 127 + 127) // 128, dtype=torch.int32, device=DEV)
+    nt, cur = torch.empty(1, dtype=torch.int32, device=DEV), torch.empty(E, dtype=torch.int32, device=DEV)
+    Y.moe_plan(counts, seg, te, nt, cur)
+    row_map = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    Y.moe_rank(idx, seg, row_map)
+    flat = idx.flatten().long()
+    order = torch.sort(flat, stable=True).indices
+    rank = torch.empty_like(order)
+    rank[order] = torch.arange(order.numel(), device=DEV)
+    starts = torch.cumsum(counts.long(), 0) - counts.long()
+    ref_rows = seg[:-1].long()[flat] + (rank - starts[flat])
+    assert torch.equal(row_map.flatten().long(), ref_rows)
+
+
+@pytest.mark.parametrize("capacity", [1, 40, 300, 100000])
+def test_moe_capacity_mask_kernel_matches_sorted_reference(capacity):
+    from pisceslx_b200.models.moe import capacity_mask
+    torch.manual_seed(capacity)
+    T, k, E = 2000, 4, 16
+    probs = torch.softmax(torch.randn(T, E, device=DEV) * 2, -1)
+    probs[::7] = probs[0]                                        # many exact ties: token order must decide
+    idx = probs.topk(k, -1).indices.int()
+    w = probs.gather(-1, idx.long())
+    w = (w / w.sum(-1, keepdim=True)).requires_grad_(True)
+    got = capacity_mask(w, idx, probs, capacity)
+    ref_w = capacity_mask(w.detach().cpu(), idx.cpu(), probs.cpu(), capacity)          # eager sort-based form
+    assert torch.allclose(got.detach().cpu(), ref_w, atol=1e-6)
+    kept_per_expert = torch.bincount(idx.flatten().long()[(got.detach() > 0).flatten()], minlength=E)
+    assert int(kept_per_expert.max()) <= capacity
+    got.sum().backward()
+    assert w.grad is not None and torch.isfinite(w.grad).all()
