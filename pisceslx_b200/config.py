@@ -227,6 +227,7 @@ class YvConfig:
     expert_parallel: int = 1
     pipeline_parallel: int = 1
     context_parallel: int = 1
+    context_parallel_mode: str = "allgather"   # "ring": K/V blocks travel round the ranks (O(S/cp) K/V memory per rank)
     sequence_parallel: bool = True
     zero_stage: int = 1
     fused_comm: bool = True                 # peer-memory fused kernels (False = NCCL baseline mode)

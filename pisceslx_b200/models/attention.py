@@ -198,8 +198,15 @@ class YvAttention(nn.Module):
             k = ref.apply_rope(k.reshape(T, self.hk, self.d), ctx.cos, ctx.sin, ctx.positions, self.rot_dim).reshape(T, nk)
         cu = ctx.cu_seqlens.tolist()
         outs = []
+        ring = getattr(self.cfg, "context_parallel_mode", "allgather") == "ring"
         for b in range(len(cu) - 1):
             sl = slice(cu[b], cu[b + 1])
+            if ring:
+                # blocks of K / V travel round the ranks in both passes: no rank ever holds the whole sequence's keys
+                outs.append(cp.ring_attention_train(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(),
+                                                    ctx.cp_group, self.hq, self.hk, self.d, causal=ctx.causal,
+                                                    scale=self.scale))
+                continue
             outs.append(cp.allgather_attention(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), ctx.cp_group,
                                                self.hq, self.hk, self.d, causal=ctx.causal, scale=self.scale))
         return torch.cat(outs, 0).to(qkv.dtype)

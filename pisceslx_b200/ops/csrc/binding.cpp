@@ -353,6 +353,17 @@ void gemm_fp8(const Tensor& a, const Tensor& b, Tensor c, const Tensor& out_scal
   check_rc(yv::launch_gemm(g, cur_stream()), "gemm_fp8");
 }
 
+void attn_merge(Tensor o_acc, Tensor lse_acc, const Tensor& o_b, const Tensor& lse_b) {
+  check_f32(o_acc, "o_acc"); check_f32(lse_acc, "lse_acc"); check_f32(o_b, "o_b"); check_f32(lse_b, "lse_b");
+  TORCH_CHECK(o_acc.is_contiguous() && lse_acc.is_contiguous() && o_b.is_contiguous() && lse_b.is_contiguous() &&
+              o_acc.sizes() == o_b.sizes() && lse_acc.sizes() == lse_b.sizes() &&
+              o_acc.numel() == lse_acc.numel() * o_acc.size(-1), "attn_merge: o [..., d] and lse [...] of both partials");
+  const c10::cuda::CUDAGuard guard(o_acc.device());
+  check_rc(yv::launch_attn_merge(o_acc.data_ptr<float>(), lse_acc.data_ptr<float>(), o_b.data_ptr<float>(),
+                                 lse_b.data_ptr<float>(), lse_acc.numel(), static_cast<int>(o_acc.size(-1)), cur_stream()),
+           "attn_merge");
+}
+
 // x [rows, K] bf16 -> q [rows, K] e4m3 + sf uint8 [ceil(rows/128), K/128, 512] (one e8m0 scale per 32 elements)
 void mx_quantize(const Tensor& x, Tensor q, Tensor sf) {
   check_bf16(x, "x"); check_fp8(q, "q");

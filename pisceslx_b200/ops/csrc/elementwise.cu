@@ -580,6 +580,31 @@ __global__ void fp8_quantize_kernel(const uint4* __restrict__ x, const float* __
   }
 }
 
+// Running attention partial <- merged with another partial over a disjoint key set (ring / context parallel attention):
+// lse = log(exp(lse_a) + exp(lse_b)), o = o_a * exp(lse_a - lse) + o_b * exp(lse_b - lse); rows with no keys on
+// either side (lse = -inf) keep zeros.  One warp per (token, head) row of d floats.
+__global__ void attn_merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc, const float* __restrict__ o_b,
+                                  const float* __restrict__ lse_b, int64_t rows, int d) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  if (row >= rows) return;
+  const float la = lse_acc[row], lb = lse_b[row];
+  const float m = fmaxf(la, lb);
+  float wa = 0.f, wb = 0.f, l = m;
+  if (m > -INFINITY) {
+    const float ea = __expf(la - m), eb = __expf(lb - m);
+    l = m + __logf(ea + eb);
+    wa = ea / (ea + eb);
+    wb = eb / (ea + eb);
+  }
+  for (int c = lane; c < d; c += 32) {
+    const int64_t i = row * d + c;
+    o_acc[i] = o_acc[i] * wa + o_b[i] * wb;
+  }
+  __syncwarp();
+  if (lane == 0) lse_acc[row] = l;
+}
+
 // Block-scaled (MX) quantisation: four lanes share one 32-element block (8 elements each).
 __global__ void mx_quantize_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, uint8_t* __restrict__ sf,
                                    int64_t n8, int K) {
@@ -630,6 +655,14 @@ __global__ void mx_quantize_kernel(const uint4* __restrict__ x, uint2* __restric
   }
 }
 }  // namespace
+
+int launch_attn_merge(float* o_acc, float* lse_acc, const float* o_b, const float* lse_b, int64_t rows, int d,
+                      cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int64_t threads = rows * 32;
+  attn_merge_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(o_acc, lse_acc, o_b, lse_b, rows, d);
+  return static_cast<int>(cudaGetLastError());
+}
 
 int launch_mx_quantize(const void* x_bf16, void* q_e4m3, void* sf, int64_t rows, int K, cudaStream_t stream) {
   if (rows <= 0) return 0;

@@ -105,6 +105,10 @@ int launch_pq_film(void* const* table_ptrs, int world, const int* idx, const voi
                    void* e_out, int64_t tokens, int C, int64_t rows_per_rank, int D, int H, uint32_t* status,
                    cudaStream_t stream);
 
+// In-place merge of two attention partials over disjoint key sets: o_acc / o_b [rows, d] fp32, lse [rows] fp32.
+int launch_attn_merge(float* o_acc, float* lse_acc, const float* o_b, const float* lse_b, int64_t rows, int d,
+                      cudaStream_t stream);
+
 // Block-scaled quantisation of x [rows, K] (bf16, K % 128 == 0): q [rows, K] e4m3 and the scale chunks
 // [ceil(rows / 128)][K / 128][512] described at GemmArgs::sfa.  Scale of a 32-element block = the smallest power of two that
 // brings the block's largest magnitude to at most 448, stored as a biased exponent byte; rows past `rows` in the last tile get scale 2^0.

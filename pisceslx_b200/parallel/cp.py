@@ -125,6 +125,121 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group: Any
     return o_acc.reshape(L, hq * d).to(q.dtype)
 
 
+# --------------------------------------------------------------------------------------------------
+# differentiable ring attention
+# --------------------------------------------------------------------------------------------------
+def _ring_exchange(tensors: List[torch.Tensor], group: Any, r: int, W: int) -> Tuple[List[torch.Tensor], list]:
+    """Post the sends of ``tensors`` to rank r+1 and the receives of their successors from rank r-1."""
+    recv = [torch.empty_like(t) for t in tensors]
+    nxt, prv = dist.get_global_rank(group, (r + 1) % W), dist.get_global_rank(group, (r - 1) % W)
+    ops = [dist.P2POp(dist.isend, t, nxt, group) for t in tensors] + [dist.P2POp(dist.irecv, t, prv, group) for t in recv]
+    return recv, dist.batch_isend_irecv(ops)
+
+
+def _merge_into(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor):
+    """Running result (fp32 [L, hq, d], [L, hq]) <- merged with one block's partial.  On the GPU one kernel does the
+    log-sum-exp, the two weights and the weighted sum in place."""
+    if o_acc.is_cuda:
+        kernels().attn_merge(o_acc, lse_acc, o_b.contiguous(), lse_b.contiguous())
+        return o_acc, lse_acc
+    return merge_partials(o_acc, lse_acc, o_b, lse_b)
+
+
+def _block_backward(do, q, k, v, o, lse, hq, hk, d, causal, scale):
+    """Gradients of ONE key/value block given the GLOBAL output and log-sum-exp of the local queries:
+    p = exp(s - lse), dv = p^T do, ds = p * (do v^T - rowsum(do * o)), dq = ds k, dk = ds^T q."""
+    L, Lk = q.shape[0], k.shape[0]
+    if q.is_cuda:
+        K = kernels()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty(hq, L, dtype=torch.float32, device=q.device)
+        cq = torch.tensor([0, L], dtype=torch.int32, device=q.device)
+        ck = torch.tensor([0, Lk], dtype=torch.int32, device=q.device)
+        K.attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, cq, ck, L, Lk, hq, hk, d, causal, scale, status_word(q.device))
+        return dq.float(), dk.float(), dv.float()
+    g = hq // hk
+    qq = q.float().view(L, hq, d).transpose(0, 1)
+    kk = k.float().view(Lk, hk, d).transpose(0, 1).repeat_interleave(g, 0)
+    vv = v.float().view(Lk, hk, d).transpose(0, 1).repeat_interleave(g, 0)
+    dd = do.float().view(L, hq, d).transpose(0, 1)
+    oo = o.float().view(L, hq, d).transpose(0, 1)
+    s_ = qq @ kk.transpose(1, 2) * scale
+    if causal:
+        i = torch.arange(L).unsqueeze(1)
+        j = torch.arange(Lk).unsqueeze(0)
+        s_ = s_.masked_fill(j > i + (Lk - L), float("-inf"))
+    p_ = torch.nan_to_num(torch.exp(s_ - lse.unsqueeze(-1)), nan=0.0)             # lse [hq, L]
+    dv = (p_.transpose(1, 2) @ dd).view(hk, g, Lk, d).sum(1)
+    ds = p_ * (dd @ vv.transpose(1, 2) - (dd * oo).sum(-1, keepdim=True)) * scale
+    dq = ds @ kk
+    dk = (ds.transpose(1, 2) @ qq).view(hk, g, Lk, d).sum(1)
+    return (dq.transpose(0, 1).reshape(L, hq * d), dk.transpose(0, 1).reshape(Lk, hk * d),
+            dv.transpose(0, 1).reshape(Lk, hk * d))
+
+
+class _RingAttention(torch.autograd.Function):
+    """Exact causal / full attention over a sequence sharded contiguously over ``group`` with O(L) key/value memory
+    per rank in BOTH directions.  Forward: K/V blocks travel round the ring, partials are merged through the
+    log-sum-exp; only q, the local k/v, the bf16 output and the log-sum-exp are kept.  Backward: the blocks travel
+    again together with their dK/dV accumulators; every rank adds the contribution of its queries to the block in
+    hand (recomputing p from the saved global log-sum-exp), and after W hops each accumulator is back at its owner."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, group, hq, hk, d, causal, scale):
+        W, r = dist.get_world_size(group), dist.get_rank(group)
+        L = q.shape[0]
+        q, cur_k, cur_v = q.contiguous(), k.contiguous(), v.contiguous()
+        o_acc = lse_acc = None
+        for step in range(W):
+            src = (r - step) % W
+            nxt = _ring_exchange([cur_k, cur_v], group, r, W) if step + 1 < W else None
+            if not causal or src <= r:
+                o_b, lse_b = _attend_block(q, cur_k, cur_v, hq, hk, d, causal and src == r, scale)
+                if o_acc is None:
+                    o_acc, lse_acc = o_b.contiguous(), lse_b.contiguous()
+                else:
+                    o_acc, lse_acc = _merge_into(o_acc, lse_acc, o_b, lse_b)
+            if nxt is not None:
+                for rq in nxt[1]:
+                    rq.wait()
+                cur_k, cur_v = nxt[0]
+        o = o_acc.reshape(L, hq * d).to(q.dtype)
+        ctx.save_for_backward(q, k.contiguous(), v.contiguous(), o, lse_acc.t().contiguous())       # lse as [hq, L]
+        ctx.cfg = (group, hq, hk, d, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        group, hq, hk, d, causal, scale = ctx.cfg
+        W, r = dist.get_world_size(group), dist.get_rank(group)
+        do = do.contiguous().to(q.dtype)
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        cur = [k, v, torch.zeros(k.shape, dtype=torch.float32, device=k.device),
+               torch.zeros(v.shape, dtype=torch.float32, device=v.device)]
+        for step in range(W):
+            src = (r - step) % W
+            if not causal or src <= r:
+                dq_b, dk_b, dv_b = _block_backward(do, q, cur[0], cur[1], o, lse, hq, hk, d, causal and src == r, scale)
+                dq += dq_b
+                cur[2] = cur[2] + dk_b
+                cur[3] = cur[3] + dv_b
+            # every hop moves the block and its gradient accumulators on; the last hop brings them home
+            send = cur if step + 1 < W else cur[2:]
+            recv, reqs = _ring_exchange([t.contiguous() for t in send], group, r, W)
+            for rq in reqs:
+                rq.wait()
+            cur = recv if step + 1 < W else [None, None] + recv
+        return dq.to(q.dtype), cur[2].to(k.dtype), cur[3].to(v.dtype), None, None, None, None, None, None
+
+
+def ring_attention_train(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group: Any, hq: int, hk: int, d: int,
+                         causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
+    """Differentiable ring attention: q [L, hq*d], k/v [L, hk*d] are this rank's contiguous chunk of one sequence."""
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    return _RingAttention.apply(q, k, v, group, hq, hk, d, causal, scale)
+
+
 class _AllGatherKV(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):

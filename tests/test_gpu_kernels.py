@@ -630,3 +630,19 @@ def test_moe_capacity_mask_kernel_matches_sorted_reference(capacity):
     assert int(kept_per_expert.max()) <= capacity
     got.sum().backward()
     assert w.grad is not None and torch.isfinite(w.grad).all()
+
+
+def test_attn_merge_kernel_matches_logaddexp_merge(Y):
+    from pisceslx_b200.parallel.cp import merge_partials
+    torch.manual_seed(41)
+    L, h, d = 300, 6, 128
+    o1, o2 = torch.randn(L, h, d, device=DEV), torch.randn(L, h, d, device=DEV)
+    l1, l2 = torch.randn(L, h, device=DEV) * 3, torch.randn(L, h, device=DEV) * 3
+    l2[5] = float("-inf")                                       # a row whose second block had no visible keys
+    l1[7], l2[7] = float("-inf"), float("-inf")                 # and one with none at all
+    ref_o, ref_l = merge_partials(o1, l1, o2, l2)
+    a, la = o1.clone(), l1.clone()
+    Y.attn_merge(a, la, o2, l2)
+    assert torch.allclose(a[torch.isfinite(ref_l)], ref_o[torch.isfinite(ref_l)], atol=2e-5)
+    assert torch.allclose(la[torch.isfinite(ref_l)], ref_l[torch.isfinite(ref_l)], atol=2e-5)
+    assert torch.equal(a[5], o1[5]) and float(a[7].abs().max()) == 0.0 and la[7, 0] == float("-inf")

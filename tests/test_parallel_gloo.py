@@ -30,6 +30,7 @@ WORKER = textwrap.dedent("""
     cfg = YvConfig.tiny_text_moe(vocab_size=1024)
     cfg.n_layer = 2
     cfg.context_parallel = cp
+    cfg.context_parallel_mode = os.environ.get("YV_TEST_CP_MODE", "allgather")
     cfg.use_gradient_checkpointing = False
     cfg.extra["moe_deterministic"] = True
     model = build_model(cfg, "cpu", torch.float32, parallel=par if par.world_size > 1 else None, seed=7)
@@ -228,15 +229,15 @@ def test_trainer_full_shard_matches_single_process(tmp_path, init_weights):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("world,cp", [(2, 2), (4, 2)])
-def test_context_parallel_training_matches_single_process(tmp_path, init_weights, world, cp):
+@pytest.mark.parametrize("world,cp,mode", [(2, 2, "allgather"), (4, 2, "allgather"), (2, 2, "ring")])
+def test_context_parallel_training_matches_single_process(tmp_path, init_weights, world, cp, mode):
     """Sequences split over context-parallel ranks (K / V all-gathered per layer, loss of local positions against the
     globally shifted targets): same losses and gradient norm as one process; with 4 ranks two data shards x cp 2."""
     steps = 3
     env = {"YV_TEST_CLIP": "1.0", "YV_TEST_BATCH": "4"}
     single = _run(tmp_path, 1, 1, 1, steps, init_weights, f"cp_single{world}", env)
     n_single = json.load(open(str(tmp_path / f"loss_cp_single{world}.json") + ".norms"))
-    multi = _run(tmp_path, world, 1, 1, steps, init_weights, f"cp_w{world}", dict(env, YV_TEST_CP=str(cp)))
+    multi = _run(tmp_path, world, 1, 1, steps, init_weights, f"cp_w{world}", dict(env, YV_TEST_CP=str(cp), YV_TEST_CP_MODE=mode))
     n_multi = json.load(open(str(tmp_path / f"loss_cp_w{world}.json") + ".norms"))
     for a, b in zip(single, multi):
         assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
