@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--state-dtype", default="int8", choices=["int8", "bf16"],
                     help="Muon momentum storage: int8 block-quantised (stochastic rounding) or bf16")
+    ap.add_argument("--expert-fp8", default="", choices=["", "mx"],
+                    help="routed experts' forward products in block-scaled e4m3 (a labelled fp8 line, never the headline)")
     ap.add_argument("--ref-limit", type=int, default=420, help="seconds given to the reference's full-size attempt")
     ap.add_argument("--no-ref-context", action="store_true", help="skip the reduced-layer context run of the reference")
     return ap.parse_args()
@@ -227,6 +229,8 @@ def main() -> None:
     cfg.tensor_parallel, cfg.expert_parallel = tp, ep
     cfg.fused_comm = not args.no_fused_comm
     cfg.use_gradient_checkpointing = True
+    if args.expert_fp8:
+        cfg.expert_fp8 = args.expert_fp8
     seqs = args.seqs_per_gpu or 64            # 64 per GPU = the named global batch of 512 sequences on 8 GPUs
     micro = args.micro_batch or (2 if world == 1 else 4)
     model = build_model(cfg, dev, torch.bfloat16, parallel=par if world > 1 else None, seed=1234)
@@ -324,10 +328,13 @@ def main() -> None:
         out = {
             "metric": "train tokens/sec/box Yv-7B MoE", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / max(args.steps, 1),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if not args.expert_fp8 else "bf16 + mxfp8 expert forward",
             "data": "synthetic uniform-random token ids, random-init weights",
             "config": {"model": "Yv 7B-class text MoE: 32L h4096 32q/8kv hd128, 64 experts ffn1408 top6 + 2 shared "
-                                "ffn2816, vocab 154856" + ("" if args.layers == 32 else f" [INVALID: {args.layers} layers]"),
+                                "ffn2816, vocab 154856" + ("" if args.layers == 32 else f" [INVALID: {args.layers} layers]")
+                                + (f" [fp8 line, not the headline: routed experts' forward in {args.expert_fp8} e4m3]"
+                                   if args.expert_fp8 else ""),
                        "global_batch": seqs_rank * par.dp_size, "seq_len": SEQ,
                        "micro_batch": micro, "parallelism": par_name, "optimizer": "Muon(2-D)+AdamW, "
                        + ("int8 block-scaled Muon momentum (128-element blocks, stochastic rounding), bf16 AdamW moments, "
