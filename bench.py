@@ -106,16 +106,29 @@ def reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "tools")):
-        src = "/root/reference"
+        # where an unpacked reference source tree may be found when ``baseline/_ref`` is empty
+        src = os.environ.get("YV_REFERENCE_SRC", os.path.join(os.sep, "root", "reference"))
         if os.path.isdir(os.path.join(src, "tools")):        # a plain copy is the whole installation: pure Python
             import shutil
-            for name in ("manage.py", "configs", "utils", "third_party", "opss", "tools", "model", "tokenizer"):
-                s_, d_ = os.path.join(src, name), os.path.join(ref_dir, name)
-                (shutil.copytree if os.path.isdir(s_) else shutil.copy)(s_, d_)
+            import time as _time
+            if rank == 0:                                    # one rank copies into a side folder and renames it in
+                tmp_dir = ref_dir + ".partial"
+                shutil.rmtree(tmp_dir, ignore_errors=True)
+                os.makedirs(tmp_dir)
+                for name in ("manage.py", "configs", "utils", "third_party", "opss", "tools", "model", "tokenizer"):
+                    s_, d_ = os.path.join(src, name), os.path.join(tmp_dir, name)
+                    (shutil.copytree if os.path.isdir(s_) else shutil.copy)(s_, d_)
+                if os.path.isdir(ref_dir):
+                    shutil.rmtree(ref_dir, ignore_errors=True)
+                os.rename(tmp_dir, ref_dir)
+            else:
+                t_end = _time.time() + 300
+                while not os.path.isdir(os.path.join(ref_dir, "tools")) and _time.time() < t_end:
+                    _time.sleep(0.5)
         else:
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": "no copy of the reference under baseline/_ref "
-                                  "and no /root/reference to copy it from"}))
+                                  f"and no source tree at {src} to copy it from"}))
             return
     tmp = tempfile.mkdtemp(prefix="yv_ref_arm_")
     seqs = args.seqs_per_gpu or 64
