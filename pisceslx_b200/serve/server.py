@@ -18,6 +18,7 @@ from typing import Any, Dict, List, Optional
 from pydantic import BaseModel, Field
 
 from ..models.generation import YvSamplingConfig
+from . import schemas as S
 from .engine import YvEngineConfig, YvInferenceEngine
 
 
@@ -52,9 +53,33 @@ class PiscesLxEmbeddingRequest(BaseModel):
     input: Any = ""
 
 
+class PiscesLxRateLimited(RuntimeError):
+    pass
+
+
+class PiscesLxRateLimiter:
+    """Token buckets by key: ``rate`` tokens per second refill a bucket of ``burst`` tokens; ``allow`` takes one or
+    says no.  The clock can be injected for tests."""
+
+    def __init__(self, rate: float, burst: int, clock=time.monotonic):
+        self.rate, self.burst, self.clock = float(rate), int(burst), clock
+        self._state: Dict[str, List[float]] = {}
+        self._lock = threading.Lock()
+
+    def allow(self, key: str = "default", cost: float = 1.0) -> bool:
+        now = self.clock()
+        with self._lock:
+            tokens, last = self._state.get(key, [float(self.burst), now])
+            tokens = min(float(self.burst), tokens + (now - last) * self.rate)
+            ok = tokens >= cost
+            self._state[key] = [tokens - cost if ok else tokens, now]
+            return ok
+
+
 class PiscesLxInferService:
-    def __init__(self, engine: YvInferenceEngine, model_name: str = "yv"):
+    def __init__(self, engine: YvInferenceEngine, model_name: str = "yv", rate_limiter: Optional[PiscesLxRateLimiter] = None):
         self.engine, self.model_name = engine, model_name
+        self.rate_limiter = rate_limiter
         self._stop = False
         self._wake = threading.Event()
         self._thread = threading.Thread(target=self._loop, daemon=True)
@@ -90,7 +115,49 @@ class PiscesLxInferService:
             return YvSamplingConfig(strategy="greedy")
         return YvSamplingConfig(strategy="top_k_top_p", temperature=temperature, top_k=top_k, top_p=top_p)
 
+    def attach_generator(self, generator: Any) -> None:
+        """Serve ``/v1/images/generations``, ``/v1/videos/generations`` and ``/v1/audio/speech`` from a
+        ``models.multimodal.YvGenerator`` (tensors become base64 of raw uint8 RGB / int16 PCM)."""
+        import base64
+
+        def image(body: Dict[str, Any]):
+            rq = S.PiscesLxImageGenerationRequest(**{k: v for k, v in body.items() if k in S.PiscesLxImageGenerationRequest.model_fields})
+            out = []
+            for i in range(max(1, rq.n)):
+                r = generator.generate_from_text(rq.prompt, "image", seed=None if rq.seed is None else rq.seed + i,
+                                                 steps=rq.steps, guidance_scale=rq.guidance_scale)
+                if not r.success:
+                    raise RuntimeError(r.error)
+                img = ((r.data[0].float().clamp(-1, 1) + 1) * 127.5).round().byte().permute(1, 2, 0).contiguous().cpu()
+                out.append(S.PiscesLxImageData(b64_json=base64.b64encode(img.numpy().tobytes()).decode(),
+                                               width=img.shape[1], height=img.shape[0]).model_dump())
+            return out
+
+        def video(body: Dict[str, Any]):
+            rq = S.PiscesLxVideoGenerationRequest(**{k: v for k, v in body.items() if k in S.PiscesLxVideoGenerationRequest.model_fields})
+            r = generator.generate_from_text(rq.prompt, "video", seed=rq.seed, num_frames=rq.num_frames)
+            if not r.success:
+                raise RuntimeError(r.error)
+            v = ((r.data[0].float().clamp(-1, 1) + 1) * 127.5).round().byte().permute(0, 2, 3, 1).contiguous().cpu()
+            return [S.PiscesLxVideoData(b64_json=base64.b64encode(v.numpy().tobytes()).decode(), frames=v.shape[0],
+                                        height=v.shape[1], width=v.shape[2], fps=int(r.metadata.get("fps", 24))).model_dump()]
+
+        def audio(body: Dict[str, Any]):
+            rq = S.PiscesLxAudioSpeechRequest(**{k: v for k, v in body.items() if k in S.PiscesLxAudioSpeechRequest.model_fields})
+            r = generator.generate_from_text(rq.input, "audio", duration=rq.duration)
+            if not r.success:
+                raise RuntimeError(r.error)
+            pcm = (r.data[0].float().clamp(-1, 1) * 32767).round().short().cpu()
+            return S.PiscesLxAudioSpeechResponse(sample_rate=int(r.metadata.get("sample_rate", 16000)), samples=pcm.numel(),
+                                                 b64_pcm16=base64.b64encode(pcm.numpy().tobytes()).decode()).model_dump()
+
+        if not hasattr(self, "media"):
+            self.media = {}
+        self.media.update({"image": image, "video": video, "audio": audio})
+
     def submit(self, prompt: str, max_tokens: int, temperature: float, top_k: int, top_p: float, on_token=None):
+        if getattr(self, "rate_limiter", None) is not None and not self.rate_limiter.allow("requests"):
+            raise PiscesLxRateLimited("request rate limit reached")
         ids = self.engine.tokenizer.encode(prompt)
         req = self.engine.add_request(ids, max_tokens, self._sampling(temperature, top_k, top_p), on_token=on_token)
         self._wake.set()
@@ -112,6 +179,14 @@ class PiscesLxInferService:
         async def _startup() -> None:
             svc.start()
 
+        @app.exception_handler(PiscesLxRateLimited)
+        async def _limited(_request, exc):
+            return JSONResponse(S.PiscesLxErrorResponse(error=str(exc), code=429).model_dump(), status_code=429)
+
+        @app.exception_handler(ValueError)
+        async def _bad_request(_request, exc):
+            return JSONResponse(S.PiscesLxErrorResponse(error=str(exc), code=400).model_dump(), status_code=400)
+
         @app.get("/healthz")
         async def healthz():
             return {"status": "ok", "uptime": time.time() - svc.started}
@@ -126,7 +201,7 @@ class PiscesLxInferService:
 
         @app.get("/v1/models")
         async def models():
-            return {"object": "list", "data": [{"id": svc.model_name, "object": "model", "owned_by": "pisceslx_b200"}]}
+            return S.PiscesLxModelListResponse(data=[S.PiscesLxModelInfo(id=svc.model_name)]).model_dump()
 
         async def _wait(req) -> None:
             while not req.finished:
@@ -141,17 +216,17 @@ class PiscesLxInferService:
             prompt = svc.chat_prompt(body.messages)
             cid = "chatcmpl-" + uuid.uuid4().hex[:24]
             if body.stream:
+                req = svc.submit(prompt, body.max_tokens, body.temperature, body.top_k, body.top_p)
+
                 async def gen():
-                    req = svc.submit(prompt, body.max_tokens, body.temperature, body.top_k, body.top_p)
                     sent = 0
                     while not req.finished or sent < len(req.output_ids):
                         while sent < len(req.output_ids):
                             piece = svc.engine.tokenizer.decode([req.output_ids[sent]])
                             sent += 1
-                            chunk = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()),
-                                     "model": body.model,
-                                     "choices": [{"index": 0, "delta": {"content": piece}, "finish_reason": None}]}
-                            yield f"data: {json.dumps(chunk)}\n\n"
+                            yield S.PiscesLxChatCompletionChunk(id=cid, model=body.model, choices=[
+                                S.PiscesLxChatCompletionChunkChoice(
+                                    delta=S.PiscesLxChatCompletionChunkDelta(content=piece))]).sse()
                         await asyncio.sleep(0.002)
                     end = {"id": cid, "object": "chat.completion.chunk", "created": int(time.time()), "model": body.model,
                            "choices": [{"index": 0, "delta": {}, "finish_reason": req.finish_reason}]}
@@ -160,28 +235,26 @@ class PiscesLxInferService:
                 return StreamingResponse(gen(), media_type="text/event-stream")
             req = svc.submit(prompt, body.max_tokens, body.temperature, body.top_k, body.top_p)
             await _wait(req)
-            return {"id": cid, "object": "chat.completion", "created": int(time.time()), "model": body.model,
-                    "choices": [{"index": 0, "message": {"role": "assistant",
-                                                         "content": svc.engine.tokenizer.decode(req.output_ids)},
-                                 "finish_reason": req.finish_reason}],
-                    "usage": _usage(req)}
+            return S.PiscesLxChatCompletionResponse(
+                id=cid, model=body.model, usage=S.PiscesLxChatCompletionUsage(**_usage(req)),
+                choices=[S.PiscesLxChatCompletionChoice(
+                    message=S.PiscesLxResponseMessage(content=svc.engine.tokenizer.decode(req.output_ids)),
+                    finish_reason=req.finish_reason)]).model_dump()
 
         @app.post("/v1/completions")
         async def completions(body: PiscesLxCompletionRequest):
             req = svc.submit(body.prompt, body.max_tokens, body.temperature, body.top_k, body.top_p)
             await _wait(req)
-            return {"id": "cmpl-" + uuid.uuid4().hex[:24], "object": "text_completion", "created": int(time.time()),
-                    "model": body.model,
-                    "choices": [{"index": 0, "text": svc.engine.tokenizer.decode(req.output_ids),
-                                 "finish_reason": req.finish_reason}],
-                    "usage": _usage(req)}
+            return S.PiscesLxCompletionResponse(
+                model=body.model, usage=S.PiscesLxChatCompletionUsage(**_usage(req)),
+                choices=[S.PiscesLxCompletionChoice(text=svc.engine.tokenizer.decode(req.output_ids),
+                                                    finish_reason=req.finish_reason)]).model_dump()
 
         @app.post("/v1/embeddings")
         async def embeddings(body: PiscesLxEmbeddingRequest):
             texts = body.input if isinstance(body.input, list) else [body.input]
-            data = [{"object": "embedding", "index": i, "embedding": svc.engine.embeddings(str(t))}
-                    for i, t in enumerate(texts)]
-            return {"object": "list", "data": data, "model": body.model}
+            data = [S.PiscesLxEmbeddingData(index=i, embedding=svc.engine.embeddings(str(t))) for i, t in enumerate(texts)]
+            return S.PiscesLxEmbeddingResponse(data=data, model=body.model).model_dump()
 
         svc._add_extended_routes(app)
         return app

@@ -89,3 +89,40 @@ def test_agentic_evolution_selects_and_mutates():
         assert len(top) == 2
     assert float(evo.evaluate_agents(x, y).max()) >= best0 and evo.generation == 15
     assert evo.best() is evo.agents[int(evo.agent_scores.argmax())]
+
+
+def test_server_media_routes_schemas_and_rate_limit():
+    import base64
+    from fastapi.testclient import TestClient
+    from pisceslx_b200 import YvConfig
+    from pisceslx_b200.models import build_model
+    from pisceslx_b200.models.multimodal import YvGenerator
+    from pisceslx_b200.serve import schemas as S
+    from pisceslx_b200.serve.engine import YvEngineConfig, YvInferenceEngine
+    from pisceslx_b200.serve.server import PiscesLxInferService, PiscesLxRateLimiter
+    t = [0.0]
+    lim = PiscesLxRateLimiter(rate=1.0, burst=2, clock=lambda: t[0])
+    assert lim.allow() and lim.allow() and not lim.allow()
+    t[0] = 1.5
+    assert lim.allow() and not lim.allow()
+    cfg = YvConfig.tiny_text_moe(vocab_size=512)
+    eng = YvInferenceEngine(build_model(cfg, "cpu", torch.float32, seed=0),
+                            cfg=YvEngineConfig(num_blocks=64, block_size=16, eos_token_id=-1))
+    svc = PiscesLxInferService(eng, rate_limiter=PiscesLxRateLimiter(rate=0.0, burst=2))
+    svc.attach_generator(YvGenerator(_gen_cfg()))
+    with TestClient(svc.build_app()) as c:
+        r = S.PiscesLxChatCompletionResponse.model_validate(
+            c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3}).json())
+        assert r.usage.completion_tokens == 3 and r.choices[0].message.role == "assistant"
+        S.PiscesLxCompletionResponse.model_validate(c.post("/v1/completions", json={"prompt": "ab", "max_tokens": 2}).json())
+        third = c.post("/v1/completions", json={"prompt": "ab", "max_tokens": 2})        # the bucket held two requests
+        assert third.status_code == 429 and S.PiscesLxErrorResponse.model_validate(third.json()).code == 429
+        S.PiscesLxModelListResponse.model_validate(c.get("/v1/models").json())
+        img = S.PiscesLxImageGenerationResponse.model_validate(
+            c.post("/v1/images/generations", json={"prompt": "a red square", "seed": 3, "n": 2}).json())
+        assert len(img.data) == 2 and len(base64.b64decode(img.data[0].b64_json)) == 32 * 32 * 3
+        aud = c.post("/v1/audio/speech", json={"input": "beep"}).json()["data"]
+        assert S.PiscesLxAudioSpeechResponse.model_validate(aud).samples == 800
+        vid = S.PiscesLxVideoGenerationResponse.model_validate(c.post("/v1/videos/generations", json={"prompt": "w", "num_frames": 2}).json())
+        assert vid.data[0].frames == 2
+    svc.stop()
