@@ -543,3 +543,66 @@ class PiscesLxPreferenceDataProcessor:
         enc = [self._encode(r["prompt"], r["completion"]) for r in records]
         return {"input_ids": self._pad([a for a, _ in enc], self.pad), "labels": self._pad([b for _, b in enc], -100),
                 "desirable": torch.tensor([bool(r["label"]) for r in records])}
+
+
+class PiscesLxRewardNormalizer:
+    """Running mean / variance of rewards (Welford, batched) with clipping of the normalised value; what PPO / GRPO
+    style trainers put between a reward model and the advantage computation so that the reward scale of one task
+    does not set the step size for all (reference opss/train/grpo.py normalises group rewards the same way)."""
+
+    def __init__(self, clip: float = 5.0, eps: float = 1e-8):
+        self.clip, self.eps = clip, eps
+        self.count, self.mean, self.m2 = 0.0, 0.0, 0.0
+
+    def update(self, rewards: torch.Tensor) -> None:
+        r = rewards.detach().double().flatten()
+        n = float(r.numel())
+        if n == 0:
+            return
+        b_mean, b_m2 = float(r.mean()), float(((r - r.mean()) ** 2).sum())
+        delta = b_mean - self.mean
+        tot = self.count + n
+        self.mean += delta * n / tot
+        self.m2 += b_m2 + delta * delta * self.count * n / tot
+        self.count = tot
+
+    @property
+    def std(self) -> float:
+        return (self.m2 / max(self.count - 1.0, 1.0)) ** 0.5 if self.count > 1 else 1.0
+
+    def __call__(self, rewards: torch.Tensor, update: bool = True) -> torch.Tensor:
+        if update:
+            self.update(rewards)
+        return ((rewards - self.mean) / (self.std + self.eps)).clamp(-self.clip, self.clip)
+
+    def state_dict(self) -> Dict[str, float]:
+        return {"count": self.count, "mean": self.mean, "m2": self.m2}
+
+    def load_state_dict(self, sd: Dict[str, float]) -> None:
+        self.count, self.mean, self.m2 = float(sd["count"]), float(sd["mean"]), float(sd["m2"])
+
+
+class PiscesLxGenerativeRewardModel:
+    """Reward from a generated judgement: the judge model is prompted with the question and the candidate answer,
+    writes a short critique ending in ``Score: n/10`` and the number becomes the reward (reference "GRM": a reward
+    model that reasons before it scores).  ``generate(prompt, max_new_tokens) -> text``."""
+
+    PROMPT = ("Question:\n{question}\n\nCandidate answer:\n{answer}\n\n"
+              "Critique the answer briefly, then finish with 'Score: n/10'.\n")
+
+    def __init__(self, generate, max_new_tokens: int = 128, default: float = 0.0, normalizer: Optional[PiscesLxRewardNormalizer] = None):
+        self.generate, self.max_new_tokens, self.default, self.normalizer = generate, max_new_tokens, default, normalizer
+
+    @staticmethod
+    def parse(text: str) -> Optional[float]:
+        import re
+        m = re.findall(r"score\s*[:=]\s*(\d+(?:\.\d+)?)\s*(?:/\s*10)?", text, re.I)
+        return min(10.0, float(m[-1])) / 10.0 if m else None
+
+    def score(self, question: str, answers: List[str]) -> torch.Tensor:
+        vals = []
+        for a in answers:
+            s = self.parse(self.generate(self.PROMPT.format(question=question, answer=a), self.max_new_tokens))
+            vals.append(self.default if s is None else s)
+        r = torch.tensor(vals, dtype=torch.float32)
+        return self.normalizer(r) if self.normalizer is not None else r

@@ -97,11 +97,93 @@ class YvVeriCoTVerifier:
         return ok
 
 
+class YvThoughtTreeReasoner:
+    """Tree of thoughts with beam search: at every depth each kept partial chain is extended by ``branch`` sampled
+    next steps, a value function scores the candidates (default: ask the model to rate the chain 1-10 and parse the
+    number), the ``beam`` best survive; a chain ends when a step states an answer.  ``value_fn(question, steps)`` can be
+    supplied (a verifier, a reward model) instead of the prompt-based rating."""
+
+    STEP = "{question}\nSteps so far:\n{steps}\nNext step (or 'Answer: ...' if done):\n"
+    RATE = "{question}\nSteps so far:\n{steps}\nRate from 1 to 10 how promising this reasoning is. Rating:"
+
+    def __init__(self, generate: GenerateFn, branch: int = 3, beam: int = 2, max_depth: int = 4, max_new_tokens: int = 64,
+                 value_fn: Optional[Callable[[str, List[str]], float]] = None):
+        self.generate, self.branch, self.beam, self.max_depth = generate, branch, beam, max_depth
+        self.max_new_tokens, self.value_fn = max_new_tokens, value_fn
+        self.expanded = 0
+
+    def _value(self, question: str, steps: List[str]) -> float:
+        if self.value_fn is not None:
+            return float(self.value_fn(question, steps))
+        out = self.generate(self.RATE.format(question=question, steps="\n".join(steps) or "(none)"), 8)
+        m = re.search(r"(\d+(?:\.\d+)?)", out)
+        return min(10.0, float(m.group(1))) if m else 0.0
+
+    def reason(self, question: str) -> YvReasoningTrace:
+        frontier: List[Tuple[float, List[str]]] = [(0.0, [])]
+        done: List[Tuple[float, List[str], str]] = []
+        for _ in range(self.max_depth):
+            cand: List[Tuple[float, List[str]]] = []
+            for _, steps in frontier:
+                seen = set()
+                for _b in range(self.branch):
+                    nxt = self.generate(self.STEP.format(question=question, steps="\n".join(steps) or "(none)"),
+                                        self.max_new_tokens).strip().split("\n")[0].strip()
+                    if not nxt or nxt in seen:
+                        continue
+                    seen.add(nxt)
+                    self.expanded += 1
+                    chain = steps + [nxt]
+                    v = self._value(question, chain)
+                    ans = extract_answer(nxt)
+                    if ans is not None:
+                        done.append((v, chain, ans))
+                    else:
+                        cand.append((v, chain))
+            if not cand:
+                break
+            cand.sort(key=lambda c: -c[0])
+            frontier = cand[: self.beam]
+        if done:
+            v, chain, ans = max(done, key=lambda c: c[0])
+            return YvReasoningTrace(steps=chain, answer=ans, votes=dict(Counter(a for _, _, a in done)))
+        best = max(frontier, key=lambda c: c[0])[1] if frontier else []
+        return YvReasoningTrace(steps=best, answer=None)
+
+
+class YvCoTMemoryReasoner:
+    """Chain of thought with an episodic memory: solved questions are stored with their steps; a new question first
+    retrieves the most similar stored ones (token-overlap similarity) and shows them as worked examples."""
+
+    def __init__(self, generate: GenerateFn, capacity: int = 256, shots: int = 2, max_new_tokens: int = 256):
+        self.cot, self.capacity, self.shots = YvCoTReasoner(generate, max_new_tokens), capacity, shots
+        self.memory: List[Tuple[str, YvReasoningTrace]] = []
+
+    @staticmethod
+    def _sim(a: str, b: str) -> float:
+        ta, tb = set(a.lower().split()), set(b.lower().split())
+        return len(ta & tb) / max(1, len(ta | tb))
+
+    def recall(self, question: str) -> List[Tuple[str, YvReasoningTrace]]:
+        ranked = sorted(self.memory, key=lambda m: -self._sim(question, m[0]))
+        return [m for m in ranked[: self.shots] if self._sim(question, m[0]) > 0]
+
+    def reason(self, question: str, remember: bool = True) -> YvReasoningTrace:
+        shots = self.recall(question)
+        prefix = "".join(f"Q: {q}\n" + "\n".join(t.steps) + f"\nAnswer: {t.answer}\n\n" for q, t in shots)
+        trace = self.cot.reason(prefix + question if prefix else question)
+        if remember and trace.answer is not None:
+            self.memory.append((question, trace))
+            del self.memory[:-self.capacity]
+        return trace
+
+
 class YvUnifiedReasoner:
     """Front door: picks a strategy by name and optionally verifies, retrying once on a failed check."""
 
     def __init__(self, generate: GenerateFn, strategy: str = "cot", verify: bool = False, **kw: Any):
-        self.impl = {"cot": YvCoTReasoner, "multipath": YvMultiPathReasoner, "recursive": YvRecursiveReasoner}[strategy](generate, **kw)
+        self.impl = {"cot": YvCoTReasoner, "multipath": YvMultiPathReasoner, "recursive": YvRecursiveReasoner,
+                     "tree": YvThoughtTreeReasoner, "memory": YvCoTMemoryReasoner}[strategy](generate, **kw)
         self.verifier = YvVeriCoTVerifier() if verify else None
 
     def reason(self, question: str) -> YvReasoningTrace:

@@ -262,3 +262,47 @@ class PiscesLxBrownoutMoEGrouper:
             if not self.active[g]:
                 m[members] = float("-inf")
         return m
+
+
+class PiscesLxSemanticCache:
+    """Answers cached by the MEANING of the prompt: a prompt whose embedding is within ``threshold`` cosine similarity
+    of a stored one gets the stored answer.  ``embed`` maps text to a vector (the engine's ``embeddings``); entries
+    leave in least-recently-used order."""
+
+    def __init__(self, embed, capacity: int = 1024, threshold: float = 0.97):
+        self.embed, self.capacity, self.threshold = embed, capacity, threshold
+        self._keys: List[torch.Tensor] = []
+        self._vals: List[str] = []
+        self._used: List[int] = []
+        self._clock = 0
+        self.hits = self.misses = 0
+
+    def _vec(self, text: str) -> torch.Tensor:
+        v = torch.as_tensor(self.embed(text), dtype=torch.float32).flatten()
+        return v / v.norm().clamp_min(1e-12)
+
+    def get(self, prompt: str) -> Optional[str]:
+        self._clock += 1
+        if self._keys:
+            sims = torch.stack(self._keys) @ self._vec(prompt)
+            i = int(sims.argmax())
+            if float(sims[i]) >= self.threshold:
+                self._used[i] = self._clock
+                self.hits += 1
+                return self._vals[i]
+        self.misses += 1
+        return None
+
+    def put(self, prompt: str, answer: str) -> None:
+        self._clock += 1
+        if len(self._keys) >= self.capacity:
+            i = min(range(len(self._used)), key=self._used.__getitem__)
+            for lst in (self._keys, self._vals, self._used):
+                lst.pop(i)
+        self._keys.append(self._vec(prompt))
+        self._vals.append(answer)
+        self._used.append(self._clock)
+
+    def stats(self) -> Dict[str, float]:
+        n = self.hits + self.misses
+        return {"entries": len(self._keys), "hits": self.hits, "misses": self.misses, "hit_rate": self.hits / n if n else 0.0}

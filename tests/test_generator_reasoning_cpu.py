@@ -126,3 +126,55 @@ def test_server_media_routes_schemas_and_rate_limit():
         vid = S.PiscesLxVideoGenerationResponse.model_validate(c.post("/v1/videos/generations", json={"prompt": "w", "num_frames": 2}).json())
         assert vid.data[0].frames == 2
     svc.stop()
+
+
+def test_thought_tree_memory_reasoner_semantic_cache_and_reward_tools():
+    from pisceslx_b200.engine.rl import PiscesLxGenerativeRewardModel, PiscesLxRewardNormalizer
+    from pisceslx_b200.models.reasoning import YvCoTMemoryReasoner, YvThoughtTreeReasoner, YvUnifiedReasoner
+    from pisceslx_b200.serve.runtime import PiscesLxSemanticCache
+    # a scripted "model": proposes a bad and a good step at depth 0, then answers; rates chains containing "good" higher
+    calls = {"n": 0}
+
+    def gen(prompt: str, n: int) -> str:
+        if "Rate from 1 to 10" in prompt:
+            return " 9" if "good" in prompt else " 2"
+        calls["n"] += 1
+        if "(none)" in prompt:
+            return "bad idea" if calls["n"] % 2 else "good idea"
+        return "Answer: 42" if "good" in prompt else "Answer: 7"
+    t = YvThoughtTreeReasoner(gen, branch=2, beam=1, max_depth=3).reason("what?")
+    assert t.answer == "42" and t.steps[0] == "good idea"
+    assert YvUnifiedReasoner(gen, strategy="tree", branch=2, beam=1).reason("what?").answer == "42"
+    seen = []
+
+    def cot(prompt: str, n: int) -> str:
+        seen.append(prompt)
+        return "step one\nAnswer: 5"
+    mem = YvCoTMemoryReasoner(cot, shots=1)
+    mem.reason("how many apples are in the red box")
+    mem.reason("how many apples are in the blue box")
+    assert "Q: how many apples are in the red box" in seen[-1] and len(mem.memory) == 2
+    # semantic cache: near-duplicate prompts hit, different ones miss, LRU eviction
+    vocab = {"hello": 0, "world": 1, "there": 2, "bye": 3}
+
+    def embed(text):
+        v = torch.zeros(4)
+        for w in text.split():
+            v[vocab.get(w, 3)] += 1
+        return v
+    c = PiscesLxSemanticCache(embed, capacity=2, threshold=0.9)
+    c.put("hello world", "A")
+    assert c.get("world hello") == "A" and c.get("bye") is None
+    c.put("bye", "B")
+    c.get("hello world")
+    c.put("there there", "C")                                   # evicts "bye" (least recently used)
+    assert c.get("bye") is None and c.get("hello world") == "A" and c.stats()["entries"] == 2
+    # reward normaliser: batched Welford equals the plain statistics
+    norm = PiscesLxRewardNormalizer(clip=3.0)
+    data = torch.randn(3, 50) * 4 + 2
+    for row in data:
+        norm.update(row)
+    assert abs(norm.mean - float(data.mean())) < 1e-5 and abs(norm.std - float(data.flatten().std())) < 1e-4
+    assert float(norm(torch.tensor([1000.0]), update=False)) == 3.0
+    grm = PiscesLxGenerativeRewardModel(lambda p, n: "fine. Score: 7/10" if "right" in p else "no score here")
+    assert torch.allclose(grm.score("q", ["right answer", "wrong"]), torch.tensor([0.7, 0.0]))
