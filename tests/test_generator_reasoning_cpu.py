@@ -178,3 +178,34 @@ def test_thought_tree_memory_reasoner_semantic_cache_and_reward_tools():
     assert float(norm(torch.tensor([1000.0]), update=False)) == 3.0
     grm = PiscesLxGenerativeRewardModel(lambda p, n: "fine. Score: 7/10" if "right" in p else "no score here")
     assert torch.allclose(grm.score("q", ["right answer", "wrong"]), torch.tensor([0.7, 0.0]))
+
+
+def test_distillation_loss_family():
+    from pisceslx_b200.engine.distill_losses import (PiscesLxAttentionDistillationLoss, PiscesLxDistillationLoss,
+                                                     PiscesLxDistillationLossConfig, PiscesLxLayerWiseDistillationLoss,
+                                                     PiscesLxLogitsDistillationLoss, PiscesLxOptimalTransportAligner)
+    torch.manual_seed(0)
+    t_logits = torch.randn(2, 5, 11)
+    kd = PiscesLxLogitsDistillationLoss(2.0)
+    assert float(kd(t_logits, t_logits)) < 1e-6 and float(kd(torch.randn(2, 5, 11), t_logits)) > 0.01
+    s_logits = torch.zeros(2, 5, 11, requires_grad=True)
+    opt = torch.optim.SGD([s_logits], lr=5.0)
+    first = float(kd(s_logits, t_logits))
+    for _ in range(100):
+        opt.zero_grad()
+        kd(s_logits, t_logits).backward()
+        opt.step()
+    assert float(kd(s_logits, t_logits)) < 0.05 * first                         # the student matches the teacher's distribution
+    a = torch.softmax(torch.randn(2, 4, 6, 6), -1)
+    assert float(PiscesLxAttentionDistillationLoss()(a, a)) < 1e-6
+    assert float(PiscesLxAttentionDistillationLoss()(torch.softmax(torch.randn(2, 2, 6, 6), -1), a)) > 0        # 2 vs 4 heads
+    ss, ts = [torch.randn(2, 5, 8) for _ in range(2)], [torch.randn(2, 5, 16) for _ in range(4)]
+    lw = PiscesLxLayerWiseDistillationLoss(8, 16)
+    assert float(lw(ss, ts)) > 0 and lw.loss.proj.weight.shape == (16, 8)
+    plan = PiscesLxOptimalTransportAligner().plan(ss, ts)
+    assert plan.shape == (2, 4) and torch.allclose(plan.sum(1), torch.full((2,), 0.5), atol=1e-3)
+    assert float(plan[0, 0]) > float(plan[0, 3]) and float(plan[1, 3]) > float(plan[1, 0])      # early to early, late to late
+    full = PiscesLxDistillationLoss(PiscesLxDistillationLossConfig(hidden_weight=0.5, contrastive_weight=0.1, hard_label_weight=0.2), 8, 16)
+    total, parts = full({"logits": torch.randn(2, 5, 11), "hidden_states": ss}, {"logits": t_logits, "hidden_states": ts},
+                        labels=torch.randint(0, 11, (2, 5)))
+    assert set(parts) == {"logits", "hidden", "contrastive", "hard"} and abs(float(total) - sum(parts.values())) < 1e-4
