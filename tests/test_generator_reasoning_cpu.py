@@ -209,3 +209,37 @@ def test_distillation_loss_family():
     total, parts = full({"logits": torch.randn(2, 5, 11), "hidden_states": ss}, {"logits": t_logits, "hidden_states": ts},
                         labels=torch.randint(0, 11, (2, 5)))
     assert set(parts) == {"logits", "hidden", "contrastive", "hard"} and abs(float(total) - sum(parts.values())) < 1e-4
+
+
+def test_numerical_shape_device_guards_and_rope_front():
+    import pytest
+    from pisceslx_b200.models.safety import (YvDeviceGuard, YvDeviceResolver, YvNumericalGuard, YvRope, YvShapeGuard)
+    G = YvNumericalGuard
+    assert G.get_eps(torch.bfloat16) > G.get_eps(torch.float32)
+    d = G.safe_div(torch.ones(3), torch.tensor([0.0, -0.0, 2.0]))
+    assert torch.isfinite(d).all() and float(d[2]) == 0.5
+    assert torch.isfinite(G.safe_log(torch.zeros(2))).all()
+    s = torch.tensor([0.3, 0.8], requires_grad=True)
+    g = G.straight_through_gate(s)
+    g.sum().backward()
+    assert g.tolist() == [0.0, 1.0] and s.grad.tolist() == [1.0, 1.0]
+    YvShapeGuard.check_matmul(torch.zeros(2, 3), torch.zeros(3, 4))
+    with pytest.raises(ValueError, match=r"\(2, 3\) @ \(5, 4\)"):
+        YvShapeGuard.check_matmul(torch.zeros(2, 3), torch.zeros(5, 4), "in q_proj")
+    with pytest.raises(ValueError):
+        YvShapeGuard.check_cat([torch.zeros(2, 3), torch.zeros(2, 4)], 0)
+    YvShapeGuard.check_cat([torch.zeros(2, 3), torch.zeros(5, 3)], 0)
+    a, b = YvDeviceGuard.align(torch.zeros(2, dtype=torch.float64), torch.ones(2, dtype=torch.float32))
+    assert b.dtype == torch.float64
+    with pytest.raises(ValueError):
+        YvDeviceGuard.assert_same_dtype(torch.zeros(1), torch.zeros(1, dtype=torch.float64))
+    dev = YvDeviceResolver.resolve("auto")
+    assert YvDeviceResolver.compute_dtype(torch.device("cpu")) == torch.float32 and dev.type in ("cpu", "cuda")
+    cos, sin = YvRope.precompute_freqs_cis(8, 16)
+    q, k = torch.randn(16, 2, 8), torch.randn(16, 1, 8)
+    qr, kr = YvRope.apply_rotary_emb(q, k, cos, sin)
+    assert torch.allclose(qr.norm(dim=-1), q.norm(dim=-1), atol=1e-5) and torch.allclose(qr[0], q[0], atol=1e-6)
+    # relative property: the score of (q at i, k at j) depends on i - j only
+    q1, k1 = YvRope.apply_rotary_emb(q[:1].expand(16, 2, 8), k[:1].expand(16, 1, 8), cos, sin)
+    sc = (q1[:, 0] @ k1[:, 0].t())
+    assert torch.allclose(sc[3, 1], sc[10, 8], atol=1e-4)
