@@ -46,7 +46,7 @@ def parse_args():
                     help="Muon momentum storage: int8 block-quantised (stochastic rounding) or bf16")
     ap.add_argument("--expert-fp8", default="", choices=["", "mx"],
                     help="routed experts' forward products in block-scaled e4m3 (a labelled fp8 line, never the headline)")
-    ap.add_argument("--ref-limit", type=int, default=420, help="seconds given to the reference's full-size attempt")
+    ap.add_argument("--ref-limit", type=int, default=300, help="seconds given to the reference's full-size attempt")
     ap.add_argument("--no-ref-context", action="store_true", help="skip the reduced-layer context run of the reference")
     return ap.parse_args()
 
