@@ -229,6 +229,7 @@ class YvConfig:
     context_parallel: int = 1
     context_parallel_mode: str = "allgather"   # "ring": K/V blocks travel round the ranks (O(S/cp) K/V memory per rank)
     sequence_parallel: bool = True
+    tp_split_head: bool = False             # training: every tensor-parallel rank runs LM head + loss on ITS token shard only
     zero_stage: int = 1
     fused_comm: bool = True                 # peer-memory fused kernels (False = NCCL baseline mode)
     expert_fp8: Optional[str] = None        # "mx": routed experts' forward products in block-scaled e4m3 (single GPU path)

@@ -203,7 +203,7 @@ class YvTrainer:
             sq = self.optimizer.sq_norm / float(n_micro * n_micro)
             if self.dp is not None:
                 if self.dp.consumed_sq is not None:
-                    sq = sq + self.dp.consumed_sq.to(sq.device)
+                    sq = sq + self.dp.consumed_sq_total().to(sq.device)
                 sq = self.dp.global_sq_norm(sq)
             grad_norm = sq.sqrt()
         self.optimizer.step()

@@ -126,8 +126,11 @@ class YvModel(nn.Module):
 
     def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
                 inputs_embeds: Optional[torch.Tensor] = None, prefix_embeds: Optional[torch.Tensor] = None,
-                ctx: Optional[AttnContext] = None, hidden_in: Optional[torch.Tensor] = None) -> YvModelOutput:
+                ctx: Optional[AttnContext] = None, hidden_in: Optional[torch.Tensor] = None,
+                gather_output: bool = True) -> YvModelOutput:
         """Returns ``hidden_states`` [B, S_total, H] (normalised on the last pipeline stage) and ``aux_loss``.
+        With ``gather_output=False`` under sequence parallelism the states stay sharded: [B * S / tp, H], the rows of
+        this tensor-parallel rank in flattened token order.
 
         ``prefix_embeds`` [B, P, H] (modal fusion tokens) are concatenated in front of the text embeddings.
         ``hidden_in`` feeds a non-first pipeline stage."""
@@ -150,6 +153,8 @@ class YvModel(nn.Module):
         else:
             out = hf if delta is None else hf + delta
         if self.parallel is not None and self.parallel.tp_size > 1 and self.cfg.sequence_parallel:
+            if not gather_output:
+                return YvModelOutput(hidden_states=out, aux_loss=aux)
             from ..parallel import tp
             out = tp.gather_sequence(out, self.parallel.tp_group)
         return YvModelOutput(hidden_states=out.view(B, S, H), aux_loss=aux)
@@ -189,6 +194,8 @@ class YvModelForCausalLM(nn.Module):
         par = self.parallel
         if par is not None and getattr(par, "cp_size", 1) > 1 and self.training and ctx is None and input_ids is not None:
             return self._forward_context_parallel(input_ids, attention_mask, labels)
+        if self._split_head_applies(labels, prefix_embeds, return_logits, return_hidden):
+            return self._forward_split_head(input_ids, attention_mask, inputs_embeds, labels, ctx, hidden_in, num_valid)
         out = self.model(input_ids, attention_mask, inputs_embeds, prefix_embeds, ctx, hidden_in)
         hidden, aux = out["hidden_states"], out["aux_loss"]
         res = YvModelOutput(aux_loss=aux, loss=None, lm_loss=None, mtp_loss=None, logits=None)
@@ -229,6 +236,37 @@ class YvModelForCausalLM(nn.Module):
                 loss = loss + cfg.moe_aux_loss_weight * aux
             res["loss"] = loss
         return res
+
+    # ---- tensor parallelism: head and loss on the local token shard ----------------------------------------------
+    def _split_head_applies(self, labels, prefix_embeds, return_logits, return_hidden) -> bool:
+        par, cfg = self.parallel, self.cfg
+        return (bool(getattr(cfg, "tp_split_head", False)) and par is not None and par.tp_size > 1 and cfg.sequence_parallel
+                and self.training and labels is not None and prefix_embeds is None and not return_logits
+                and not return_hidden and self.model.is_last_stage and not self.tied and self.num_mtp == 0)
+
+    def _forward_split_head(self, input_ids, attention_mask, inputs_embeds, labels, ctx, hidden_in, num_valid):
+        """The trunk's output stays sequence-sharded; every tensor-parallel rank projects ITS rows onto the vocabulary
+        and sums their losses (normalised by the GLOBAL target count).  Nothing is computed twice and the final
+        all-gather disappears.  The returned loss has the value of the full mean (one scalar all-reduce) and the
+        gradient of the local part, which is what the sharded trunk expects: the backward of the old all-gather kept
+        the local rows of an identical gradient anyway.  The head weight now receives a partial gradient per rank and
+        is reduced over tensor- x data-parallel ranks like the norm weights (``parallel.zero`` reads the same flag)."""
+        import torch.distributed as dist
+        par, cfg = self.parallel, self.cfg
+        out = self.model(input_ids, attention_mask, inputs_embeds, None, ctx, hidden_in, gather_output=False)
+        h_loc, aux = out["hidden_states"], out["aux_loss"]
+        B, L = labels.shape
+        rows = h_loc.shape[0]
+        assert rows * par.tp_size == B * L, "tp_split_head needs labels for every position (no modal prefix)"
+        tgt = torch.cat([labels[:, 1:], labels.new_full((B, 1), -100)], 1).reshape(-1)
+        nv = int(num_valid) if num_valid is not None else int((tgt != -100).sum().item())
+        lo = par.tp_rank * rows
+        local = linear_cross_entropy(h_loc, self.head_weight, tgt[lo:lo + rows].contiguous(), -100, nv)
+        tot = local.detach().clone()
+        dist.all_reduce(tot, group=par.tp_group)
+        lm_loss = local + (tot - local.detach())
+        loss = lm_loss if cfg.moe_aux_loss_free else lm_loss + cfg.moe_aux_loss_weight * aux
+        return YvModelOutput(aux_loss=aux, loss=loss, lm_loss=lm_loss, mtp_loss=None, logits=None)
 
     def _forward_context_parallel(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor],
                                   labels: Optional[torch.Tensor]) -> YvModelOutput:

@@ -293,19 +293,24 @@ def symmetric_flat_buffers(group: Any, name: str, numel: int, dtype: torch.dtype
     return (pb, pb.tensor(dtype, numel)), (gb, gb.tensor(dtype, numel))
 
 
-def reduce_scatter_grads(g: Any, scale: float, optimizer: Any = None, sumsq: Any = None) -> List[str]:
+def reduce_scatter_grads(g: Any, scale: float, optimizer: Any = None, sumsq: Any = None, sumsq_rep: Any = None,
+                         replicated: Any = ()) -> List[str]:
     """Owner-side pull reduction of flat-group ``g``.  Tensors whose optimizer update could be fused into the
-    reduction are returned by name (their gradients need no further handling)."""
+    reduction are returned by name (their gradients need no further handling).  The squared norm of every folded
+    gradient is added to ``sumsq``, or to ``sumsq_rep`` for the tensors named in ``replicated`` (tensors of which
+    every tensor-parallel rank holds and reduces an identical copy: the caller weights that sum by 1 / tp)."""
     K = kernels()
     heap = heap_for(g.group)
     heap.barrier()                                          # all ranks finished accumulating their gradients
     handled: List[str] = []
     ptrs = g.symm_grad.ptrs
     streaming = bool(getattr(optimizer, "_streaming", False))
+    sumsq_plain = sumsq
     for n, p in g.owned():
         off = g.offsets[n]
         numel = p.numel()
         fused_done = False
+        sumsq = sumsq_rep if (sumsq_rep is not None and n in replicated) else sumsq_plain
         if optimizer is not None and streaming and numel % 2 == 0 and g.flat_grad.dtype == _BF16:
             group = optimizer._group_of(p)
             state = optimizer._state_for(p, group)

@@ -104,18 +104,20 @@ class YvGradientSynchronizer:
         # squared norm of the reduced gradients that were consumed here (fused fold or consume_external_grad)
         # and are therefore no longer visible as ``p.grad``; reset at the first micro-batch of a step
         self.consumed_sq: Optional[torch.Tensor] = None
+        self.consumed_sq_rep: Optional[torch.Tensor] = None      # same, for tensors every tensor-parallel rank reduces too
         # three replication classes (the gradient scale is 1 / (dp * micro-batches) for all of them):
         #   routed experts            replicated over tp x edp   (tensor-parallel peers hold different tokens)
         #   sequence-parallel params  replicated over tp x dp    (norm weights, router, shared-expert mix)
         #   everything else           replicated over dp         (tp-sharded matrices, embeddings, LM head)
         dense, expert, seqpar = [], [], []
+        split_head = bool(getattr(getattr(model, "cfg", None), "tp_split_head", False))
         for n, p in model.named_parameters():
             if not p.requires_grad or getattr(p, "_yv_sharded", False):     # FULL_SHARD slices reduce themselves
                 continue
             if _is_expert_param(n):
                 expert.append((n, p))
-            elif parallel.tp_size > 1 and _is_sequence_parallel_param(n):
-                seqpar.append((n, p))
+            elif parallel.tp_size > 1 and (_is_sequence_parallel_param(n) or (split_head and n.endswith("lm_head"))):
+                seqpar.append((n, p))          # partial gradient per tensor-parallel rank: reduce over tp x dp
             else:
                 dense.append((n, p))
         self.groups: List[_FlatGroup] = []
@@ -145,10 +147,14 @@ class YvGradientSynchronizer:
         self._local_experts = [p for n, p in expert if id(p) not in self._managed] if parallel.ep_size > 1 else []
         # unmanaged parameters that are identical on all tensor-parallel ranks: their squared norm is weighted
         # 1 / tp when the ranks' contributions are summed
+        # Dense parameters that tensor parallelism does not split (embeddings, LM head, MTP heads) are computed on the
+        # full sequence by every tensor-parallel rank: each of the tp data-parallel groups reduces its own identical
+        # copy, so every such tensor appears tp times among "the gradients a rank alone accounts for", managed or not.
         self._tp_replicated = set()
+        self._tp_replicated_names = set()
         if parallel.tp_size > 1:
-            self._tp_replicated = {id(p) for n, p in dense if id(p) not in self._managed
-                                   and not _is_tp_sharded_param(n)}
+            self._tp_replicated = {id(p) for n, p in dense if not _is_tp_sharded_param(n)}
+            self._tp_replicated_names = {n for n, p in dense if not _is_tp_sharded_param(n)}
         self.tp_size = parallel.tp_size
         self._hooks = []
         for g in self.groups:
@@ -159,6 +165,13 @@ class YvGradientSynchronizer:
 
     def manages(self, p: torch.nn.Parameter) -> bool:
         return id(p) in self._managed
+
+    def consumed_sq_total(self) -> Optional[torch.Tensor]:
+        """Squared norm of the reduced gradients already handed to the optimizer, with the tensor-parallel
+        replicas weighted 1 / tp (None before the first step)."""
+        if self.consumed_sq is None:
+            return None
+        return self.consumed_sq + self.consumed_sq_rep / float(self.tp_size)
 
     def norm_weight(self, p: torch.nn.Parameter) -> float:
         """Weight of this rank's copy of ``p`` in the global squared gradient norm."""
@@ -172,6 +185,7 @@ class YvGradientSynchronizer:
             if self.groups:
                 dev = self.groups[0].flat_grad.device
                 self.consumed_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+                self.consumed_sq_rep = torch.zeros(1, dtype=torch.float32, device=dev)
 
     def _make_hook(self, g: _FlatGroup, name: str):
         def hook(p: torch.nn.Parameter) -> None:
@@ -190,7 +204,8 @@ class YvGradientSynchronizer:
             handled: List[str] = []
             if self.fused and g.symm_grad is not None:
                 from . import fused as fz
-                handled = fz.reduce_scatter_grads(g, scale, self.optimizer, sumsq=self.consumed_sq)
+                handled = fz.reduce_scatter_grads(g, scale, self.optimizer, sumsq=self.consumed_sq,
+                                                  sumsq_rep=self.consumed_sq_rep, replicated=self._tp_replicated_names)
             else:
                 shard = g.my_grad_shard()
                 if g.flat_grad.is_cuda:
@@ -205,11 +220,12 @@ class YvGradientSynchronizer:
                 grad = g.grad_views[n]
                 if hasattr(self.optimizer, "consume_external_grad"):
                     if self.consumed_sq is not None:
+                        acc = self.consumed_sq_rep if n in self._tp_replicated_names else self.consumed_sq
                         if grad.is_cuda:
                             from ..ops import kernels
-                            kernels().sumsq(grad.contiguous(), self.consumed_sq)
+                            kernels().sumsq(grad.contiguous(), acc)
                         else:
-                            self.consumed_sq += grad.float().pow(2).sum()
+                            acc += grad.float().pow(2).sum()
                     self.optimizer.consume_external_grad(p, grad)
                 else:
                     p.grad = grad

@@ -30,6 +30,9 @@ WORKER = textwrap.dedent("""
     cfg = YvConfig.tiny_text_moe(vocab_size=1024)
     cfg.n_layer = 2
     cfg.context_parallel = cp
+    if os.environ.get("YV_TEST_UNTIED") == "1":
+        cfg.tie_word_embeddings = False
+    cfg.tp_split_head = os.environ.get("YV_TEST_SPLIT_HEAD") == "1"
     cfg.context_parallel_mode = os.environ.get("YV_TEST_CP_MODE", "allgather")
     cfg.use_gradient_checkpointing = False
     cfg.extra["moe_deterministic"] = True
@@ -255,6 +258,25 @@ def test_pipeline_parallel_through_the_trainer_matches_single_process(tmp_path, 
     n_single = json.load(open(str(tmp_path / "loss_pp_single.json") + ".norms"))
     multi = _run(tmp_path, 2, 1, 1, steps, init_weights, "pp_w2", dict(env, YV_TEST_PP="2"))
     n_multi = json.load(open(str(tmp_path / "loss_pp_w2.json") + ".norms"))
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
+    for a, b in zip(n_single, n_multi):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (n_single, n_multi)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("world,tp,ep,split", [(2, 2, 1, "1"), (4, 2, 2, "1"), (4, 2, 2, "0")])
+def test_tensor_parallel_head_on_the_local_token_shard_matches_single_process(tmp_path, init_weights, world, tp, ep, split):
+    """``tp_split_head``: every tensor-parallel rank runs the LM head and the loss on its own token rows (no final
+    all-gather, no duplicated head work); the head weight's partial gradients are reduced over tp x dp.  Losses and
+    clipped gradient norms over three steps equal the single process.  The run without the flag on tp 2 x dp 2 pins
+    the norm accounting of the tensors that every tensor-parallel rank reduces a copy of (embeddings, head)."""
+    steps = 3
+    env = {"YV_TEST_CLIP": "1.0", "YV_TEST_BATCH": "4", "YV_TEST_UNTIED": "1"}
+    single = _run(tmp_path, 1, 1, 1, steps, init_weights, f"sh_single{world}", env)
+    n_single = json.load(open(str(tmp_path / f"loss_sh_single{world}.json") + ".norms"))
+    multi = _run(tmp_path, world, tp, ep, steps, init_weights, f"sh_w{world}", dict(env, YV_TEST_SPLIT_HEAD=split))
+    n_multi = json.load(open(str(tmp_path / f"loss_sh_w{world}.json") + ".norms"))
     for a, b in zip(single, multi):
         assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, multi)
     for a, b in zip(n_single, n_multi):
