@@ -126,12 +126,15 @@ class YvTokenSparseAttention(_ProjectedAttention):
         sc = torch.matmul(q[..., :r].float(), rep.transpose(-1, -2)) * r ** -0.5
         qblk = (torch.arange(S, device=q.device) + (T - S)) // self.bs
         blk = torch.arange(nb, device=q.device)
-        vis = blk[None, :] <= qblk[:, None]
-        p = torch.softmax(sc.masked_fill(~vis, float("-inf")), -1)
+        # Only STRICTLY EARLIER blocks are ranked: the mean key of the query's own block contains tokens after the
+        # query, and letting it into the softmax would make the choice of earlier blocks (hence the output of this
+        # token) depend on the future.  The own block is kept unconditionally and attended under the causal mask.
+        earlier = blk[None, :] < qblk[:, None]
+        p = torch.nan_to_num(torch.softmax(sc.masked_fill(~earlier, float("-inf")), -1), nan=0.0)
         ps, order = p.sort(-1, descending=True)
         before = ps.cumsum(-1) - ps                                           # mass accumulated before each block
         keep_sorted = (before < self.target) & (torch.arange(nb, device=q.device) < self.max_blocks)
-        sel = torch.zeros_like(p, dtype=torch.bool).scatter_(-1, order, keep_sorted) & vis
+        sel = torch.zeros_like(p, dtype=torch.bool).scatter_(-1, order, keep_sorted) & earlier
         sel |= (blk[None, :] == qblk[:, None])
         return sel
 
@@ -161,15 +164,18 @@ class YvHISAAttention(_ProjectedAttention):
         qblk = (torch.arange(S, device=q.device) + (T - S)) // self.bs
         blk = torch.arange(nb, device=q.device)
         sblk = torch.arange(ns, device=q.device)
-        s_vis = sblk[None, :] <= (qblk // self.sb)[:, None]
-        ssc = torch.matmul(q.float(), srep.transpose(-1, -2)).masked_fill(~s_vis, float("-inf"))
+        # Ranking uses representatives made of PAST tokens only: super-blocks strictly before the query's own, and
+        # blocks strictly before its own block.  The own super-block and the own block are always kept (the causal
+        # mask handles the tokens inside), so a later token can never change what an earlier one selects.
+        s_earlier = sblk[None, :] < (qblk // self.sb)[:, None]
+        ssc = torch.matmul(q.float(), srep.transpose(-1, -2)).masked_fill(~s_earlier, float("-inf"))
         sidx = ssc.topk(min(self.top_super, ns), -1).indices
-        ssel = torch.zeros(B, H, S, ns, dtype=torch.bool, device=q.device).scatter_(-1, sidx, True) & s_vis
+        ssel = torch.zeros(B, H, S, ns, dtype=torch.bool, device=q.device).scatter_(-1, sidx, True) & s_earlier
         ssel |= (sblk[None, :] == (qblk // self.sb)[:, None])
-        b_vis = (blk[None, :] <= qblk[:, None]) & ssel.repeat_interleave(self.sb, -1)[..., :nb]
-        bsc = torch.matmul(q.float(), rep.transpose(-1, -2)).masked_fill(~b_vis, float("-inf"))
+        b_earlier = (blk[None, :] < qblk[:, None]) & ssel.repeat_interleave(self.sb, -1)[..., :nb]
+        bsc = torch.matmul(q.float(), rep.transpose(-1, -2)).masked_fill(~b_earlier, float("-inf"))
         bidx = bsc.topk(min(self.top_blocks, nb), -1).indices
-        bsel = torch.zeros(B, H, S, nb, dtype=torch.bool, device=q.device).scatter_(-1, bidx, True) & b_vis
+        bsel = torch.zeros(B, H, S, nb, dtype=torch.bool, device=q.device).scatter_(-1, bidx, True) & b_earlier
         bsel |= (blk[None, :] == qblk[:, None])
         return bsel
 
@@ -183,8 +189,10 @@ class YvHISAAttention(_ProjectedAttention):
 class YvCirculantAttention(nn.Module):
     """Token mixing by a learned, input-conditioned circular convolution evaluated with FFTs (O(N log N)): per head,
     the softmax over positions of a pooled query-key product gives the first column of a circulant mixing matrix,
-    which multiplies the values in the frequency domain.  ``causal`` zero-pads to 2N so that the circular wrap does
-    not leak the future."""
+    which multiplies the values in the frequency domain.  ``causal`` zero-pads to 2N so that the convolution does not
+    wrap around (with a FIXED kernel, output t reads values at positions <= t only).  The kernel itself is pooled over
+    the whole sequence, so the layer is an encoder-style mixer and NOT autoregressive: it is not offered as a block of
+    the causal language model."""
 
     def __init__(self, hidden: int, n_head: int, causal: bool = True):
         super().__init__()

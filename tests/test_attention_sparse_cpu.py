@@ -2,6 +2,7 @@
 its definition, and each variant against dense causal attention in the limit where it must agree."""
 from __future__ import annotations
 
+import pytest
 import torch
 
 from pisceslx_b200.models.attention_sparse import (YvAttentionMaskFactory, YvCirculantAttention, YvDynamicH2OAttention,
@@ -59,13 +60,14 @@ def test_token_sparse_mass_target_and_hisa():
     assert sel.sum() < all_.select(q, k).sum()
     # the kept blocks hold at least the target mass of the representative softmax
     qblk = torch.arange(96) // 8
-    vis = torch.arange(12)[None, :] <= qblk[:, None]
+    vis = torch.arange(12)[None, :] < qblk[:, None]              # strictly earlier blocks are the ranked ones
     from pisceslx_b200.models.attention_sparse import _block_means
     p = torch.softmax((q.float() @ _block_means(k, 8).transpose(-1, -2) * 8 ** -0.5).masked_fill(~vis, float("-inf")), -1)
-    assert ((p * sel).sum(-1) >= 0.5 - 1e-5).all()
+    has_past = qblk > 0
+    assert ((torch.nan_to_num(p) * sel).sum(-1)[..., has_past] >= 0.5 - 1e-5).all()
     h = YvHISAAttention(32, 4, block_size=8, super_size=3, top_super=1, top_blocks=2)
     hs = h.select(*h.qkv(x)[:2])
-    assert hs[..., torch.arange(96), qblk].all() and int(hs.sum(-1).max()) <= 3
+    assert hs[..., torch.arange(96), qblk].all() and int(hs.sum(-1).max()) <= 3      # two ranked blocks + the own block
     later = torch.arange(12)[None, :] > qblk[:, None]
     assert not (hs & later).any()
     hfull = YvHISAAttention(32, 4, block_size=8, super_size=3, top_super=9, top_blocks=99)
@@ -140,3 +142,27 @@ def test_egmla_cache_and_memory_cross_attention():
     y2 = mc(x, mem, mask)
     mem2 = mem.clone(); mem2[1, 2:] = 9.0
     assert torch.allclose(mc(x, mem2, mask), y2, atol=1e-5)
+
+
+@pytest.mark.parametrize("cls,kw", [("YvTokenSparseAttention", dict(block_size=8, target=0.5, max_blocks=3)),
+                                    ("YvMixtureBlockAttention", dict(block_size=8, top_k=2)),
+                                    ("YvHISAAttention", dict(block_size=8, super_size=2, top_super=1, top_blocks=2))])
+def test_block_sparse_attention_is_structurally_causal(cls, kw):
+    """Perturbing one token leaves every EARLIER output bit-identical, selection map included: block representatives
+    that contain future tokens must never take part in a ranking (the reference states the same contract for its
+    token-sparse layer, tools/test/test_block_sparse_attn_contract.py:103)."""
+    import pisceslx_b200.models.attention_sparse as A
+    torch.manual_seed(0)
+    m = getattr(A, cls)(64, 4, **kw)
+    x = torch.randn(2, 64, 64)
+    y = m(x)
+    q, k, _ = m.qkv(x)
+    sel = m.select(q, k)
+    for j in (5, 21, 43, 62):
+        x2 = x.clone()
+        x2[:, j] += torch.randn(64)
+        y2 = m(x2)
+        q2, k2, _ = m.qkv(x2)
+        assert torch.equal(y[:, :j], y2[:, :j]), (cls, j)
+        assert torch.equal(sel[:, :, :j], m.select(q2, k2)[:, :, :j]), (cls, j)
+        assert not torch.equal(y[:, j:], y2[:, j:])
