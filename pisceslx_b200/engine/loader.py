@@ -42,6 +42,9 @@ def attach_optional_components(model: Any, cfg: YvConfig, parallel: Any = None) 
     elif cfg.use_subconscious and trunk.subconscious is None:
         from ..models.subconscious import YvSubconsciousSystem
         trunk.attach("subconscious", YvSubconsciousSystem(cfg).to(p.device))
+    if getattr(cfg, "use_subconscious_blocks", False) and trunk.block_field is None:
+        from ..models.block_field import YvSubconsciousBlockField
+        trunk.attach("block_field", YvSubconsciousBlockField.from_config(cfg).to(p.device))
     if cfg.vision_hidden_size and trunk.vision_encoder is None:
         from ..models.multimodal import attach_multimodal
         attach_multimodal(model, vision=True)

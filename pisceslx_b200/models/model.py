@@ -63,6 +63,8 @@ class YvModel(nn.Module):
                                         cfg.max_position_embeddings) if cfg.use_rotary_pos_emb else None
         # optional components, attached by their builders (lazy like the reference, model.py:1276-1516)
         self.subconscious: Optional[nn.Module] = None      # YvSubconsciousSystem / YvPQKnowledgeField
+        self.block_field: Optional[nn.Module] = None       # YvSubconsciousBlockField: applied once, to the embeddings
+        self.block_field_diagnostics: Optional[dict] = None
         self.vision_encoder: Optional[nn.Module] = None
         self.video_encoder: Optional[nn.Module] = None
         self.audio_encoder: Optional[nn.Module] = None
@@ -138,6 +140,10 @@ class YvModel(nn.Module):
             h = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids, attention_mask)
             if prefix_embeds is not None:
                 h = torch.cat([prefix_embeds.to(h.dtype), h], dim=1)
+            if self.block_field is not None and ctx is None:
+                # one read per forward, before the first layer; only values leave through the diagnostics
+                h, diag = self.block_field.read_and_modulate(h)
+                self.block_field_diagnostics = {k: v for k, v in diag.items() if not torch.is_tensor(v)}
         else:
             h = hidden_in
         B, S, H = h.shape

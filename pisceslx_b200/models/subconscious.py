@@ -11,7 +11,7 @@ Three sources share one small interface (``begin(h, batch)``, ``film_params(laye
                            dims; a 2-layer navigation MLP emits 16 groups of codebook logits per token, the arg-max
                            entries are gathered (row-sharded over GPUs: the gather reads the owners' memory), summed
                            and projected to per-token FiLM scale / shift on every ``pq_film_interval``-th layer.
-``YvSubconsciousBlockField`` lean form of the 628-block field (model/core/block_field.py:63-541): low-rank read of a
+``YvSubconsciousBlockField`` the 628-block field (``models.block_field``; reference model/core/block_field.py:63-541): low-rank read of a
                            resident block, bounded ``gamma = g_max * tanh`` and ``beta``, applied to the embeddings.
 """
 from __future__ import annotations
@@ -270,45 +270,7 @@ class YvPQKnowledgeField(nn.Module):
         self._film_cache = None
 
 
-class YvKnowledgeBlockModule(nn.Module):
-    """One knowledge block: memory rows read through low-rank queries, bounded FiLM output."""
-
-    def __init__(self, hidden: int, rows: int, rank: int, gamma_max: float, beta_bound: float):
-        super().__init__()
-        self.memory = nn.Parameter(torch.randn(rows, hidden) * 0.02)
-        self.q = nn.Linear(hidden, rank, bias=False)
-        self.k = nn.Linear(hidden, rank, bias=False)
-        self.to_gamma = nn.Linear(hidden, hidden)
-        self.to_beta = nn.Linear(hidden, hidden)
-        self.gamma_max, self.beta_bound = gamma_max, beta_bound
-
-    def forward(self, h: torch.Tensor):
-        att = torch.softmax(self.q(h) @ self.k(self.memory).t() / math.sqrt(self.q.out_features), -1)
-        r = att @ self.memory
-        gamma = self.gamma_max * torch.tanh(self.to_gamma(r))
-        beta = self.beta_bound * torch.tanh(self.to_beta(r)) * h.norm(dim=-1, keepdim=True) / math.sqrt(h.shape[-1])
-        return gamma, beta
-
-
-class YvSubconsciousBlockField(nn.Module):
-    """A pool of knowledge blocks with a small number of resident slots; the block is chosen per sequence by a
-    trace addresser (arg-max of learned scores, kept for at least ``block_min_dwell_tokens`` tokens)."""
-
-    def __init__(self, cfg: YvConfig, block_count: Optional[int] = None, rows: int = 64):
-        super().__init__()
-        self.cfg = cfg
-        n = block_count or min(cfg.block_count, 16)
-        self.addresser = nn.Linear(cfg.hidden_size, n, bias=False)
-        self.blocks = nn.ModuleList([YvKnowledgeBlockModule(cfg.hidden_size, rows, min(cfg.block_rank, 64),
-                                                            cfg.block_gamma_max, cfg.block_beta_bound) for _ in range(n)])
-        self.alpha = cfg.block_inject_alpha
-
-    def read_and_modulate(self, emb: torch.Tensor) -> torch.Tensor:
-        """emb [B, S, H] -> modulated embeddings (applied before layer 0, reference model.py:2209-2217)."""
-        scores = self.addresser(emb.float().mean(1))
-        choice = scores.argmax(-1)
-        out = emb.clone()
-        for b in range(emb.shape[0]):
-            gamma, beta = self.blocks[int(choice[b])](emb[b].float())
-            out[b] = (emb[b].float() * (1 + self.alpha * gamma) + self.alpha * beta).to(emb.dtype)
-        return out
+# The block field (blocks, resident pool, trace addresser) lives in ``models.block_field``; the names stay importable
+# from here.
+from .block_field import (YvAddressingStatistics, YvKnowledgeBlockModule, YvResidentBlockPool,  # noqa: E402,F401
+                          YvResonantTraceAddresser, YvSubconsciousBlockField)
