@@ -153,10 +153,33 @@ class YvResonantTraceAddresser(nn.Module):
             out[b] = torch.tensor(fixed, dtype=selected.dtype, device=selected.device)
         return out
 
-    def select_sequence(self, hidden: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        """hidden [B, T, d] -> (ids [B, T] with the dwell floor applied, scores [B, T, n_blocks] with grad)."""
+    def select_sequence(self, hidden: torch.Tensor, max_distinct: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """hidden [B, T, d] -> (ids [B, T], scores [B, T, n_blocks] with grad).  The ids obey the dwell floor and, with
+        ``max_distinct``, use at most that many different blocks in the whole call (what fits the device at once): a
+        request for one block too many is answered with the best-scoring block among those already in use.  Every
+        decision depends on earlier tokens of the row (and on earlier rows of the batch) only."""
         s = self.scores(hidden)
-        ids = self.apply_dwell_constraint(s.argmax(-1), self.min_dwell)
+        raw = s.argmax(-1)
+        if max_distinct is None:
+            ids = self.apply_dwell_constraint(raw, self.min_dwell)
+        else:
+            sc = s.detach().float().cpu()
+            used: List[int] = []
+            ids = raw.clone()
+            for b, row in enumerate(raw.detach().cpu().tolist()):
+                cur, run, fixed = None, 0, []
+                for t, v in enumerate(row):
+                    if cur is None or (v != cur and run >= self.min_dwell):
+                        if v not in used:
+                            if len(used) < max_distinct:
+                                used.append(v)
+                            else:
+                                v = used[int(sc[b, t, used].argmax())]
+                        if v != cur:
+                            cur, run = v, 0
+                    fixed.append(cur)
+                    run += 1
+                ids[b] = torch.tensor(fixed, dtype=raw.dtype, device=raw.device)
         self.stats.record(ids)
         return ids, s
 
@@ -289,14 +312,13 @@ class YvSubconsciousBlockField(nn.Module):
         if hidden.dim() != 3:
             raise ValueError(f"read_and_modulate expects [B, T, d], got {tuple(hidden.shape)}")
         B, T, d = hidden.shape
-        selected, scores = self.addresser.select_sequence(hidden)
+        # at most ``slots`` different blocks per call: all of them are resident together, so none is evicted while
+        # the autograd graph of this forward still points at its parameters
+        selected, scores = self.addresser.select_sequence(hidden, max_distinct=self.pool.slots)
         gate = self._straight_through_gate(scores, selected)
         flat = hidden.reshape(B * T, d)
         ids = selected.reshape(-1)
-        uniq = torch.unique(ids).tolist()
-        # most used blocks first: if more blocks are asked for than there are slots, the rarest go without
-        uniq.sort(key=lambda u: -int((ids == u).sum()))
-        served = uniq[: self.pool.slots]
+        served = uniq = torch.unique(ids).tolist()
         out = flat.float()
         for u in served:
             m = self._ensure_resident(int(u), hidden.device)
