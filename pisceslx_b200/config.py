@@ -89,7 +89,7 @@ class YvConfig:
     moe_dropout: float = 0.0
     moe_expert_intermediate_size: Optional[int] = None
     moe_shared_intermediate_size: Optional[int] = None
-    moe_gate_type: str = "stable"          # "stable" (YvStableMoEGate) | "lean" (YvMoEGate)
+    moe_gate_type: str = "stable"          # "stable" (YvStableMoEGate) | "lean" (YvMoEGate) | "research" (YvResearchMoEGate)
     moe_use_load_predictor: bool = False    # optional LSTM load predictor of YvStableMoEGate
     moe_drop_tokens: bool = False           # capacity dropping (lowest score dropped by zeroing)
     moe_skip_prev_shared: bool = False      # the 0.1 * previous shared output skip term

@@ -86,6 +86,14 @@ class YvTransformerBlock(nn.Module):
                                       int(ex.get("mamba_expand", 2)), init_std=cfg.initializer_range)
             self.fusion = YvUnifiedFusion(cfg.hidden_size)
             self.sparse_gate_ssm = nn.Parameter(torch.zeros(()))
+            self.sparsity_reg_weight = float(ex.get("ssm_sparsity_reg_weight", 1e-4))
+
+    def sparsity_loss(self) -> Optional[torch.Tensor]:
+        """Regulariser of the gate in front of the SSM branch (reference model/core/hybrid.py:1298-1307); parameters
+        only, folded into the objective by the trunk's walk."""
+        if self.ssm is None:
+            return None
+        return self.sparsity_reg_weight * torch.sigmoid(self.sparse_gate_ssm.float())
 
     def _body(self, recomputing: bool, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: AttnContext,
               film: Optional[Dict[str, torch.Tensor]]):

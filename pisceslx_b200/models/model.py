@@ -72,6 +72,24 @@ class YvModel(nn.Module):
         self.materialized_components: List[str] = []
 
     # ------------------------------------------------------------------------------------------------
+    def sparsity_objective(self) -> Optional[torch.Tensor]:
+        """Sum of the parameter-only sparsity regularisers that this module's descendants declare through a callable
+        ``sparsity_loss`` (reference model/core/model.py:1951-1976).  Each is the objective of its own gate - a learned
+        scalar in front of a sparse branch - and depends on parameters only, so it is evaluated here at loss time rather
+        than threaded out of every layer's forward.  It must not ride inside the routing loss: the aux-loss-free
+        balancing mode keeps that lump out of the objective, which would leave the gates untrained.  ``modules()`` yields
+        every submodule once, so a nested contributor is counted once.  Also callable unbound on any module tree."""
+        total = None
+        for module in self.modules():
+            accessor = getattr(module, "sparsity_loss", None)
+            if not callable(accessor):
+                continue
+            term = accessor()
+            if not isinstance(term, torch.Tensor) or not term.requires_grad:
+                continue
+            total = term if total is None else total + term
+        return total
+
     def attach(self, name: str, module: nn.Module) -> None:
         setattr(self, name, module)
         if name not in self.materialized_components:
@@ -189,6 +207,31 @@ class YvModelForCausalLM(nn.Module):
         """hidden [..., H] -> fp32 logits [..., V] (inference / evaluation only)."""
         return F_.linear(hidden, self.head_weight, out_fp32=True)
 
+    def sparsity_objective(self) -> Optional[torch.Tensor]:
+        """The trunk's walk over this whole model.  The contributors are looked up once per training / evaluation
+        switch (the walk visits thousands of modules on a deep model and the step is launch-bound on the host).  With
+        sequence-parallel tensor parallelism the gradients of replicated parameters are SUMMED over the group, because
+        each rank normally holds the part of its own tokens; a parameter-only term is whole on every rank, so it is
+        divided by the group size here."""
+        found = self.__dict__.get("_sparsity_contributors")
+        if found is None:
+            found = [m for m in self.modules() if m is not self and m is not self.model
+                     and callable(getattr(m, "sparsity_loss", None))]
+            self.__dict__["_sparsity_contributors"] = found
+        total = None
+        for m in found:
+            term = m.sparsity_loss()
+            if isinstance(term, torch.Tensor) and term.requires_grad:
+                total = term if total is None else total + term
+        par = self.parallel
+        if total is not None and par is not None and par.tp_size > 1 and self.cfg.sequence_parallel:
+            total = total / par.tp_size
+        return total
+
+    def train(self, mode: bool = True):
+        self.__dict__.pop("_sparsity_contributors", None)
+        return super().train(mode)
+
     def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
                 labels: Optional[torch.Tensor] = None, prefix_embeds: Optional[torch.Tensor] = None,
                 inputs_embeds: Optional[torch.Tensor] = None, ctx: Optional[AttnContext] = None,
@@ -240,6 +283,9 @@ class YvModelForCausalLM(nn.Module):
                 loss = loss + mtp
             if not cfg.moe_aux_loss_free:
                 loss = loss + cfg.moe_aux_loss_weight * aux
+            sparsity_loss = self.sparsity_objective()
+            if sparsity_loss is not None:
+                loss = loss + sparsity_loss
             res["loss"] = loss
         return res
 
@@ -272,6 +318,9 @@ class YvModelForCausalLM(nn.Module):
         dist.all_reduce(tot, group=par.tp_group)
         lm_loss = local + (tot - local.detach())
         loss = lm_loss if cfg.moe_aux_loss_free else lm_loss + cfg.moe_aux_loss_weight * aux
+        sparsity_loss = self.sparsity_objective()
+        if sparsity_loss is not None:
+            loss = loss + sparsity_loss
         return YvModelOutput(aux_loss=aux, loss=loss, lm_loss=lm_loss, mtp_loss=None, logits=None)
 
     def _forward_context_parallel(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor],
@@ -305,6 +354,9 @@ class YvModelForCausalLM(nn.Module):
             res["lm_loss"] = res["loss"] = lm
             if not cfg.moe_aux_loss_free:
                 res["loss"] = lm + cfg.moe_aux_loss_weight * aux
+            sparsity_loss = self.sparsity_objective()
+            if sparsity_loss is not None:
+                res["loss"] = res["loss"] + sparsity_loss      # whole on every rank; the ranks' losses are averaged
         return res
 
     # ------------------------------------------------------------------------------------------------

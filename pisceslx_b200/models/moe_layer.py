@@ -34,7 +34,11 @@ class YvDeepSeekMoELayer(nn.Module):
         assert E % ep_size == 0
         self.num_experts, self.num_local = E, E // ep_size
         self.ffn = F
-        gate_cls = YvStableMoEGate if cfg.moe_gate_type == "stable" else YvMoEGate
+        if cfg.moe_gate_type == "research":
+            from .moe_gate_research import YvResearchMoEGate
+            gate_cls = YvResearchMoEGate
+        else:
+            gate_cls = YvStableMoEGate if cfg.moe_gate_type == "stable" else YvMoEGate
         self.router = gate_cls(cfg)
         std = cfg.initializer_range
         out_std = std / math.sqrt(2 * cfg.n_layer) if cfg.use_scaled_init else std

@@ -184,8 +184,11 @@ class YvHybridBlock(nn.Module):
         self.sparse_gate_ssm = nn.Parameter(torch.zeros(()))
         self.sparsity_reg_weight = float(ex.get("ssm_sparsity_reg_weight", 1e-4))
 
-    def sparsity_objective(self) -> torch.Tensor:
-        return self.sparsity_reg_weight * torch.sigmoid(self.sparse_gate_ssm)
+    def sparsity_loss(self) -> torch.Tensor:
+        """Parameter-only regulariser of the SSM gate; the trunk's ``sparsity_objective`` walk sums it."""
+        return self.sparsity_reg_weight * torch.sigmoid(self.sparse_gate_ssm.float())
+
+    sparsity_objective = sparsity_loss
 
     def forward(self, x: torch.Tensor, ctx: Any = None, film_params: Optional[Dict[str, torch.Tensor]] = None):
         """x [B, S, H] -> (x', aux)."""
