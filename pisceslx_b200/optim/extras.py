@@ -70,8 +70,9 @@ class PiscesLxGaLoreAdamW(torch.optim.Optimizer):
         return sum(t.numel() * t.element_size() for s in self.state.values() for t in s.values() if torch.is_tensor(t))
 
 
-class PiscesLxROOTOptimizer(torch.optim.Optimizer):
-    """Robust orthogonalised optimizer: momentum -> outlier clipping of the update by a soft threshold (a proximal
+class PiscesLxROOTMomentumOptimizer(torch.optim.Optimizer):
+    """The momentum-only form of the robust orthogonalised optimizer (``optim.root.PiscesLxROOTOptimizer`` is the
+    configured form with Adam moments, soft threshold and spectral clip): momentum -> outlier clipping of the update by a soft threshold (a proximal
     step that removes gradient spikes) -> Newton-Schulz orthogonalisation with shape-adapted scaling."""
 
     def __init__(self, params, lr=2e-4, momentum=0.95, weight_decay=0.0, ns_steps=5, outlier_quantile=0.99):
@@ -98,6 +99,9 @@ class PiscesLxROOTOptimizer(torch.optim.Optimizer):
                 if g["weight_decay"]:
                     p.mul_(1 - g["lr"] * g["weight_decay"])
                 p.add_(upd.to(p.dtype), alpha=-g["lr"])
+
+
+PiscesLxROOTOptimizer = PiscesLxROOTMomentumOptimizer           # the name this class had before optim/root.py existed
 
 
 class PiscesLxTERAIOManager:
