@@ -427,7 +427,7 @@ class PiscesLxPPOOperator:
             self.opt.zero_grad(set_to_none=True)
             loss.backward()
             self.opt.step()
-            stats = {"policy_loss": float(pg), "value_loss": float(vf)}
+            stats = {"policy_loss": float(pg.detach()), "value_loss": float(vf.detach())}
         kl_mean = float(kl_tok.sum() / m.sum().clamp_min(1))
         self.kl.update(kl_mean, ids.shape[0])
         self.model.train(was_training)
