@@ -132,6 +132,84 @@ class YvPredictiveDeltaCoder(nn.Module):
         return (kv.float() - self.predict(prev_hidden).float()).pow(2).mean()
 
 
+class YvDeltaCacheEntry:
+    """One delta-coded block of keys / values: the quantised residuals and their scales, and (optionally) the predictions
+    that were subtracted, so that the block can be rebuilt without the predictor (reference model/core/
+    predictive_delta.py:443-510).  With ``pack=True`` residuals of 4 bits or fewer are held two per byte; ``residual_k`` /
+    ``residual_v`` always return int8 codes."""
+
+    def __init__(self, residual_k: torch.Tensor, residual_v: torch.Tensor, scale_k: torch.Tensor, scale_v: torch.Tensor,
+                 pred_k: Optional[torch.Tensor] = None, pred_v: Optional[torch.Tensor] = None, pack: bool = False):
+        self._packed = bool(pack) and residual_k.shape[-1] % 2 == 0 and residual_v.shape[-1] % 2 == 0
+        self._rk = self._pack(residual_k) if self._packed else residual_k
+        self._rv = self._pack(residual_v) if self._packed else residual_v
+        self.scale_k, self.scale_v, self.pred_k, self.pred_v = scale_k, scale_v, pred_k, pred_v
+
+    @staticmethod
+    def _pack(q: torch.Tensor) -> torch.Tensor:
+        u = (q.to(torch.int16) & 0xF).to(torch.uint8)
+        return u[..., 0::2] | (u[..., 1::2] << 4)
+
+    @staticmethod
+    def _unpack(p: torch.Tensor) -> torch.Tensor:
+        lo, hi = (p & 0xF).to(torch.int8), (p >> 4).to(torch.int8)
+        lo, hi = torch.where(lo > 7, lo - 16, lo), torch.where(hi > 7, hi - 16, hi)
+        return torch.stack([lo, hi], -1).flatten(-2)
+
+    @property
+    def residual_k(self) -> torch.Tensor:
+        return self._unpack(self._rk) if self._packed else self._rk
+
+    @property
+    def residual_v(self) -> torch.Tensor:
+        return self._unpack(self._rv) if self._packed else self._rv
+
+    @classmethod
+    def encode(cls, coder_k: "YvPredictiveDeltaCoder", coder_v: "YvPredictiveDeltaCoder", k: torch.Tensor, v: torch.Tensor,
+               prev_hidden: torch.Tensor, prev_k: Optional[torch.Tensor] = None, prev_v: Optional[torch.Tensor] = None,
+               keep_predictions: bool = False) -> "YvDeltaCacheEntry":
+        qk, sk = coder_k.encode(k, prev_hidden, prev_k)
+        qv, sv = coder_v.encode(v, prev_hidden, prev_v)
+        pk = coder_k.predict(prev_hidden, prev_k).detach() if keep_predictions else None
+        pv = coder_v.predict(prev_hidden, prev_v).detach() if keep_predictions else None
+        return cls(qk, qv, sk, sv, pk, pv, pack=max(coder_k.bits, coder_v.bits) <= 4)
+
+    def decode(self, coder_k: Optional["YvPredictiveDeltaCoder"] = None, coder_v: Optional["YvPredictiveDeltaCoder"] = None,
+               prev_hidden: Optional[torch.Tensor] = None, prev_k: Optional[torch.Tensor] = None, prev_v: Optional[torch.Tensor] = None):
+        """(k, v): from the stored predictions when they were kept, else from the predictors and ``prev_hidden``."""
+        if self.pred_k is not None and self.pred_v is not None:
+            return (self.pred_k.float() + self.residual_k.float() * self.scale_k, self.pred_v.float() + self.residual_v.float() * self.scale_v)
+        if coder_k is None or coder_v is None or prev_hidden is None:
+            raise ValueError("the predictions were not kept: the predictors and prev_hidden are needed to decode")
+        return (coder_k.decode(self.residual_k, self.scale_k, prev_hidden, prev_k), coder_v.decode(self.residual_v, self.scale_v, prev_hidden, prev_v))
+
+    @property
+    def num_tokens(self) -> int:
+        r = self._rk
+        return r.shape[-2] if r.dim() >= 2 else 1
+
+    @property
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self._rk, self._rv, self.scale_k, self.scale_v, self.pred_k, self.pred_v) if t is not None)
+
+    def _map(self, fn) -> "YvDeltaCacheEntry":
+        e = object.__new__(YvDeltaCacheEntry)
+        e._packed = self._packed
+        e._rk, e._rv, e.scale_k, e.scale_v = fn(self._rk), fn(self._rv), fn(self.scale_k), fn(self.scale_v)
+        e.pred_k = fn(self.pred_k) if self.pred_k is not None else None
+        e.pred_v = fn(self.pred_v) if self.pred_v is not None else None
+        return e
+
+    def to(self, device) -> "YvDeltaCacheEntry":
+        return self._map(lambda t: t.to(device))
+
+    def detach(self) -> "YvDeltaCacheEntry":
+        return self._map(lambda t: t.detach())
+
+    def clone(self) -> "YvDeltaCacheEntry":
+        return self._map(lambda t: t.clone())
+
+
 @dataclass
 class _TrieNode:
     children: Dict[int, "_TrieNode"] = field(default_factory=dict)

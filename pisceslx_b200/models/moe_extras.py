@@ -108,8 +108,9 @@ class YvExpertDiversityRegularizer:
         return self.weight * off.pow(2).sum() / max(E * (E - 1), 1)
 
 
-class YvGradientClusterInitializer:
-    """Initialises experts from k-means centroids of per-token gradient (or activation) features so that experts start
+class YvGateClusterInitializer:
+    """The gate-only form (``models/expert_init.YvGradientClusterInitializer`` is the full one: streamed gradient
+    statistics per parameter, elbow choice of k, experts displaced by cluster).  Initialises experts from k-means centroids of per-token gradient (or activation) features so that experts start
     specialised on different clusters."""
 
     def __init__(self, num_experts: int, iters: int = 10, seed: int = 0):
@@ -132,6 +133,9 @@ class YvGradientClusterInitializer:
         cent, _ = self.cluster(feats)
         with torch.no_grad():
             gate_weight.copy_(F.normalize(cent, dim=1).to(gate_weight.dtype) * gate_weight.float().norm(dim=1).mean())
+
+
+YvGradientClusterInitializer = YvGateClusterInitializer        # the name this class had before models/expert_init.py existed
 
 
 class YvExpertEvolution:
