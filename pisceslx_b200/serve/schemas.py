@@ -245,3 +245,25 @@ class PiscesLxAudioSpeechResponse(BaseModel):
     sample_rate: int
     samples: int
     b64_pcm16: str                              # base64 of little-endian int16 PCM
+
+
+class PiscesLxResponseFormat(BaseModel):
+    type: str = "text"                              # "text" | "json_object"
+
+
+class PiscesLxTool(BaseModel):
+    type: str = "function"
+    function: Dict[str, Any]
+
+
+class PiscesLxServiceStats(BaseModel):
+    uptime_seconds: float = 0
+    request_count: int = 0
+    success_count: int = 0
+    error_count: int = 0
+    qps: float = 0
+    latency_p50_ms: Optional[float] = None
+    latency_p95_ms: Optional[float] = None
+    model_size: Optional[str] = None
+    engine_status: Optional[Dict[str, Any]] = None
+    resource: Optional[Dict[str, Any]] = None
