@@ -4,7 +4,9 @@
 ``YvExpertDiversityRegularizer``; model/moe/layer.py ``YvDynamicMoELayer`` :519-963)."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from dataclasses import dataclass
+from enum import Enum
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -153,3 +155,139 @@ class YvExpertEvolution:
         for w in stacked_weights:
             w[lo].copy_(w[hi] + self.noise * w[hi].float().std().to(w.dtype) * torch.randn_like(w[hi]))
         return lo, hi
+
+
+# ------------------------------------------------------------------------------------------------ configured experts
+class YvExpertType(str, Enum):
+    STANDARD = "standard"
+    SWIGLU = "swiglu"
+    GEGLU = "geglu"
+    MULTI_LAYER = "multi_layer"
+    SHARED = "shared"
+    ATTENTION = "attention"
+
+
+class YvExpertMode(str, Enum):
+    PURE_COMPUTE = "pure_compute"      # a trainable feed-forward expert
+    PURE_LOOKUP = "pure_lookup"        # frozen: static knowledge storage beside the reasoning experts
+
+
+@dataclass
+class YvExpertConfig:
+    hidden_size: int = 2048
+    intermediate_size: int = 5632
+    expert_type: YvExpertType = YvExpertType.SWIGLU
+    dropout: float = 0.0
+    use_bias: bool = False
+    activation: str = "silu"
+    mode: YvExpertMode = YvExpertMode.PURE_COMPUTE
+    num_layers: int = 2                # multi-layer experts
+    num_heads: int = 4                 # attention experts
+    init_std: float = 0.02
+
+    def __post_init__(self) -> None:
+        self.expert_type = YvExpertType(getattr(self.expert_type, "value", self.expert_type))
+        self.mode = YvExpertMode(getattr(self.mode, "value", self.mode))
+        if self.activation not in ("silu", "gelu", "relu"):
+            raise ValueError(f"unknown activation {self.activation}")
+
+
+class YvExpertBase(nn.Module):
+    """An expert built from a ``YvExpertConfig`` (reference model/moe/expert.py:231-290): ``forward(x)`` keeps the shape of
+    ``x`` ([tokens, hidden] or [batch, sequence, hidden]); a ``PURE_LOOKUP`` expert is frozen after construction."""
+
+    def __init__(self, config: YvExpertConfig, mode: Optional[YvExpertMode] = None):
+        super().__init__()
+        self.config = config
+        self.mode = YvExpertMode(getattr(mode, "value", mode)) if mode is not None else config.mode
+        self.drop = nn.Dropout(config.dropout) if config.dropout > 0 else nn.Identity()
+
+    def _freeze_if_lookup(self) -> None:
+        if self.mode is YvExpertMode.PURE_LOOKUP:
+            for p in self.parameters():
+                p.requires_grad_(False)
+
+    def body(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError("an expert implements body(x)")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.drop(self.body(x))
+
+
+class _WrappedExpert(YvExpertBase):
+    def __init__(self, config: YvExpertConfig, core: nn.Module, mode: Optional[YvExpertMode] = None):
+        super().__init__(config, mode)
+        self.core = core
+        self._freeze_if_lookup()
+
+    def body(self, x: torch.Tensor) -> torch.Tensor:
+        return self.core(x)
+
+
+class YvSharedExpert(YvExpertBase):
+    """The always-on expert beside the routed ones: a SwiGLU block whose output is scaled by a learned sigmoid gate of the
+    token (so the layer can learn how much every token leans on shared knowledge)."""
+
+    def __init__(self, config: YvExpertConfig, mode: Optional[YvExpertMode] = None):
+        super().__init__(config, mode)
+        self.core = YvSwiGLUExpert(config.hidden_size, config.intermediate_size, config.init_std)
+        self.gate = nn.Parameter(torch.zeros(1, config.hidden_size))
+        self._freeze_if_lookup()
+
+    def body(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.sigmoid(F_.linear(x, self.gate.to(x.dtype))) * 2.0 * self.core(x)
+
+
+class YvAttentionExpert(YvExpertBase):
+    """An expert that mixes along the sequence: causal self-attention over the tokens it is given, then a projection.  It needs
+    [batch, sequence, hidden] input; a flat [tokens, hidden] input is treated as one sequence."""
+
+    def __init__(self, config: YvExpertConfig, mode: Optional[YvExpertMode] = None):
+        super().__init__(config, mode)
+        h = config.hidden_size
+        if h % config.num_heads:
+            raise ValueError("hidden_size must be a multiple of num_heads")
+        self.qkv = nn.Parameter(torch.empty(3 * h, h).normal_(std=config.init_std))
+        self.o = nn.Parameter(torch.empty(h, h).normal_(std=config.init_std))
+        self._freeze_if_lookup()
+
+    def body(self, x: torch.Tensor) -> torch.Tensor:
+        flat = x.dim() == 2
+        x3 = x.unsqueeze(0) if flat else x
+        B, T, H = x3.shape
+        nh = self.config.num_heads
+        q, k, v = F_.linear(x3, self.qkv.to(x.dtype)).view(B, T, 3, nh, H // nh).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=T > 1).transpose(1, 2).reshape(B, T, H)
+        out = F_.linear(a, self.o.to(x.dtype))
+        return out[0] if flat else out
+
+
+def _core_for(c: YvExpertConfig) -> nn.Module:
+    t = c.expert_type
+    if t is YvExpertType.SWIGLU:
+        return YvSwiGLUExpert(c.hidden_size, c.intermediate_size, c.init_std)
+    if t is YvExpertType.GEGLU:
+        return YvGeGLUExpert(c.hidden_size, c.intermediate_size, c.init_std)
+    if t is YvExpertType.STANDARD:
+        return YvStandardExpert(c.hidden_size, c.intermediate_size, c.activation, c.init_std)
+    if t is YvExpertType.MULTI_LAYER:
+        return YvMultiLayerExpert(c.hidden_size, c.intermediate_size, c.num_layers, c.init_std)
+    raise ValueError(f"no feed-forward core for {t}")
+
+
+_EXPERT_REGISTRY: Dict[YvExpertType, Callable[[YvExpertConfig, Optional[YvExpertMode]], YvExpertBase]] = {
+    YvExpertType.SHARED: YvSharedExpert, YvExpertType.ATTENTION: YvAttentionExpert}
+
+
+def create_expert(config: YvExpertConfig, mode: Optional[YvExpertMode] = None) -> YvExpertBase:
+    """The configured-expert constructor (``YvExpertFactory.create`` builds bare cores from sizes)."""
+    maker = _EXPERT_REGISTRY.get(config.expert_type)
+    return maker(config, mode) if maker is not None else _WrappedExpert(config, _core_for(config), mode)
+
+
+def register_expert(expert_type: YvExpertType, expert_class: Callable[[YvExpertConfig, Optional[YvExpertMode]], YvExpertBase]) -> None:
+    _EXPERT_REGISTRY[YvExpertType(getattr(expert_type, "value", expert_type))] = expert_class
+
+
+YvExpertFactory.create_from_config = staticmethod(create_expert)
+YvExpertFactory.register = staticmethod(register_expert)
