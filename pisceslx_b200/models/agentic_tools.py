@@ -472,3 +472,22 @@ class YvReActEngine:
                 self.sm.to(YvAgenticState.ACTING, "continue")
         return {"answer": answer, "state": self.sm.state.value, "observations": obs, "reflections": refl,
                 "transitions": len(self.sm.history)}
+
+
+# The names the executor module of the reference gives these tools and types (model/multimodal/seer_executor.py:42-135).
+YvSEERToolType = YvToolType
+YvSEERResult = YvToolResult
+YvSEERSearchTool = YvSearchTool
+YvSEERCodeExecTool = YvCodeExecTool
+YvSEERCalculateTool = YvCalculateTool
+YvSEERFileTool = YvFileTool
+
+
+def register_seer_tools(registry: Any, tools: Sequence[YvSEERToolBase]) -> List[str]:
+    """Registers tool objects in a ``models.agentic_mcp.YvCoreMCPToolRegistry`` (native tools whose handler is ``tool.run``)."""
+    from .agentic_mcp import YvMCPToolMetadata, YvMCPToolType
+    names = []
+    for t in tools:
+        if registry.register(YvMCPToolMetadata(t.name, (t.__doc__ or "").strip().split("\n")[0], {}, YvMCPToolType.NATIVE, t.run, tags=[str(getattr(t.tool_type, "value", t.tool_type))])):
+            names.append(t.name)
+    return names
