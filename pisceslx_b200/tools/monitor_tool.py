@@ -118,3 +118,139 @@ class PiscesLxToolsMonitorRunner:
 
 PiscesLxToolsMonitorOrchestrator = PiscesLxToolsMonitorImpl = PiscesLxToolsMonitorRunner
 PiscesLxMonitorAlertManager, PiscesLxMonitorStatsCollector = PiscesLxAlertManager, PiscesLxStatsCollector
+
+
+# ---- context, cache and configuration helpers of the monitor (reference tools/monitor/context_utils.py, alert_manager.py:30-45, config.py:31-41) ----
+class PiscesLxMonitorCache:
+    """A small key-value store with an optional time-to-live per entry and a directory per cache name."""
+
+    def __init__(self, root: Optional[str] = None, clock: Callable[[], float] = time.time):
+        self._data: Dict[str, Any] = {}
+        self._expiry: Dict[str, float] = {}
+        self._root, self._clock = root or os.path.join(os.path.expanduser("~"), ".pisceslx", "cache"), clock
+
+    def get_cache_dir(self, name: str) -> str:
+        d = os.path.join(self._root, name)
+        os.makedirs(d, exist_ok=True)
+        return d
+
+    def get(self, key: str, default: Any = None) -> Any:
+        t = self._expiry.get(key)
+        if t is not None and self._clock() >= t:
+            self._data.pop(key, None)
+            self._expiry.pop(key, None)
+        return self._data.get(key, default)
+
+    def set(self, key: str, value: Any, ttl: Optional[float] = None) -> None:
+        self._data[key] = value
+        if ttl is not None:
+            self._expiry[key] = self._clock() + ttl
+        else:
+            self._expiry.pop(key, None)
+
+    def __len__(self) -> int:
+        return len(self._data)
+
+
+class PiscesLxCoreEnhancedCacheManager(PiscesLxMonitorCache):
+    """The alert side's cache: entries live 300 s unless told otherwise."""
+
+    def set(self, key: str, value: Any, ttl: Optional[float] = 300.0) -> None:
+        super().set(key, value, ttl)
+
+
+class PiscesLxCoreConfigManager:
+    def __init__(self, data: Optional[Dict[str, Any]] = None):
+        self._data = dict(data or {})
+
+    def get(self, key: str, default: Any = None) -> Any:
+        cur: Any = self._data
+        for part in key.split("."):
+            if not isinstance(cur, dict) or part not in cur:
+                return default
+            cur = cur[part]
+        return cur
+
+    def set(self, key: str, value: Any) -> None:
+        cur = self._data
+        *path, leaf = key.split(".")
+        for part in path:
+            cur = cur.setdefault(part, {})
+        cur[leaf] = value
+
+
+class PiscesLxMonitorContext:
+    """Shared values and event hooks of one monitor; a hook that raises is dropped from that event, not from the list."""
+
+    def __init__(self) -> None:
+        self._ctx: Dict[str, Any] = {}
+        self._hooks: List[Callable[[str, Dict[str, Any]], None]] = []
+        self.hook_errors: List[str] = []
+
+    def set_context(self, key: str, value: Any) -> None:
+        self._ctx[key] = value
+
+    def get_context(self, key: str, default: Any = None) -> Any:
+        return self._ctx.get(key, default)
+
+    def add_hook(self, hook: Callable[[str, Dict[str, Any]], None]) -> None:
+        self._hooks.append(hook)
+
+    def emit_event(self, event_type: str, data: Optional[Dict[str, Any]] = None, **kwargs: Any) -> int:
+        payload = {**(data or {}), **kwargs}
+        n = 0
+        for h in list(self._hooks):
+            try:
+                h(event_type, payload)
+                n += 1
+            except Exception as e:
+                self.hook_errors.append(f"{event_type}: {type(e).__name__}: {e}")
+        return n
+
+
+class PiscesLxMonitorUtils:
+    """The helpers a monitor asks for: cache, device list (read-only NVML through ``utils.monitor``), filesystem, logger."""
+
+    def __init__(self, cache: Optional[PiscesLxMonitorCache] = None, system_monitor: Any = None, logger: Any = None):
+        self._cache, self._sys, self._logger = cache or PiscesLxMonitorCache(), system_monitor, logger
+
+    def get_cache_manager(self) -> PiscesLxMonitorCache:
+        return self._cache
+
+    def get_device_manager(self) -> Any:
+        if self._sys is None:
+            from ..utils.monitor import PiscesLxSystemMonitor
+            self._sys = PiscesLxSystemMonitor()
+        return self._sys
+
+    def get_fs_manager(self) -> Any:
+        from ..utils.core import PiscesLxFilesystem
+        return PiscesLxFilesystem()
+
+    def PiscesLxLogger(self) -> Any:
+        if self._logger is None:
+            import logging
+            self._logger = logging.getLogger("PiscesLx.Tools.Monitor")
+        return self._logger
+
+
+class PiscesLxMonitorContextManager(PiscesLxMonitorContext):
+    def __init__(self) -> None:
+        super().__init__()
+        self._utils = PiscesLxMonitorUtils()
+
+    def set_utils(self, cache_manager: Any = None, device_manager: Any = None, fs_manager: Any = None, logger: Any = None) -> None:
+        self._utils = PiscesLxMonitorUtils(cache_manager or self._utils._cache, device_manager or self._utils._sys, logger or self._utils._logger)
+        self._fs = fs_manager
+
+    def get_cache_manager(self) -> Any:
+        return self._utils.get_cache_manager()
+
+    def get_device_manager(self) -> Any:
+        return self._utils.get_device_manager()
+
+    def get_fs_manager(self) -> Any:
+        return getattr(self, "_fs", None) or self._utils.get_fs_manager()
+
+    def PiscesLxLogger(self) -> Any:
+        return self._utils.PiscesLxLogger()
