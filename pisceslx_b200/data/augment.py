@@ -207,3 +207,6 @@ def resolve_dataset(name: str, roots: Optional[Sequence[str]] = None) -> str:
     raise PiscesLxDatasetUnavailable(
         f"dataset {name!r} is not available offline; looked in: {', '.join(tried)}. Copy it there (any of jsonl / txt / "
         f"parquet / bin+idx) and re-run.")
+
+
+PiscesLxDataTextAugmenter = PiscesLxTextAugmenter                         # the reference names it by its folder (tools/data/augment/text_aug.py)
